@@ -1,0 +1,141 @@
+// Greedy choice and temperature sampling over 32-bit logits, one block per row.
+//
+// tamnd/fastmlx takes argmax at temperature 0, the first index on ties
+// (compute/sampler.go:38-39,61-72), and otherwise draws from softmax(logits / T) after its
+// filters; the draw itself is left to the tensor library there (sampler.go:17-22).  Here
+// the draw is an inverse-CDF walk in index order with a uniform number that the caller
+// derives from (seed, request, token index), so the token does not depend on what else is
+// in the batch.  Filters (top-p, min-p, top-k) are applied by the caller as a keep mask of
+// one byte per token, or none.
+#include <math.h>
+#include "common.cuh"
+
+namespace {
+constexpr int SBLOCK = 1024;
+
+struct Best { float v; int i; };
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+  // higher value wins; on equal values the lower index
+  if (b.i >= 0 && (a.i < 0 || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
+  return a;
+}
+
+__device__ Best block_argmax(const float* row, const unsigned char* keep, int V) {
+  __shared__ Best part[SBLOCK / 32];
+  __shared__ Best result;
+  Best b{-INFINITY, -1};
+  for (int i = threadIdx.x; i < V; i += SBLOCK) {
+    if (keep && !keep[i]) continue;
+    const float v = row[i];
+    if (b.i < 0 || v > b.v) b = Best{v, i};
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+    b = better(b, other);
+  }
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = b;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    Best c = threadIdx.x < SBLOCK / 32 ? part[threadIdx.x] : Best{-INFINITY, -1};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best other{__shfl_xor_sync(0xffffffffu, c.v, o), __shfl_xor_sync(0xffffffffu, c.i, o)};
+      c = better(c, other);
+    }
+    if (threadIdx.x == 0) result = c;
+  }
+  __syncthreads();
+  Best r = result;
+  __syncthreads();
+  return r;
+}
+
+// Inclusive prefix sum over the block in thread order; returns this thread's inclusive
+// value and the block total.
+__device__ float block_scan(float v, float* total) {
+  __shared__ float wsum[SBLOCK / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  if (lane == 31) wsum[warp] = x;
+  __syncthreads();
+  if (warp == 0) {
+    float s = wsum[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float y = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += y;
+    }
+    wsum[lane] = s;
+  }
+  __syncthreads();
+  const float before = warp > 0 ? wsum[warp - 1] : 0.f;
+  *total = wsum[SBLOCK / 32 - 1];
+  __syncthreads();
+  return x + before;
+}
+
+__global__ void __launch_bounds__(SBLOCK)
+sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
+              const float* __restrict__ uniform, const unsigned char* __restrict__ keep, long long keep_ld,
+              int* __restrict__ out) {
+  const int r = blockIdx.x;
+  const float* row = logits + (long long)r * ld;
+  const unsigned char* kp = keep ? keep + (long long)r * keep_ld : nullptr;
+  const Best top = block_argmax(row, kp, V);
+  const float T = temperature ? temperature[r] : 0.f;
+  if (!(T > 0.f) || top.i < 0) {
+    if (threadIdx.x == 0) out[r] = top.i;
+    return;
+  }
+  const float inv_t = 1.0f / T;
+  // total weight, each thread over a contiguous chunk so that the walk below is in index order
+  const int per = (V + SBLOCK - 1) / SBLOCK;
+  const int lo = threadIdx.x * per, hi = min(V, lo + per);
+  float mine = 0.f;
+  for (int i = lo; i < hi; ++i)
+    if (!kp || kp[i]) mine += expf((row[i] - top.v) * inv_t);
+  float total;
+  const float incl = block_scan(mine, &total);
+  const float target = uniform[r] * total;
+  __shared__ int chosen;
+  if (threadIdx.x == 0) chosen = -1;
+  __syncthreads();
+  const float before = incl - mine;
+  if (mine > 0.f && target >= before && target < incl) {
+    float run = before;
+    int pick = -1;
+    for (int i = lo; i < hi; ++i) {
+      if (kp && !kp[i]) continue;
+      const float wgt = expf((row[i] - top.v) * inv_t);
+      if (wgt <= 0.f) continue;
+      pick = i;
+      run += wgt;
+      if (target < run) break;
+    }
+    chosen = pick;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[r] = chosen >= 0 ? chosen : top.i;   // rounding at the far end: the mode
+}
+}  // namespace
+
+// out[r] = argmax of row r (first index on ties) where temperature[r] <= 0 or temperature is
+// null; else a draw from softmax(row / temperature[r]) restricted to keep[r, :] != 0, by the
+// uniform number uniform[r] in [0, 1).
+FMX_EXPORT int fmx_sample(const float* logits, long long ld, int rows, int V, const float* temperature,
+                          const float* uniform, const unsigned char* keep, long long keep_ld, int* out,
+                          cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (rows < 0 || V <= 0 || ld < V) return fmx_fail("fmx_sample: bad sizes rows=%d V=%d ld=%lld", rows, V, ld);
+  if (temperature != nullptr && uniform == nullptr) return fmx_fail("fmx_sample: a temperature needs uniform numbers");
+  sample_kernel<<<rows, SBLOCK, 0, stream>>>(logits, ld, V, temperature, uniform, keep, keep_ld, out);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}

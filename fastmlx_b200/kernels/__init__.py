@@ -1,0 +1,154 @@
+"""The kernel namespace that parts call: tensors in, tensors out, CUDA underneath.
+
+Every function launches hand-written sm_100a kernels from `csrc/` on the current stream.
+Matrix products of the bfloat16 path go to cuBLAS through `torch.mm`, where tamnd/fastmlx
+calls its library's matmul (compute/models/qwen3_forward.go:111-115 -> mlxgo/binding_cgo.go:
+324-328); the 32-bit path uses its own fixed-order kernel and never a reduced-precision
+matrix mode.  Nothing here runs on the CPU.
+"""
+from __future__ import annotations
+
+import torch
+
+from .lib import KernelError, call, load, loaded_libraries
+
+F32, BF16 = 0, 1
+BAD_TOKEN, BAD_SLOT, BAD_PAGE, BAD_ROW = 1, 2, 3, 4
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {t.dtype}")
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+# ----------------------------------------------------------------------------- rows
+def gather_rows(table: torch.Tensor, ids: torch.Tensor, status, code: int = BAD_ROW) -> torch.Tensor:
+    _need_cuda(table, ids)
+    assert ids.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    n, d = ids.numel(), table.shape[1]
+    out = torch.empty((n, d), dtype=table.dtype, device=table.device)
+    call("common", "fmx_gather_rows", table.data_ptr(), ids.data_ptr(), out.data_ptr(), n, d, table.shape[0],
+         _dt(table), _ptr(status), code, _stream())
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, status) -> torch.Tensor:
+    return gather_rows(table, ids, status, BAD_TOKEN)
+
+
+def add_rmsnorm(x: torch.Tensor, residual, weight: torch.Tensor, eps: float):
+    """-> (norm(residual + x) * weight, residual + x); the sum replaces `residual` in place.
+    Without a residual, x itself is the stream and is returned as such."""
+    _need_cuda(x, residual, weight)
+    assert x.dim() == 2 and x.is_contiguous() and weight.dtype == torch.float32
+    assert residual is None or (residual.shape == x.shape and residual.is_contiguous() and residual.dtype == x.dtype)
+    out = torch.empty_like(x)
+    call("common", "fmx_add_rmsnorm", x.data_ptr(), _ptr(residual), weight.data_ptr(), out.data_ptr(),
+         x.shape[0], x.shape[1], float(eps), _dt(x), _stream())
+    return out, (residual if residual is not None else x)
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    _need_cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    call("common", "fmx_silu_mul", gate_up.data_ptr(), out.data_ptr(), rows, inter, _dt(gate_up), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- matrix products
+def gemm_simple(x, w, bias, out_dtype) -> torch.Tensor:
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    call("common", "fmx_gemm_simple", x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
+         x.stride(0), w.stride(0), out.stride(0), _dt(x), _dt(w), _dt(out), _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
+    """x[M, K] @ w[N, K]^T (+ bias) -> [M, N] in `out_dtype`, accumulated in 32-bit."""
+    _need_cuda(x, w, bias)
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
+    assert x.stride(1) == 1 and w.stride(1) == 1
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0:
+        wt = w.t()
+        if bias is not None:
+            if out_dtype == torch.bfloat16:
+                return torch.addmm(bias.to(torch.bfloat16), x, wt)
+            return gemm_simple(x, w, bias, out_dtype)
+        if out_dtype == torch.bfloat16:
+            return torch.mm(x, wt)
+        return torch.mm(x, wt, out_dtype=out_dtype)
+    return gemm_simple(x, w, bias, out_dtype)
+
+
+# ----------------------------------------------------------------------------- positions and cache
+def rope_kv_write(qkv, positions, inv_freq, rotary_dim, traditional, slot_mapping, kv, nh, nkv, hd, status) -> None:
+    """Rotate q and k of qkv[T, (nh + 2 nkv) hd] in place and store k, v at slot_mapping."""
+    _need_cuda(qkv, positions, inv_freq, slot_mapping, kv)
+    assert qkv.dim() == 2 and qkv.stride(1) == 1 and positions.dtype == torch.int32
+    if kv is not None:
+        assert kv.is_contiguous() and kv.dtype == qkv.dtype and kv.shape[1] == 2 and kv.shape[2] == nkv \
+            and kv.shape[4] == hd and slot_mapping is not None and slot_mapping.dtype == torch.int64
+        num_pages, page_size = kv.shape[0], kv.shape[3]
+    else:
+        num_pages, page_size = 0, 1
+    call("common", "fmx_rope_kv_write", qkv.data_ptr(), positions.data_ptr(), _ptr(inv_freq), _ptr(slot_mapping),
+         _ptr(kv), qkv.shape[0], nh, nkv, hd, int(rotary_dim), int(bool(traditional)), page_size, num_pages,
+         qkv.stride(0), _dt(qkv), _ptr(status), _stream())
+
+
+def paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Tensor:
+    T = qkv.shape[0]
+    out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    bt = group.block_tables
+    call("common", "fmx_paged_attention_simple", qkv.data_ptr(), qkv.stride(0), kv.data_ptr(), bt.data_ptr(),
+         bt.stride(0), ctx.token_row.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), T, nh, nkv, hd,
+         kv.shape[3], kv.shape[0], float(scale), int(window), bt.shape[0], _dt(qkv), _ptr(ctx.status), _stream())
+    return out
+
+
+def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Tensor:
+    """Attention of every token of the step over the pages of its own request.
+    qkv[T, >= nh*hd] holds the (rotated) queries first; -> [T, nh*hd]."""
+    _need_cuda(qkv, kv)
+    assert kv.is_contiguous() and kv.dtype == qkv.dtype and qkv.stride(1) == 1
+    return paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
+
+
+# ----------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, temperature=None, uniform=None, keep=None) -> torch.Tensor:
+    """Row-wise token choice: argmax where temperature <= 0 (or None), else a draw from
+    softmax(logits / temperature) among keep != 0 by the given uniform numbers."""
+    _need_cuda(logits, temperature, uniform, keep)
+    assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if keep is not None:
+        assert keep.dtype == torch.uint8 and keep.shape == logits.shape and keep.stride(1) == 1
+    call("common", "fmx_sample", logits.data_ptr(), logits.stride(0), rows, V, _ptr(temperature), _ptr(uniform),
+         _ptr(keep), keep.stride(0) if keep is not None else 0, out.data_ptr(), _stream())
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    return sample(logits)

@@ -1,0 +1,63 @@
+"""Loads the CUDA libraries and declares their C entry points.
+
+There is no other implementation behind these calls: when the GPU, nvcc or a library is
+missing, the first kernel call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+from ..csrc import build as _build
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
+
+# name -> argument types (all return int: 0 ok, else fmx_last_error() tells why)
+_SIGNATURES = {
+    "common": {
+        "fmx_gather_rows": [_P, _P, _P, _I, _I, _L, _I, _P, _I, _P],
+        "fmx_add_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
+        "fmx_silu_mul": [_P, _P, _I, _I, _I, _P],
+        "fmx_gemm_simple": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
+        "fmx_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _L, _I, _P, _P],
+        "fmx_paged_attention_simple": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P],
+        "fmx_sample": [_P, _L, _I, _I, _P, _P, _P, _L, _P, _P],
+    },
+    "bf16": {},
+}
+
+_libs: dict[str, ctypes.CDLL] = {}
+
+
+def load(group: str) -> ctypes.CDLL:
+    lib = _libs.get(group)
+    if lib is not None:
+        return lib
+    try:
+        path = _build.build(group)
+        lib = ctypes.CDLL(path)
+    except (OSError, _build.BuildError) as e:
+        raise KernelError(f"the CUDA library of group {group!r} is not available: {e}") from None
+    lib.fmx_last_error.restype = ctypes.c_char_p
+    for name, args in _SIGNATURES[group].items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+    _libs[group] = lib
+    return lib
+
+
+def call(group: str, name: str, *args) -> None:
+    lib = load(group)
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise KernelError(lib.fmx_last_error().decode(errors="replace"))
+
+
+def loaded_libraries() -> dict[str, str]:
+    return {g: lib._name for g, lib in _libs.items()}

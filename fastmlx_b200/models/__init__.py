@@ -1,0 +1,2 @@
+"""Architectures.  Importing this package registers them."""
+from . import llama  # noqa: F401

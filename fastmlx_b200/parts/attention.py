@@ -1,0 +1,50 @@
+"""Grouped-query attention over a paged cache."""
+from __future__ import annotations
+
+from .base import Mixer, PagedKVSpec, PositionEncoding, Runtime
+from .linear import Linear
+
+
+class GQAAttention(Mixer):
+    """softmax(scale * q k^T + causal mask) v with nh query heads sharing nkv key/value
+    heads: query head h reads kv head h // (nh / nkv) (tamnd/fastmlx
+    compute/models/llama.go:403-422; the grouping happens inside its fused call,
+    mlxgo/binding_cgo.go:619-634).  Every query token sees the keys of its own request at
+    positions <= its own (compute/models/batch_mask.go:33-41), or only the last `window`.
+
+    The step writes this step's k and v into the pages first and then attends from the
+    pages alone, so a token's result does not depend on how the tokens were cut into steps.
+    With `share_kv=True` the part has no k/v projections and reads the cache of the
+    schedule entry it is pointed at.
+    """
+
+    def __init__(self, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 pos: PositionEncoding, name: str, bias: bool = False, scale: float | None = None,
+                 window: int = 0, share_kv: bool = False,
+                 proj_names=("q_proj", "k_proj", "v_proj", "o_proj")):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are no multiple of {num_kv_heads} kv heads")
+        self.nh, self.nkv, self.hd = int(num_heads), int(num_kv_heads), int(head_dim)
+        self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
+        self.window = int(window)
+        self.share_kv = bool(share_kv)
+        self.pos = pos
+        qn, kn, vn, on = (f"{name}.{p}" for p in proj_names)
+        outs = [(qn, self.nh * self.hd)]
+        if not share_kv:
+            outs += [(kn, self.nkv * self.hd), (vn, self.nkv * self.hd)]
+        self.qkv = Linear(width, outs, bias)
+        self.o = Linear(self.nh * self.hd, [(on, width)], bias)
+
+    def children(self):
+        return (self.qkv, self.o, self.pos)
+
+    def cache_spec(self):
+        return PagedKVSpec(self.nkv, self.hd, self.window)
+
+    def forward(self, x, ctx, cache):
+        qkv = self.qkv.forward(x)
+        self.pos.apply_and_store(qkv, ctx, cache, self.nh, 0 if self.share_kv else self.nkv, self.hd)
+        a = self.rt.k.paged_attention(qkv, cache.kv, ctx, ctx.groups[cache.group],
+                                      self.nh, self.nkv, self.hd, self.scale, self.window)
+        return self.o.forward(a)

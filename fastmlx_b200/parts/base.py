@@ -1,0 +1,145 @@
+"""Interfaces of the parts a model is assembled from.
+
+A part owns its sizes and constants as constructor parameters, declares the checkpoint
+tensors it binds (`weight_specs`) and what it needs from the cache manager, and runs on
+a flat batch of T tokens.  No part knows which model it is in: names of tensors are
+handed to it by the architecture's builder.
+
+tamnd/fastmlx hard-wires these choices inside one forward function
+(compute/models/llama.go:371-442) and models per-layer cache kinds as a list behind one
+interface (compute/kvcache.go:41-53) with two fixed-size state fields on the tensor cache
+(compute/models/cache.go:28-34); the split into parts below keeps that generality and
+makes the choice a per-layer datum.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Sequence
+
+import torch
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    """One checkpoint tensor: `kind` picks the random init (matrix, embedding and bias
+    N(0, 0.02); norm 1 + N(0, 0.02))."""
+    name: str
+    shape: tuple[int, ...]
+    kind: str = "matrix"
+
+
+@dataclass(frozen=True)
+class PagedKVSpec:
+    """A mixer that keeps keys and values of earlier tokens in pages.  `window` = 0
+    keeps every key; w > 0 only the last w (the page manager gives older pages back)."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size, kept in a slot (zero when a request starts)."""
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class Runtime:
+    """Where and how parts compute: the device, the activation dtype (bfloat16 or
+    float32) and the kernel namespace every part calls."""
+    device: torch.device
+    dtype: torch.dtype
+    k: Any                       # fastmlx_b200.kernels, or a stand-in with its functions
+
+    @property
+    def is_fp32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+class Part:
+    """Base of all parts: a tree whose leaves declare tensors."""
+
+    def children(self) -> Sequence["Part"]:
+        return ()
+
+    def own_weight_specs(self) -> list[WeightSpec]:
+        return []
+
+    def weight_specs(self) -> list[WeightSpec]:
+        specs = list(self.own_weight_specs())
+        for c in self.children():
+            specs.extend(c.weight_specs())
+        return specs
+
+    def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        """Take this part's tensors (already checked for presence and shape) onto the
+        device in the layout its kernels want."""
+        self.rt = rt
+        self.bind_own(tensors, rt)
+        for c in self.children():
+            c.bind(tensors, rt)
+
+    def bind_own(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        pass
+
+    def weight_bytes(self) -> int:
+        """Bytes of device weights one step reads (for the roofline)."""
+        return sum(c.weight_bytes() for c in self.children())
+
+
+def to_compute(t: torch.Tensor, rt: Runtime) -> torch.Tensor:
+    """A matrix for the compute path.  bfloat16 tensors widen exactly on the 32-bit path;
+    a tensor stored in 32-bit stays in 32-bit on either path."""
+    if t.dtype == torch.float32:
+        return t.to(rt.device).contiguous()
+    return t.to(device=rt.device, dtype=rt.dtype).contiguous()
+
+
+def to_f32_vector(t: torch.Tensor, rt: Runtime) -> torch.Tensor:
+    """Norm weights and biases are held in 32-bit (exact for either stored dtype)."""
+    return t.to(device=rt.device, dtype=torch.float32).contiguous()
+
+
+class Mixer(Part):
+    """Token mixer of a block (attention here).  forward(x[T, d], ctx, cache) -> [T, d_out]."""
+
+    def cache_spec(self) -> PagedKVSpec | None:
+        return None
+
+    def state_spec(self) -> StateSpec | None:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """forward(x[T, d], ctx) -> [T, d]; dense here, a routed one has the same face."""
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Norm(Part):
+    """forward(x, residual) -> (normed, residual'): residual' = residual + x (or x when
+    residual is None), summed in 32-bit and rounded once; normed = norm(residual')."""
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None):  # pragma: no cover
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Puts positions into the projected q and k of an attention mixer and stores k and v
+    in the layer's pages (one fused kernel)."""
+
+    def apply_and_store(self, qkv, ctx, cache, nh: int, nkv: int, hd: int) -> None:  # pragma: no cover
+        raise NotImplementedError
+
+
+@dataclass(frozen=True)
+class Run:
+    """One entry of a model's schedule: run `layer`; `cache_from` names an earlier
+    schedule entry whose cache this run reads instead of owning one."""
+    layer: int
+    cache_from: int | None = None

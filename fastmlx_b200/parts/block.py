@@ -1,0 +1,28 @@
+"""The arrangement of norm, mixer and feed-forward in one layer."""
+from __future__ import annotations
+
+from .base import FeedForward, Mixer, Norm, Part
+
+
+class PreNormBlock(Part):
+    """h += mixer(norm1(h)); h += ffn(norm2(h)) (tamnd/fastmlx compute/models/llama.go:402-429).
+    The stream is carried as (delta, residual): each norm first adds the delta to the
+    residual in 32-bit, then normalises the sum, so the add costs no pass of its own."""
+
+    def __init__(self, mixer: Mixer, ffn: FeedForward, norm1: Norm, norm2: Norm):
+        self.mixer, self.ffn, self.norm1, self.norm2 = mixer, ffn, norm1, norm2
+
+    def children(self):
+        return (self.norm1, self.mixer, self.norm2, self.ffn)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def state_spec(self):
+        return self.mixer.state_spec()
+
+    def forward(self, delta, residual, ctx, cache):
+        x, residual = self.norm1.forward(delta, residual)
+        a = self.mixer.forward(x, ctx, cache)
+        y, residual = self.norm2.forward(a, residual)
+        return self.ffn.forward(y, ctx), residual

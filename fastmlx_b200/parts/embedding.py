@@ -1,0 +1,53 @@
+"""Token embedding and output head."""
+from __future__ import annotations
+
+import torch
+
+from .base import Part, Runtime, WeightSpec, to_compute
+
+
+class Embedding(Part):
+    """h[t] = E[id_t], no scaling (tamnd/fastmlx compute/models/llama.go:385-390)."""
+
+    def __init__(self, vocab: int, width: int, name: str):
+        self.vocab, self.width, self.name = int(vocab), int(width), name
+        self.weight = None
+
+    def own_weight_specs(self):
+        return [WeightSpec(self.name + ".weight", (self.vocab, self.width), "embedding")]
+
+    def bind_own(self, tensors, rt: Runtime):
+        self.weight = to_compute(tensors[self.name + ".weight"], rt)
+
+    def weight_bytes(self):
+        return 0          # a step reads T rows, not the table
+
+    def forward(self, ids, ctx):
+        return self.rt.k.embedding(ids, self.weight, ctx.status)
+
+
+class LMHead(Part):
+    """logits = x W^T in 32-bit, no bias, cap or scale; W is the embedding table when the
+    model ties them (tamnd/fastmlx compute/models/llama.go:433-437).  Only the rows whose
+    logits are wanted reach it."""
+
+    def __init__(self, vocab: int, width: int, name: str | None, tied: Embedding | None = None):
+        if (name is None) == (tied is None):
+            raise ValueError("LMHead takes either a tensor name or an embedding to tie to")
+        self.vocab, self.width, self.name, self.tied = int(vocab), int(width), name, tied
+        self.weight = None
+
+    def own_weight_specs(self):
+        return [] if self.tied is not None else [WeightSpec(self.name + ".weight", (self.vocab, self.width), "matrix")]
+
+    def bind_own(self, tensors, rt: Runtime):
+        if self.tied is None:
+            self.weight = to_compute(tensors[self.name + ".weight"], rt)
+
+    def weight_bytes(self):
+        w = self.tied.weight if self.tied is not None else self.weight
+        return w.numel() * w.element_size()
+
+    def forward(self, x):
+        w = self.tied.weight if self.tied is not None else self.weight
+        return self.rt.k.linear(x, w, None, torch.float32)

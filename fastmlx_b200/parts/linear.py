@@ -1,0 +1,41 @@
+"""y = x W^T (+ b), W stored [out, in]."""
+from __future__ import annotations
+
+import torch
+
+from .base import Part, Runtime, WeightSpec, to_compute, to_f32_vector
+
+
+class Linear(Part):
+    """One or several checkpoint matrices applied as a single product: `names` lists
+    (tensor name prefix, out features); their rows are stacked at bind time, so q/k/v or
+    gate/up run as one matrix product (tamnd/fastmlx runs them one by one,
+    compute/models/llama.go:403-405,426-427, through compute/models/qwen3_forward.go:111-115)."""
+
+    def __init__(self, in_features: int, names, bias: bool = False):
+        self.in_features = int(in_features)
+        self.names = [(n, int(o)) for n, o in names]
+        self.out_features = sum(o for _, o in self.names)
+        self.has_bias = bool(bias)
+        self.weight = None
+        self.bias = None
+
+    def own_weight_specs(self):
+        specs = [WeightSpec(n + ".weight", (o, self.in_features), "matrix") for n, o in self.names]
+        if self.has_bias:
+            specs += [WeightSpec(n + ".bias", (o,), "bias") for n, o in self.names]
+        return specs
+
+    def bind_own(self, tensors, rt: Runtime):
+        ws = [to_compute(tensors[n + ".weight"], rt) for n, _ in self.names]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        self.weight = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
+        if self.has_bias:
+            self.bias = torch.cat([to_f32_vector(tensors[n + ".bias"], rt) for n, _ in self.names]).contiguous()
+
+    def weight_bytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, x, out_dtype=None):
+        return self.rt.k.linear(x, self.weight, self.bias, out_dtype or self.rt.dtype)

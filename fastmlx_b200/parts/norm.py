@@ -1,0 +1,25 @@
+"""RMSNorm with the residual sum fused in front of it."""
+from __future__ import annotations
+
+from .base import Norm, Runtime, WeightSpec, to_f32_vector
+
+
+class RMSNorm(Norm):
+    """x * rsqrt(mean(x^2) + eps) * w; the weight is a plain multiplier
+    (tamnd/fastmlx compute/models/llama.go:402,425,432 -> mlxgo/binding_cgo.go:382-396).
+    Sum of squares, rsqrt and the residual sum are 32-bit."""
+
+    def __init__(self, width: int, eps: float, name: str):
+        self.width, self.eps, self.name = int(width), float(eps), name
+
+    def own_weight_specs(self):
+        return [WeightSpec(self.name + ".weight", (self.width,), "norm")]
+
+    def bind_own(self, tensors, rt: Runtime):
+        self.weight = to_f32_vector(tensors[self.name + ".weight"], rt)
+
+    def weight_bytes(self):
+        return self.weight.numel() * 4
+
+    def forward(self, x, residual):
+        return self.rt.k.add_rmsnorm(x, residual, self.weight, self.eps)
