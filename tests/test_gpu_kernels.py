@@ -1,0 +1,325 @@
+"""Each CUDA kernel alone against its plain statement (tests/plain_ops.py), at sizes other
+than the engine's, in 32-bit and in bfloat16."""
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_ops
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def k():
+    import fastmlx_b200.kernels as kern
+    return kern
+
+
+def status():
+    return torch.zeros(4, dtype=torch.int32, device=DEV)
+
+
+def close(got, ref, dtype, what="", scale=None):
+    """32-bit: a few units of float32 rounding of the result's scale.  bfloat16: the same
+    value may round to the neighbouring bfloat16 (one unit in the last place = 2^-7
+    relative at worst) when 32-bit and 64-bit arithmetic land on different sides."""
+    got, ref = got.detach().double().cpu(), ref.detach().double().cpu()
+    s = ref.abs().max().item() if scale is None else scale
+    s = max(s, 1e-30)
+    if dtype == torch.float32:
+        tol = 2e-6 * s
+        bad = (got - ref).abs() > tol + 2e-6 * ref.abs()
+    else:
+        bad = (got - ref).abs() > 2.0 ** -7 * ref.abs() + 1e-3 * s
+    assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} off, worst {(got - ref).abs().max().item():.3e} (scale {s:.3e})"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+# ----------------------------------------------------------------------------- rows
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,d,n", [(131, 80, 7), (320, 2048, 33), (50, 100, 5), (17, 3, 4)])
+def test_embedding(dtype, V, d, n):
+    table = rnd(V, d, dtype=dtype)
+    ids = torch.randint(0, V, (n,), dtype=torch.int32)
+    st = status()
+    out = k().embedding(ids.to(DEV), table.to(DEV), st)
+    assert torch.equal(out.cpu(), table[ids.long()])
+    assert st.tolist()[0] == 0
+
+
+def test_embedding_bad_id_leaves_code_not_fault():
+    table = rnd(10, 16).to(DEV)
+    st = status()
+    out = k().embedding(torch.tensor([1, 10, 2], dtype=torch.int32, device=DEV), table, st)
+    assert st.tolist()[0] == k().BAD_TOKEN and st.tolist()[1] == 10
+    assert torch.equal(out[0].cpu(), table[1].cpu()) and float(out[1].abs().sum()) == 0.0
+
+
+# ----------------------------------------------------------------------------- norm
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,d,eps", [(1, 64, 1e-5), (5, 192, 1e-6), (33, 80, 1e-3), (4, 2048, 1e-5), (3, 1000, 1e-5), (2, 5, 0.0)])
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_add_rmsnorm(dtype, rows, d, eps, with_residual):
+    x = rnd(rows, d, dtype=dtype, seed=1, scale=3.0)
+    res = rnd(rows, d, dtype=dtype, seed=2, scale=5.0) if with_residual else None
+    w = 1 + rnd(d, seed=3, scale=0.1)
+    ref_out, ref_res = plain_ops.add_rmsnorm(x.clone(), res.clone() if with_residual else None, w, eps)
+    xd = x.to(DEV)
+    rd = res.to(DEV) if with_residual else None
+    out, res_out = k().add_rmsnorm(xd, rd, w.to(DEV), eps)
+    close(out, ref_out, dtype, "norm")
+    if with_residual:
+        assert res_out.data_ptr() == rd.data_ptr()
+        close(res_out, ref_res, dtype, "residual")
+    else:
+        assert res_out.data_ptr() == xd.data_ptr()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,I", [(1, 176), (7, 512), (3, 200), (65, 8192), (2, 1)])
+def test_silu_mul(dtype, rows, I):
+    gu = rnd(rows, 2 * I, dtype=dtype, seed=4, scale=4.0)
+    close(k().silu_mul(gu.to(DEV)), plain_ops.silu_mul(gu), dtype, "silu_mul")
+
+
+# ----------------------------------------------------------------------------- matrix products
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (7, 131, 80), (65, 192, 500), (130, 70, 33), (3, 320, 192), (64, 64, 16)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_f32_fixed_order(M, N, K, bias):
+    x, w = rnd(M, K, seed=5), rnd(N, K, seed=6)
+    b = rnd(N, seed=7) if bias else None
+    ref = plain_ops.linear(x, w, b, torch.float64)
+    got = k().linear(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, torch.float32)
+    bound = (x.abs().double() @ w.abs().double().t()) * 1.2e-7 * 4 + 1e-30   # a few roundings of the running sum
+    assert ((got.cpu().double() - ref).abs() <= bound * (K ** 0.5 + 2)).all()
+
+
+def test_gemm_f32_result_does_not_depend_on_the_batch():
+    """A row's product is bit-identical whether it runs alone or among 100 others."""
+    x, w = rnd(101, 300, seed=8).to(DEV), rnd(77, 300, seed=9).to(DEV)
+    full = k().linear(x, w, None, torch.float32)
+    for r in (0, 50, 100):
+        alone = k().linear(x[r:r + 1].contiguous(), w, None, torch.float32)
+        assert torch.equal(alone[0], full[r])
+    part = k().linear(x[37:90], w, None, torch.float32)       # a strided view of rows
+    assert torch.equal(part, full[37:90])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (9, 136, 80), (70, 192, 512), (2048, 320, 192)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_bf16(M, N, K, out_dtype, bias):
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=5), rnd(N, K, dtype=torch.bfloat16, seed=6)
+    b = rnd(N, seed=7).bfloat16().float() if bias else None
+    ref = plain_ops.linear(x, w, b, torch.float64)
+    got = k().linear(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, out_dtype)
+    assert got.dtype == out_dtype
+    close(got, ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32, "linear", scale=ref.abs().max().item() * 8)
+
+
+@pytest.mark.parametrize("ta,tw,tc", [(torch.bfloat16, torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32, torch.float32),
+                                      (torch.bfloat16, torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16)])
+def test_gemm_simple_mixed_types(ta, tw, tc):
+    x, w = rnd(19, 70, dtype=ta, seed=1), rnd(45, 70, dtype=tw, seed=2)
+    got = k().gemm_simple(x.to(DEV), w.to(DEV), None, tc)
+    close(got, plain_ops.linear(x, w, None, torch.float64), tc, "gemm_simple", scale=None)
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+def _paged(n_rows, lens, page_size, num_pages, seed=0):
+    """Block tables that scatter each row's pages over the pool in a shuffled order."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    max_blocks = max(-(-n // page_size) for n in lens)
+    bt = torch.full((n_rows, max_blocks + 1), -1, dtype=torch.int32)
+    for r, n in enumerate(lens):
+        for b in range(-(-n // page_size)):
+            bt[r, b] = perm.pop()
+    return bt
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot,trad", [(4, 2, 16, 16, False), (6, 3, 32, 32, False), (5, 1, 48, 48, True),
+                                                 (8, 2, 64, 32, False), (3, 3, 128, 128, False), (2, 1, 80, 40, True),
+                                                 (4, 0, 32, 32, False), (4, 2, 32, 0, False)])
+def test_rope_kv_write(dtype, nh, nkv, hd, rot, trad):
+    T, page_size, num_pages = 23, 8, 9
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=1)
+    positions = torch.tensor([0, 1, 2, 3, 63, 64, 65, 500, 8191, 8192, 100000, 131071] + list(range(7, 18)), dtype=torch.int32)
+    inv_freq = (10000.0 ** (-torch.arange(0, max(rot, 2), 2, dtype=torch.float64) / max(rot, 2))).float()
+    slots = torch.randperm(num_pages * page_size, generator=torch.Generator().manual_seed(2))[:T].long()
+    slots[5] = -1                                                # a padding token is stored nowhere
+    kv_ref = torch.zeros(num_pages, 2, max(nkv, 1), page_size, hd, dtype=dtype)
+    kv_dev = kv_ref.clone().to(DEV)
+    q_ref = qkv.clone()
+    st_ref = torch.zeros(4, dtype=torch.int32)
+    plain_ops.rope_kv_write(q_ref, positions, inv_freq, rot, trad, slots, kv_ref if nkv else None, nh, nkv, hd, st_ref)
+    q_dev = qkv.clone().to(DEV)
+    st = status()
+    k().rope_kv_write(q_dev, positions.to(DEV), inv_freq.to(DEV), rot, trad, slots.to(DEV), kv_dev if nkv else None,
+                      nh, nkv, hd, st)
+    assert st.tolist()[0] == 0
+    close(q_dev, q_ref, dtype, "rotated qkv")
+    close(kv_dev, kv_ref, dtype, "pages", scale=1.0)
+
+
+def test_rope_bad_slot_leaves_code():
+    qkv = rnd(2, 4 * 16).to(DEV)
+    kv = torch.zeros(2, 2, 1, 4, 16, device=DEV)
+    st = status()
+    k().rope_kv_write(qkv, torch.zeros(2, dtype=torch.int32, device=DEV), torch.ones(8, device=DEV), 16, False,
+                      torch.tensor([0, 99], device=DEV), kv, 2, 1, 16, st)
+    assert st.tolist()[:2] == [k().BAD_SLOT, 99]
+
+
+# ----------------------------------------------------------------------------- attention over pages
+def _attention_case(dtype, nh, nkv, hd, page_size, rows, window=0, seed=0, spike=None):
+    """rows: list of (ctx_before, q_len).  Pages are filled for every position < ctx+q."""
+    lens = [c + q for c, q in rows]
+    num_pages = sum(-(-n // page_size) for n in lens) + 3
+    bt = _paged(len(rows), lens, page_size, num_pages, seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    kv = torch.randn(num_pages, 2, nkv, page_size, hd, generator=g).to(dtype)
+    T = sum(q for _, q in rows)
+    q = torch.randn(T, nh * hd, generator=g).to(dtype)
+    pos, trow = [], []
+    for r, (c, ql) in enumerate(rows):
+        pos += list(range(c, c + ql))
+        trow += [r] * ql
+    if spike is not None:
+        # One far key is made to stand out for one query: the query and that key are scaled
+        # along a common direction so its score dominates, and its value row is marked.
+        t, key_pos, head = spike
+        r = trow[t]
+        page = int(bt[r, key_pos // page_size])
+        gk = head // (nh // nkv)
+        d = torch.randn(hd, generator=g)
+        d = d / d.norm()
+        q[t, head * hd:(head + 1) * hd] = (d * 12.0).to(dtype)
+        kv[page, 0, gk, key_pos % page_size] = (d * 12.0).to(dtype)
+        kv[page, 1, gk, key_pos % page_size] = torch.full((hd,), 7.0).to(dtype)
+    ctx = SimpleNamespace(positions=torch.tensor(pos, dtype=torch.int32), token_row=torch.tensor(trow, dtype=torch.int32),
+                          status=torch.zeros(4, dtype=torch.int32))
+    grp = SimpleNamespace(block_tables=bt)
+    return q, kv, ctx, grp
+
+
+def _to_dev(ctx, grp):
+    return (SimpleNamespace(positions=ctx.positions.to(DEV), token_row=ctx.token_row.to(DEV), status=status(),
+                            all_decode=False, max_q_len=0, max_ctx_after=0, row_start=None, row_ctx=None, R=grp.block_tables.shape[0], scratch={}),
+            SimpleNamespace(block_tables=grp.block_tables.to(DEV), page_size=None))
+
+
+ATT_SHAPES = [(4, 2, 16, 16), (6, 3, 32, 16), (5, 1, 48, 8), (8, 8, 64, 32), (12, 4, 128, 64), (3, 3, 80, 16), (2, 1, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,page_size", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 24])
+def test_paged_attention_simple_mixed_rows(dtype, nh, nkv, hd, page_size, window):
+    rows = [(0, 37), (90, 1), (31, 2), (0, 1), (15, 17), (64, 1)]
+    q, kv, ctx, grp = _attention_case(dtype, nh, nkv, hd, page_size, rows, window)
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, window)
+    dctx, dgrp = _to_dev(ctx, grp)
+    got = k().paged_attention_simple(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, window)
+    assert dctx.status.tolist()[0] == 0
+    close(got, ref, dtype, "attention", scale=1.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key_pos", [0, 15, 16, 17, 31, 32, 63, 64, 511, 512, 700])
+def test_paged_attention_simple_far_key_stands_out(dtype, key_pos):
+    """Among 701 keys one is made dominant; a kernel that misses it (a page's edge, a
+    chunk's edge) returns something far from its marked value."""
+    nh, nkv, hd, page_size = 4, 2, 32, 16
+    rows = [(700, 1), (0, 5)]
+    q, kv, ctx, grp = _attention_case(dtype, nh, nkv, hd, page_size, rows, spike=(0, key_pos, 3))
+    dctx, dgrp = _to_dev(ctx, grp)
+    got = k().paged_attention_simple(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, 1.0, 0)
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, 1.0, 0)
+    assert (ref[0, 3 * hd:4 * hd].float() - 7.0).abs().max() < 0.1
+    close(got, ref, dtype, "attention with a dominant key", scale=7.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_simple_window_edge(dtype):
+    """The key just outside a window must not count even when it would dominate; the one
+    just inside must."""
+    nh, nkv, hd, page_size, window = 2, 1, 32, 16, 40
+    for key_pos, inside in ((100 - 40, False), (100 - 39, True)):
+        rows = [(100, 1)]
+        q, kv, ctx, grp = _attention_case(dtype, nh, nkv, hd, page_size, rows, window, spike=(0, key_pos, 1))
+        dctx, dgrp = _to_dev(ctx, grp)
+        got = k().paged_attention_simple(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, 1.0, window)
+        ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, 1.0, window)
+        assert ((ref[0, hd:].float() - 7.0).abs().max() < 0.1) == inside
+        close(got, ref, dtype, "window edge", scale=7.0)
+
+
+def test_paged_attention_never_reads_unseen_keys():
+    """Pages hold NaN wherever a key is not visible: the result must stay finite."""
+    nh, nkv, hd, page_size = 4, 2, 32, 16
+    rows = [(20, 3), (0, 9)]
+    q, kv, ctx, grp = _attention_case(torch.float32, nh, nkv, hd, page_size, rows)
+    lens = [c + ql for c, ql in rows]
+    poisoned = torch.full_like(kv, float("nan"))
+    for r, n in enumerate(lens):
+        for j in range(n):
+            p = int(grp.block_tables[r, j // page_size])
+            poisoned[p, :, :, j % page_size] = kv[p, :, :, j % page_size]
+    dctx, dgrp = _to_dev(ctx, grp)
+    got = k().paged_attention_simple(q.to(DEV), poisoned.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, 0)
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, 0)
+    assert torch.isfinite(got).all()
+    close(got, ref, torch.float32, "attention", scale=1.0)
+
+
+# ----------------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("V", [131, 320, 1000, 128256])
+def test_argmax_first_index_on_ties(V):
+    logits = rnd(5, V, seed=3)
+    logits[1, 7] = logits[1, V - 2] = 50.0
+    logits[2, :] = 0.0
+    logits[3, V - 1] = 60.0
+    got = k().argmax(logits.to(DEV)).cpu()
+    assert got.tolist() == plain_ops.argmax(logits).tolist()
+    assert got[1] == 7 and got[2] == 0 and got[3] == V - 1
+
+
+@pytest.mark.parametrize("V", [131, 320, 5000, 128256])
+def test_temperature_sampling_matches_inverse_cdf(V):
+    rows = 24
+    logits = rnd(rows, V, seed=5, scale=3.0)
+    temps = torch.tensor([0.0, 0.7, 1.0, 1.5] * (rows // 4))
+    u = torch.rand(rows, generator=torch.Generator().manual_seed(6))
+    u[1], u[2] = 0.0, 0.99999994
+    got = k().sample(logits.to(DEV), temps.to(DEV), u.to(DEV)).cpu()
+    for r in range(rows):
+        if temps[r] == 0:
+            assert got[r] == int(torch.argmax(logits[r]))
+            continue
+        w = torch.softmax(logits[r].double() / temps[r].double(), 0)
+        c = torch.cumsum(w, 0)
+        i = int(got[r])
+        lo, hi = (c[i - 1].item() if i > 0 else 0.0), c[i].item()
+        # the chosen token's interval of the CDF holds u, up to 32-bit rounding of the running sum
+        assert lo - 1e-4 <= u[r].item() <= hi + 1e-4, (r, i, lo, u[r].item(), hi)
+
+
+def test_sampling_keep_mask():
+    V = 300
+    logits = rnd(6, V, seed=8)
+    keep = torch.zeros(6, V, dtype=torch.uint8)
+    keep[:, 100:110] = 1
+    temps = torch.tensor([0.0, 1.0, 1.0, 2.0, 0.5, 1.0])
+    u = torch.tensor([0.1, 0.0, 0.999, 0.5, 0.3, 0.7])
+    got = k().sample(logits.to(DEV), temps.to(DEV), u.to(DEV), keep.to(DEV)).cpu()
+    assert ((got >= 100) & (got < 110)).all()
+    assert got.tolist() == plain_ops.sample(logits, temps, u, keep).tolist()
