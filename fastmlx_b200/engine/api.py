@@ -1,0 +1,167 @@
+"""The Python entry point: an engine that takes token ids and gives token ids.
+
+Modelled on tamnd/fastmlx's enginecore.BatchedEngine (enginecore/batched.go:38-82: Submit,
+Abort, Start/Stop around a scheduler) and its core loop (enginecore/core.go:134-171: drain
+submissions, step the scheduler, deliver outputs).  There is no tokenizer and no HTTP
+layer here; prompts are lists of token ids.
+"""
+from __future__ import annotations
+
+import hashlib
+import itertools
+from dataclasses import dataclass
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..sampling import Sampler, SamplingParams
+from .loading import load_model, parse_dtype, random_model
+from .request import Request, RequestOutput, RequestStatus
+from .scheduler import Scheduler, SchedulerConfig
+from .step import StepError, StepFunction
+
+
+@dataclass
+class EngineConfig:
+    """Option names follow `fastmlx serve` where it has them (cmd/fastmlx/serve.go:55-75:
+    --max-concurrent-requests, --initial-cache-blocks) and its scheduler's config
+    (scheduler/scheduler.go:30-47: MaxNumSeqs, MaxNumBatchedTokens)."""
+    dtype: str = "bfloat16"
+    block_size: int = 16                      # tokens per cache page
+    initial_cache_blocks: int = 0             # pages per layer group; 0 = from kv_memory_gb or max_cache_tokens
+    kv_memory_gb: float = 0.0
+    max_cache_tokens: int = 0
+    max_concurrent_requests: int = 8          # the scheduler's MaxNumSeqs
+    max_num_batched_tokens: int = 8192
+    prefill_chunk: int = 0
+    seed: int = 0
+    cuda_graphs: bool = True
+    device: str = "cuda"
+
+
+def _request_seed(engine_seed: int, request_id: str) -> int:
+    h = hashlib.sha256(f"{engine_seed}:{request_id}".encode()).digest()
+    return int.from_bytes(h[:8], "little") & (2**63 - 1)
+
+
+class Engine:
+    def __init__(self, model_dir: str | None = None, *, config: dict | None = None, weights_seed: int = 0,
+                 engine_config: EngineConfig | None = None, kernels=None, **overrides):
+        """Either `model_dir` (config.json + safetensors) or `config` (a config.json dict,
+        with seeded random weights)."""
+        ec = engine_config or EngineConfig()
+        for k, v in overrides.items():
+            if not hasattr(ec, k):
+                raise TypeError(f"unknown engine option {k!r}")
+            setattr(ec, k, v)
+        self.engine_config = ec
+        if (model_dir is None) == (config is None):
+            raise ValueError("give either a model folder or a configuration")
+        if model_dir is not None:
+            self.config, self.model, self.rt = load_model(model_dir, ec.dtype, ec.device, kernels)
+        else:
+            self.config, self.model, self.rt = random_model(config, weights_seed, ec.dtype, ec.device, kernels)
+        needs = self.model.cache_needs()
+        probe = CacheManager(needs, page_size=ec.block_size, num_pages=1, max_requests=1, dtype=self.rt.dtype,
+                             allocate=False)
+        per_token = max(1, probe.bytes_per_token())
+        if ec.initial_cache_blocks > 0:
+            pages = ec.initial_cache_blocks
+        elif ec.max_cache_tokens > 0:
+            pages = -(-ec.max_cache_tokens // ec.block_size)
+        elif ec.kv_memory_gb > 0:
+            pages = int(ec.kv_memory_gb * 2**30 // (per_token * ec.block_size))
+        else:
+            limit = self.model.max_positions or 8192
+            pages = -(-min(limit, 8192) // ec.block_size) * ec.max_concurrent_requests
+        self.manager = CacheManager(needs, page_size=ec.block_size, num_pages=max(1, pages),
+                                    max_requests=ec.max_concurrent_requests, dtype=self.rt.dtype,
+                                    device=self.rt.device)
+        self.step_fn = StepFunction(self.model, self.manager, self.rt, cuda_graphs=ec.cuda_graphs)
+        self.scheduler = Scheduler(self.manager, SchedulerConfig(ec.max_concurrent_requests,
+                                                                 ec.max_num_batched_tokens, ec.prefill_chunk),
+                                   eos_token_ids=self.model.eos_token_ids, max_positions=self.model.max_positions)
+        self.sampler = Sampler(self.rt)
+        self._ids = itertools.count()
+        self._pending_outputs: list[RequestOutput] = []
+        self._requests: dict[str, Request] = {}
+        self.counters = {"steps": 0, "prompt_tokens": 0, "generated_tokens": 0, "preemptions": 0, "h2d_bytes": 0,
+                         "d2h_bytes": 0}
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, prompt_token_ids, sampling: SamplingParams | None = None, request_id: str | None = None) -> str:
+        rid = request_id if request_id is not None else f"req-{next(self._ids)}"
+        if rid in self._requests:
+            raise KeyError(f"request id {rid!r} is in use")
+        sp = sampling or SamplingParams()
+        req = Request(rid, [int(t) for t in prompt_token_ids], sp)
+        req.seed = sp.seed if sp.seed is not None else _request_seed(self.engine_config.seed, rid)
+        out = self.scheduler.add_request(req)
+        if out is not None:
+            self._pending_outputs.append(out)
+        else:
+            self._requests[rid] = req
+        return rid
+
+    def abort(self, request_id: str) -> None:
+        self.scheduler.abort(request_id)
+
+    def has_unfinished(self) -> bool:
+        return bool(self._pending_outputs) or self.scheduler.has_unfinished()
+
+    # ------------------------------------------------------------------ one iteration
+    def step(self) -> list[RequestOutput]:
+        outs, self._pending_outputs = self._pending_outputs, []
+        if not self.scheduler.has_unfinished():
+            return outs
+        plan = self.scheduler.schedule()
+        for req in plan.finished:
+            outs.append(self.scheduler._output(req, []))
+            self._requests.pop(req.request_id, None)
+        self.counters["preemptions"] = self.scheduler.num_preemptions
+        if not plan.entries:
+            return outs
+        try:
+            logits = self.step_fn.run(plan.entries, reserved=True, check=False)
+            rows = [(req.sampling, req.seed, len(req.output_token_ids), req.all_token_ids)
+                    for req, s in zip(plan.requests, plan.samples) if s]
+            tokens = self.sampler.sample(logits, rows).tolist() if rows else []
+            self.step_fn.check_status()
+        except (StepError, RuntimeError) as e:
+            outs.extend(self.scheduler.step_failed(plan, str(e)))
+            for req in plan.requests:
+                self._requests.pop(req.request_id, None)
+            return outs
+        self.counters["steps"] += 1
+        self.counters["h2d_bytes"] += self.step_fn.last_h2d_bytes
+        self.counters["d2h_bytes"] += 4 * len(tokens) + 16
+        for req, entry, s in zip(plan.requests, plan.entries, plan.samples):
+            done_before = req.num_computed
+            n_prompt = len(req.prompt_token_ids)
+            self.counters["prompt_tokens"] += max(0, min(n_prompt, done_before + len(entry.tokens)) - min(n_prompt, done_before))
+        self.counters["generated_tokens"] += len(tokens)
+        for out in self.scheduler.step_done(plan, tokens):
+            outs.append(out)
+            if out.finished:
+                self._requests.pop(out.request_id, None)
+        return outs
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts, sampling: SamplingParams | list[SamplingParams] | None = None) -> list[RequestOutput]:
+        """Run the prompts (lists of token ids) to the end; -> final outputs in prompt order."""
+        if prompts and isinstance(prompts[0], int):
+            prompts = [prompts]
+        params = sampling if isinstance(sampling, list) else [sampling] * len(prompts)
+        ids = [self.submit(p, sp) for p, sp in zip(prompts, params)]
+        final: dict[str, RequestOutput] = {}
+        while self.has_unfinished():
+            for out in self.step():
+                if out.finished:
+                    final[out.request_id] = out
+        return [final[i] for i in ids]
+
+    def stats(self) -> dict:
+        g = self.manager.groups
+        return dict(self.counters, waiting=len(self.scheduler.waiting), running=len(self.scheduler.running),
+                    pages_total=sum(x.pool.num_pages for x in g), pages_used=sum(x.pool.used_pages for x in g),
+                    model_steps=self.step_fn.steps, graph_replays=self.step_fn.graph_replays)

@@ -26,16 +26,21 @@ _STATUS_TEXT = {1: "a token id outside the vocabulary", 2: "a cache slot outside
 
 
 class StepFunction:
-    def __init__(self, model, manager: CacheManager, rt):
+    def __init__(self, model, manager: CacheManager, rt, cuda_graphs: bool = False):
         self.model, self.manager, self.rt = model, manager, rt
+        self.cuda_graphs = bool(cuda_graphs) and rt.device.type == "cuda"
+        self.graph_replays = 0
+        self.last_h2d_bytes = 0
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=rt.device)
         self.steps = 0
         self.tokens_run = 0
         self.last_ctx: StepContext | None = None
 
-    def run(self, entries: list[StepEntry]) -> torch.Tensor:
+    def run(self, entries: list[StepEntry], reserved: bool = False, check: bool = True) -> torch.Tensor:
         """-> float32 logits [sum(len(e.want)), vocab] on the device, in the order of the
-        entries and of their `want`."""
+        entries and of their `want`.  `reserved`: the caller (the scheduler) has taken the
+        pages already and commits or rolls back itself.  `check=False` leaves the read of
+        the kernels' status word to the caller, who reads results from the device anyway."""
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -48,20 +53,23 @@ class StepFunction:
             limit = self.model.max_positions
             if limit and e.request.length + len(e.tokens) > limit:
                 raise StepError(f"request {e.request.request_id!r} would pass max_position_embeddings ({limit})")
-        reserved = []
+        taken = []
         try:
-            for e in entries:
-                self.manager.reserve(e.request, len(e.tokens))
-                reserved.append(e.request)
+            if not reserved:
+                for e in entries:
+                    self.manager.reserve(e.request, len(e.tokens))
+                    taken.append(e.request)
             ctx = build_context(entries, self.manager, self.rt.device, self.status)
             logits = self.model.forward(ctx)
-            self.check_status()
+            if check:
+                self.check_status()
         except BaseException:
-            for r in reserved:
+            for r in taken:
                 self.manager.rollback(r)
             raise
-        for r in reserved:
+        for r in taken:
             self.manager.commit(r)
+        self.last_h2d_bytes = ctx.scratch.get("h2d_bytes", 0)
         self.steps += 1
         self.tokens_run += ctx.T
         self.last_ctx = ctx

@@ -152,3 +152,32 @@ def sample(logits: torch.Tensor, temperature=None, uniform=None, keep=None) -> t
 
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     return sample(logits)
+
+
+def filter_mask(logits, top_p=None, min_p=None, top_k=None, min_keep=None) -> torch.Tensor:
+    """uint8 [rows, V]: 1 where the row's filters (top-p, then min-p, then top-k) keep the token.
+    Each argument is a per-row tensor (float32 / int32) or None for "off"."""
+    _need_cuda(logits, top_p, min_p, top_k, min_keep)
+    assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
+    rows, V = logits.shape
+    keep = torch.empty((rows, V), dtype=torch.uint8, device=logits.device)
+    call("common", "fmx_filter_mask", logits.data_ptr(), logits.stride(0), rows, V, _ptr(top_p), _ptr(min_p),
+         _ptr(top_k), _ptr(min_keep), keep.data_ptr(), keep.stride(0), _stream())
+    return keep
+
+
+def penalties(logits, history, repetition, presence, frequency, windows) -> None:
+    """In place on float32 logits [rows, V].  history int32 [rows, H] (oldest first, -1 padded
+    in front); repetition/presence/frequency float32 [rows] or None; windows int32 [rows, 3]."""
+    _need_cuda(logits, history, repetition, presence, frequency, windows)
+    assert logits.dtype == torch.float32 and history.dtype == torch.int32 and windows.dtype == torch.int32
+    call("common", "fmx_penalties", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1],
+         history.data_ptr(), history.shape[1], _ptr(repetition), _ptr(presence), _ptr(frequency),
+         windows.data_ptr(), _stream())
+
+
+def logit_bias(logits, rows, ids, values) -> None:
+    """logits[rows[i], ids[i]] += values[i], in place."""
+    _need_cuda(logits, rows, ids, values)
+    call("common", "fmx_logit_bias", logits.data_ptr(), logits.stride(0), logits.shape[1], rows.data_ptr(),
+         ids.data_ptr(), values.data_ptr(), rows.numel(), _stream())

@@ -1,0 +1,168 @@
+"""Generation through the Python entry point and the command line, on the GPU, against the
+plain model; what happens when pages run out; sampling with a fixed seed."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama
+import tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {n: tiny.make_model_dir(root, c, seed=21) for n, c in tiny.CONFIGS.items()}
+
+
+def _plain_greedy_with_margins(cfg, W, prompt, n, round_to):
+    """Tokens of the plain model, and for each the gap between its two best logits."""
+    seq, margins = list(prompt), []
+    for _ in range(n):
+        row = plain_llama.forward(cfg, W, seq, round_to)[-1]
+        top = torch.topk(row, 2).values
+        margins.append((top[0] - top[1]).item() / row.abs().max().item())
+        seq.append(int(torch.argmax(row)))
+    return seq[len(prompt):], margins
+
+
+def _agree(got, want, margins, slack):
+    """Equal token by token; where the plain model's two best logits are closer than the
+    dtype's tolerance either may win, and the sequences part ways legitimately."""
+    for i, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            assert margins[i] < slack, f"token {i}: engine {g}, plain {w}, margin {margins[i]:.2e}"
+            return
+    assert len(got) == len(want)
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-5), ("bfloat16", 2e-2)])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_matches_plain(dirs, dtype, slack, graphs):
+    from fastmlx_b200 import Engine, SamplingParams
+    cfg = tiny.TINY_A
+    W = tiny.load_plain_weights(dirs["A"])
+    prompts = [tiny.rand_tokens(n, cfg["vocab_size"], 40 + n) for n in (7, 13, 29)]
+    eng = Engine(dirs["A"], dtype=dtype, block_size=16, max_cache_tokens=512, max_concurrent_requests=4,
+                 cuda_graphs=graphs)
+    outs = eng.generate(prompts, SamplingParams(max_tokens=16, temperature=0.0))
+    rt = torch.bfloat16 if dtype == "bfloat16" else None
+    for p, out in zip(prompts, outs):
+        assert out.finished and out.finish_reason == "length" and out.completion_tokens == 16
+        want, margins = _plain_greedy_with_margins(cfg, W, p, 16, rt)
+        _agree(out.output_token_ids, want, margins, slack)
+    st = eng.stats()
+    assert st["pages_used"] == 0 and st["generated_tokens"] == 48 and st["prompt_tokens"] == 49
+    if graphs:
+        assert st["graph_replays"] > 0
+
+
+def test_mixed_batch_with_temperature_is_reproducible_and_cut_invariant(dirs):
+    """Five prompts of 1..200 tokens, 32-token portions, 24 decoded tokens each, temperature
+    0.7 from a fixed seed, page size 16: the tokens do not depend on the token budget, on the
+    number of sequences that run together, or on whether a request runs alone."""
+    from fastmlx_b200 import Engine, SamplingParams
+    cfg = tiny.TINY_B
+    prompts = [tiny.rand_tokens(n, cfg["vocab_size"], 60 + n) for n in (1, 17, 64, 100, 200)]
+    sps = [SamplingParams(max_tokens=24, temperature=0.7, seed=1234 + i) for i in range(5)]
+
+    def run(**kw):
+        eng = Engine(dirs["B"], dtype="float32", block_size=16, max_cache_tokens=2048, **kw)
+        return [o.output_token_ids for o in eng.generate(prompts, sps)], eng.stats()
+
+    base, st = run(max_concurrent_requests=8, max_num_batched_tokens=64, prefill_chunk=32)
+    assert all(len(t) == 24 for t in base) and st["pages_used"] == 0
+    assert len({tuple(t) for t in base}) == 5
+    other, _ = run(max_concurrent_requests=2, max_num_batched_tokens=4096)
+    assert other == base
+    third, _ = run(max_concurrent_requests=3, max_num_batched_tokens=7, prefill_chunk=5, cuda_graphs=False)
+    assert third == base
+    eng = Engine(dirs["B"], dtype="float32", block_size=16, max_cache_tokens=2048)
+    for p, sp, want in zip(prompts, sps, base):
+        assert eng.generate([p], sp)[0].output_token_ids == want
+    # the plain model, fed the engine's own tokens, gives each of them a fair probability
+    W = tiny.load_plain_weights(dirs["B"])
+    logits = plain_llama.forward(cfg, W, prompts[1] + base[1])
+    probs = torch.softmax(logits[len(prompts[1]) - 1: -1] / 0.7, dim=-1)
+    assert all(probs[i, t] > 1e-4 for i, t in enumerate(base[1]))
+
+
+def test_preemption_changes_no_token(dirs):
+    """With a pool of 12 pages three requests cannot all grow: the newest is preempted and
+    recomputed, and still every request produces what it produces alone."""
+    from fastmlx_b200 import Engine, SamplingParams
+    cfg = tiny.TINY_A
+    prompts = [tiny.rand_tokens(n, cfg["vocab_size"], 80 + n) for n in (30, 28, 25)]
+    sp = SamplingParams(max_tokens=40, temperature=0.0)
+    roomy = Engine(dirs["A"], dtype="float32", block_size=8, initial_cache_blocks=64, max_concurrent_requests=4)
+    want = [o.output_token_ids for o in roomy.generate(prompts, sp)]
+    tight = Engine(dirs["A"], dtype="float32", block_size=8, initial_cache_blocks=18, max_concurrent_requests=4)
+    outs = tight.generate(prompts, sp)
+    assert tight.stats()["preemptions"] > 0
+    assert [o.output_token_ids for o in outs] == want
+    assert tight.stats()["pages_used"] == 0
+    tight.manager.check()
+
+
+def test_errors_are_reported_per_request(dirs):
+    from fastmlx_b200 import Engine, SamplingParams
+    eng = Engine(dirs["A"], dtype="float32", block_size=16, max_cache_tokens=256)
+    outs = eng.generate([[], [1, 2, 999999], [3, 4, 5]], SamplingParams(max_tokens=2, temperature=0.0))
+    assert outs[0].finish_reason == "error" and "empty" in outs[0].err
+    assert outs[1].finish_reason == "error" and "vocabulary" in outs[1].err
+    # the bad token's step took its neighbours down with it, as a backend error does in the
+    # reference; a later request runs normally
+    ok = eng.generate([[3, 4, 5]], SamplingParams(max_tokens=2, temperature=0.0))[0]
+    assert ok.finish_reason == "length" and ok.completion_tokens == 2
+    assert eng.stats()["pages_used"] == 0
+
+
+def test_abort_and_eos(dirs):
+    from fastmlx_b200 import Engine, SamplingParams
+    cfg = tiny.TINY_A
+    W = tiny.load_plain_weights(dirs["A"])
+    prompt = tiny.rand_tokens(9, cfg["vocab_size"], 5)
+    want = plain_llama.greedy_generate(cfg, W, prompt, 6)
+    eng = Engine(dirs["A"], dtype="float32", block_size=16, max_cache_tokens=256)
+    out = eng.generate([prompt], SamplingParams(max_tokens=20, temperature=0.0, stop_token_ids=[want[3]]))[0]
+    assert out.finish_reason == "stop" and out.output_token_ids == want[:want.index(want[3]) + 1]
+    rid = eng.submit(prompt, SamplingParams(max_tokens=1000, temperature=0.0))
+    eng.step()
+    eng.abort(rid)
+    outs = []
+    while eng.has_unfinished():
+        outs += eng.step()
+    assert outs[-1].request_id == rid and outs[-1].finish_reason == "abort"
+    assert eng.stats()["pages_used"] == 0
+
+
+def test_command_line_generate(dirs, tmp_path):
+    cfg = tiny.TINY_A
+    W = tiny.load_plain_weights(dirs["A"])
+    prompt = tiny.rand_tokens(11, cfg["vocab_size"], 9)
+    want = plain_llama.greedy_generate(cfg, W, prompt, 5)
+    cmd = [sys.executable, "-m", "fastmlx_b200", "generate", "--model-dir", dirs["A"], "--dtype", "float32",
+           "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "5", "--temperature", "0",
+           "--max-cache-tokens", "256"]
+    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    out = json.loads(res.stdout.strip().splitlines()[-1])
+    assert out["output_token_ids"] == want and out["finish_reason"] == "length"
+    # a folder written by the command line's random-model runs too
+    cpath = tmp_path / "c.json"
+    cpath.write_text(json.dumps(tiny.TINY_C))
+    made = subprocess.run([sys.executable, "-m", "fastmlx_b200", "random-model", "--config", str(cpath), "--out",
+                           str(tmp_path / "m"), "--seed", "3"], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert made.returncode == 0, made.stderr[-2000:]
+    res = subprocess.run([sys.executable, "-m", "fastmlx_b200", "generate", "--model-dir", str(tmp_path / "m"),
+                          "--prompt-ids", "1,2,3;4,5", "--max-tokens", "3", "--seed", "7", "--max-cache-tokens", "256"],
+                         cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [json.loads(l) for l in res.stdout.strip().splitlines()]
+    assert len(lines) == 2 and all(l["completion_tokens"] == 3 for l in lines)

@@ -1,0 +1,319 @@
+"""Each part alone against the plain functions; a schedule that runs a layer twice and lets
+a layer read another layer's cache; and a toy mixer with state of its own, defined here,
+registered, built, loaded and stepped through the public interfaces only."""
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_llama as pl
+import tiny
+import traces
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def runtime(dtype):
+    from fastmlx_b200.engine.loading import make_runtime
+    return make_runtime(dtype)
+
+
+def rnd(*shape, seed=0, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale).to(dtype)
+
+
+def close(got, ref, dtype, scale=None):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    s = scale or ref.abs().max().item()
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    err = (got - ref).abs().max().item() / s
+    assert err < tol, err
+
+
+def step_context(manager, rows, rt):
+    """rows: [(request cache, tokens)] -> a reserved step context."""
+    from fastmlx_b200.engine.batch import StepEntry, build_context
+    entries = [StepEntry(rc, toks, []) for rc, toks in rows]
+    for e in entries:
+        manager.reserve(e.request, len(e.tokens))
+    ctx = build_context(entries, manager, rt.device, torch.zeros(4, dtype=torch.int32, device=rt.device))
+    return ctx, entries
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_linear_mlp_embedding_head_alone(dtype):
+    from fastmlx_b200.parts import Embedding, Linear, LMHead, RMSNorm, SwiGLU
+    rt = runtime(dtype)
+    rto = torch.bfloat16 if dtype == "bfloat16" else None
+    d, I, V, T = 72, 136, 50, 9
+    W = {"n.weight": 1 + rnd(d, seed=1, scale=0.1), "m.g.weight": rnd(I, d, seed=2, scale=0.1),
+         "m.u.weight": rnd(I, d, seed=3, scale=0.1), "m.dn.weight": rnd(d, I, seed=4, scale=0.1),
+         "m.g.bias": rnd(I, seed=5, scale=0.1), "m.u.bias": rnd(I, seed=6, scale=0.1), "m.dn.bias": rnd(d, seed=7, scale=0.1),
+         "e.weight": rnd(V, d, seed=8), "h.weight": rnd(V, d, seed=9, scale=0.1)}
+    x = rnd(T, d, seed=10).to(rt.dtype)
+    res = rnd(T, d, seed=11).to(rt.dtype)
+
+    norm = RMSNorm(d, 1e-4, "n")
+    norm.bind(W, rt)
+    out, r2 = norm.forward(x.to(DEV), res.clone().to(DEV))
+    h = pl._rnd(x.double() + res.double(), rto)
+    close(r2, h, dtype)
+    close(out, pl._rnd(pl.rms_norm(h, W["n.weight"], 1e-4), rto), dtype)
+
+    mlp = SwiGLU(d, I, "m", bias=True, proj_names=("g", "u", "dn"))
+    mlp.bind(W, rt)
+    close(mlp.forward(x.to(DEV), None), pl.swiglu(x, W["m.g.weight"], W["m.u.weight"], W["m.dn.weight"], W["m.g.bias"],
+                                                  W["m.u.bias"], W["m.dn.bias"], rto), dtype)
+
+    lin = Linear(d, [("m.g", I)], bias=False)
+    lin.bind(W, rt)
+    close(lin.forward(x.to(DEV)), pl.linear(x, W["m.g.weight"]), dtype)
+
+    emb = Embedding(V, d, "e")
+    emb.bind(W, rt)
+    ids = torch.tensor([3, 0, 49, 3], dtype=torch.int32, device=DEV)
+    ctx = type("C", (), {"status": torch.zeros(4, dtype=torch.int32, device=DEV)})()
+    assert torch.equal(emb.forward(ids, ctx).cpu(), W["e.weight"].to(rt.dtype)[ids.cpu().long()])
+    for head in (LMHead(V, d, "h"), LMHead(V, d, None, tied=emb)):
+        head.bind(W, rt)
+        logits = head.forward(x.to(DEV))
+        assert logits.dtype == torch.float32
+        close(logits, pl.linear(x, W["h.weight"] if head.tied is None else W["e.weight"]), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,window,trad,rot", [(4, 2, 16, 0, False, None), (6, 2, 32, 0, True, None),
+                                                       (3, 1, 64, 9, False, None), (4, 4, 48, 0, False, 24)])
+def test_attention_part_alone_with_rotary(dtype, nh, nkv, hd, window, trad, rot):
+    """One attention mixer over its own small cache, a sequence fed in three portions, with
+    a window and with a partial rotary dimension, against plain attention on the whole."""
+    from fastmlx_b200.cache import CacheManager
+    from fastmlx_b200.parts import GQAAttention, RotaryEmbedding
+    rt = runtime(dtype)
+    rto = torch.bfloat16 if dtype == "bfloat16" else None
+    d, T = 40, 37
+    mixer = GQAAttention(d, nh, nkv, hd, RotaryEmbedding(hd, 777.0, None, trad, rot), "a", window=window)
+    W = {s.name: rnd(*s.shape, seed=i, scale=0.3) for i, s in enumerate(mixer.weight_specs())}
+    mixer.bind(W, rt)
+    x = rnd(T, d, seed=99).to(rt.dtype)
+    manager = CacheManager([(mixer.cache_spec(), None, None)], page_size=8, num_pages=8, max_requests=1,
+                           dtype=rt.dtype, device=DEV)
+    rc = manager.add_request("r")
+    outs, at = [], 0
+    for n in (20, 2, 15):
+        ctx, _ = step_context(manager, [(rc, [0] * n)], rt)
+        outs.append(mixer.forward(x[at:at + n].to(DEV), ctx, manager.entries[0]))
+        assert ctx.status.tolist()[0] == 0
+        manager.commit(rc)
+        at += n
+    got = torch.cat(outs)
+    # plain: the same weights through the plain attention block, with this part's options
+    cfg = {"num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "attention_bias": False,
+           "rope_traditional": trad}
+    inv = pl.rope_inv_freq(rot or hd, 777.0, None)
+    Wp = {"self_attn." + k[2:]: v for k, v in W.items()}
+    ref = pl.attention_block(x, Wp, "", cfg, torch.arange(T), inv, rto, window or None)
+    close(got, ref, dtype)
+
+
+def test_llama3_frequency_table_matches_plain():
+    from fastmlx_b200.config import RopeScaling
+    from fastmlx_b200.parts import inverse_frequencies
+    sc = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 64}
+    got = inverse_frequencies(32, 500000.0, RopeScaling.from_dict(sc))
+    want = pl.rope_inv_freq(32, 500000.0, sc)
+    assert torch.allclose(got, want, rtol=1e-14, atol=0)
+    plain = pl.rope_inv_freq(32, 500000.0, None)
+    ratio = (got / plain)
+    assert (ratio == 1).any() and (ratio == 1 / 8).any() and ((ratio > 1 / 8) & (ratio < 1)).any()   # all three bands
+
+
+# ----------------------------------------------------------------------------- schedules
+@dataclass(frozen=True)
+class LoopCfg:
+    vocab_size: int = 90
+    width: int = 48
+    eos_token_id: int = -1
+
+    @staticmethod
+    def from_dict(d):
+        return LoopCfg(int(d.get("vocab_size", 90)), int(d.get("width", 48)))
+
+
+def build_loop(cfg):
+    """Two blocks run as 0, 1, 0: the second reads the first one's cache and has no k/v
+    projections; the first runs twice, with a cache for each run."""
+    from fastmlx_b200.parts import (Embedding, GQAAttention, LMHead, Model, PreNormBlock, RMSNorm, RotaryEmbedding,
+                                    Run, SwiGLU)
+    d = cfg.width
+    emb = Embedding(cfg.vocab_size, d, "emb")
+
+    def block(i, share):
+        return PreNormBlock(GQAAttention(d, 4, 2, 16, RotaryEmbedding(16, 10000.0), f"l{i}.attn", share_kv=share),
+                            SwiGLU(d, 64, f"l{i}.mlp"), RMSNorm(d, 1e-5, f"l{i}.n1"), RMSNorm(d, 1e-5, f"l{i}.n2"))
+    return Model(emb, [block(0, False), block(1, True)], RMSNorm(d, 1e-5, "norm"), LMHead(cfg.vocab_size, d, None, tied=emb),
+                 schedule=[Run(0), Run(1, cache_from=0), Run(0)], vocab_size=cfg.vocab_size, max_positions=256)
+
+
+def plain_loop(W, toks):
+    T = len(toks)
+    pos = torch.arange(T)
+    inv = pl.rope_inv_freq(16, 10000.0, None)
+    h = pl.embedding(torch.tensor(toks), W["emb.weight"])
+    first_kv = None
+    for run, share in ((0, False), (1, True), (0, False)):
+        p = f"l{run}."
+        x = pl.rms_norm(h, W[p + "n1.weight"], 1e-5)
+        q = pl.apply_rope(pl.linear(x, W[p + "attn.q_proj.weight"]).view(T, 4, 16), pos, inv)
+        if share:
+            k, v = first_kv
+        else:
+            k = pl.apply_rope(pl.linear(x, W[p + "attn.k_proj.weight"]).view(T, 2, 16), pos, inv)
+            v = pl.linear(x, W[p + "attn.v_proj.weight"]).view(T, 2, 16)
+            if first_kv is None:
+                first_kv = (k, v)
+        a = pl.attention(q, k, v, 16 ** -0.5).reshape(T, 64)
+        h = h + pl.linear(a, W[p + "attn.o_proj.weight"])
+        y = pl.rms_norm(h, W[p + "n2.weight"], 1e-5)
+        h = h + pl.swiglu(y, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"], W[p + "mlp.down_proj.weight"])
+    return pl.linear(pl.rms_norm(h, W["norm.weight"], 1e-5), W["emb.weight"])
+
+
+def test_schedule_runs_a_layer_twice_and_shares_a_cache(tmp_path):
+    from fastmlx_b200 import registry, write_random_model
+    from fastmlx_b200.engine.replay import Replayer
+    registry.register("toy_loop", LoopCfg.from_dict, build_loop, replace=True)
+    try:
+        d = write_random_model(str(tmp_path / "loop"), {"model_type": "toy_loop", "vocab_size": 90, "width": 48}, seed=2)
+        W = tiny.load_plain_weights(d)
+        assert "l1.attn.k_proj.weight" not in W and "l0.attn.k_proj.weight" in W
+        prompts = {f"r{i}": tiny.rand_tokens(n, 90, i) for i, n in enumerate([21, 40, 5, 33])}
+        ref = {r: plain_loop(W, t) for r, t in prompts.items()}
+        rp = Replayer(d, "float32", 256, page_size=8)
+        assert len(rp.manager.groups) == 1 and rp.manager.groups[0].entries == [0, 2]
+        for cut in (traces.whole, traces.portions, traces.mixed):
+            steps = cut(prompts)
+            rows = traces.collect(steps, [rp.step(s) for s in steps])
+            for r, t in prompts.items():
+                got = torch.tensor([rows[r][i].tolist() for i in range(len(t))], dtype=torch.float64)
+                assert (got - ref[r]).abs().max().item() / ref[r].abs().max().item() < 1e-5, (cut.__name__, r)
+            rp.manager.check()
+    finally:
+        registry.unregister("toy_loop")
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state
+def make_toy():
+    """Defined with the public interfaces only: a mixer whose per-request state is a decaying
+    sum of its projected inputs (s_t = decay * s_{t-1} + x_t P^T, y_t = s_t)."""
+    from fastmlx_b200.parts import (Embedding, GQAAttention, Linear, LMHead, Mixer, Model, PreNormBlock, RMSNorm,
+                                    RotaryEmbedding, StateSpec, SwiGLU)
+
+    class DecayingSum(Mixer):
+        def __init__(self, width, decay, name):
+            self.width, self.decay = width, decay
+            self.proj = Linear(width, [(name + ".proj", width)])
+
+        def children(self):
+            return (self.proj,)
+
+        def state_spec(self):
+            return StateSpec((self.width,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            u = self.proj.forward(x).float()
+            out = torch.empty_like(u)
+            for r in range(ctx.R):
+                a, b, slot = ctx.h_row_start[r], ctx.h_row_start[r + 1], ctx.h_row_slot[r]
+                s = cache.state[slot]
+                for t in range(a, b):
+                    s = self.decay * s + u[t]
+                    out[t] = s
+                cache.state[slot] = s
+            return out.to(x.dtype)
+
+    @dataclass(frozen=True)
+    class ToyCfg:
+        vocab_size: int
+        width: int
+        decay: float
+        eos_token_id: int = -1
+
+        @staticmethod
+        def from_dict(d):
+            return ToyCfg(int(d["vocab_size"]), int(d["width"]), float(d["decay"]))
+
+    def build(cfg):
+        d = cfg.width
+        emb = Embedding(cfg.vocab_size, d, "emb")
+        blocks = [
+            PreNormBlock(DecayingSum(d, cfg.decay, "l0.mix"), SwiGLU(d, 56, "l0.mlp"), RMSNorm(d, 1e-5, "l0.n1"),
+                         RMSNorm(d, 1e-5, "l0.n2")),
+            PreNormBlock(GQAAttention(d, 2, 1, 16, RotaryEmbedding(16, 100.0), "l1.attn"), SwiGLU(d, 56, "l1.mlp"),
+                         RMSNorm(d, 1e-5, "l1.n1"), RMSNorm(d, 1e-5, "l1.n2")),
+        ]
+        return Model(emb, blocks, RMSNorm(d, 1e-5, "norm"), LMHead(cfg.vocab_size, d, "head"),
+                     vocab_size=cfg.vocab_size, max_positions=512)
+
+    return ToyCfg, build
+
+
+def plain_toy(W, toks, decay):
+    T = len(toks)
+    pos = torch.arange(T)
+    h = pl.embedding(torch.tensor(toks), W["emb.weight"])
+    x = pl.rms_norm(h, W["l0.n1.weight"], 1e-5)
+    u = pl.linear(x, W["l0.mix.proj.weight"])
+    s = torch.zeros(u.shape[1], dtype=torch.float64)
+    y = torch.empty_like(u)
+    for t in range(T):
+        s = decay * s + u[t]
+        y[t] = s
+    h = h + y
+    h = h + pl.swiglu(pl.rms_norm(h, W["l0.n2.weight"], 1e-5), W["l0.mlp.gate_proj.weight"], W["l0.mlp.up_proj.weight"],
+                      W["l0.mlp.down_proj.weight"])
+    x = pl.rms_norm(h, W["l1.n1.weight"], 1e-5)
+    inv = pl.rope_inv_freq(16, 100.0, None)
+    q = pl.apply_rope(pl.linear(x, W["l1.attn.q_proj.weight"]).view(T, 2, 16), pos, inv)
+    k = pl.apply_rope(pl.linear(x, W["l1.attn.k_proj.weight"]).view(T, 1, 16), pos, inv)
+    v = pl.linear(x, W["l1.attn.v_proj.weight"]).view(T, 1, 16)
+    h = h + pl.linear(pl.attention(q, k, v, 0.25).reshape(T, 32), W["l1.attn.o_proj.weight"])
+    h = h + pl.swiglu(pl.rms_norm(h, W["l1.n2.weight"], 1e-5), W["l1.mlp.gate_proj.weight"], W["l1.mlp.up_proj.weight"],
+                      W["l1.mlp.down_proj.weight"])
+    return pl.linear(pl.rms_norm(h, W["norm.weight"], 1e-5), W["head.weight"])
+
+
+def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
+    from fastmlx_b200 import Engine, SamplingParams, registry, write_random_model
+    from fastmlx_b200.engine.replay import Replayer
+    ToyCfg, build = make_toy()
+    registry.register(["toy_decay", "ToyDecayForCausalLM"], ToyCfg.from_dict, build, replace=True)
+    try:
+        config = {"architectures": ["ToyDecayForCausalLM"], "vocab_size": 77, "width": 40, "decay": 0.9}
+        d = write_random_model(str(tmp_path / "toy"), config, seed=4)
+        W = tiny.load_plain_weights(d)
+        prompts = {f"r{i}": tiny.rand_tokens(n, 77, 10 + i) for i, n in enumerate([19, 34, 3, 50, 27, 41])}
+        ref = {r: plain_toy(W, t, 0.9) for r, t in prompts.items()}
+        rp = Replayer(d, "float32", 256, page_size=8)
+        assert rp.manager.entries[0].state is not None and rp.manager.entries[0].kv is None
+        assert rp.manager.entries[1].state is None and rp.manager.entries[1].kv is not None
+        for cut in (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
+            steps = cut(prompts)
+            rows = traces.collect(steps, [rp.step(s) for s in steps])
+            for r, t in prompts.items():
+                got = torch.tensor([rows[r][i].tolist() for i in range(len(t))], dtype=torch.float64)
+                assert (got - ref[r]).abs().max().item() / ref[r].abs().max().item() < 1e-5, (cut.__name__, r)
+            rp.manager.check()
+        # and it generates through the entry point, slots being reused by later requests
+        eng = Engine(d, dtype="float32", block_size=8, max_cache_tokens=512, max_concurrent_requests=2)
+        ps = [prompts["r0"], prompts["r2"], prompts["r4"]]
+        outs = eng.generate(ps, SamplingParams(max_tokens=6, temperature=0.0))
+        for p, o in zip(ps, outs):
+            seq = list(p)
+            for _ in range(6):
+                seq.append(int(torch.argmax(plain_toy(W, seq, 0.9)[-1])))
+            assert o.output_token_ids == seq[len(p):]
+    finally:
+        registry.unregister(["toy_decay", "ToyDecayForCausalLM"])

@@ -1,0 +1,146 @@
+"""Sampling filters and logits processors on the GPU against the plain statements and,
+when that checkout is present, tamnd/fastmlx's own fixtures."""
+import json
+import os
+
+import pytest
+import torch
+
+import plain_sampling as ps
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+REF = os.environ.get("FASTMLX_REFERENCE", "/root/reference")
+HAVE_REF = os.path.isdir(os.path.join(REF, "compute", "testdata"))
+
+
+def k():
+    import fastmlx_b200.kernels as kern
+    return kern
+
+
+def _mask(logits, top_p=0.0, min_p=0.0, top_k=0, min_keep=1):
+    rows = logits.shape[0]
+    f = lambda v: torch.full((rows,), float(v), device=DEV)
+    i = lambda v: torch.full((rows,), int(v), dtype=torch.int32, device=DEV)
+    return k().filter_mask(logits.to(DEV), f(top_p), f(min_p), i(top_k), i(min_keep)).cpu()
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="the reference checkout is not present")
+def test_filters_match_the_reference_fixture():
+    with open(os.path.join(REF, "compute", "testdata", "sampler_filters.json")) as f:
+        fx = json.load(f)
+    for case in fx["cases"]:
+        lp = torch.tensor([ps.log_softmax(case["logits"])], dtype=torch.float32)
+        p = case["params"]
+        if case["op"] == "apply_top_p":
+            got = _mask(lp, top_p=p["top_p"])
+        elif case["op"] == "apply_min_p":
+            got = _mask(lp, min_p=p["min_p"], min_keep=p.get("min_tokens_to_keep", 1))
+        elif case["op"] == "apply_top_k":
+            got = _mask(lp, top_k=p["top_k"])
+        else:
+            continue
+        assert got[0].bool().tolist() == case["kept"], case["label"]
+
+
+@pytest.mark.parametrize("V", [12, 131, 1000, 5000])
+@pytest.mark.parametrize("params", [dict(top_p=0.9), dict(top_p=0.3), dict(min_p=0.05), dict(min_p=0.5, min_keep=7),
+                                     dict(top_k=1), dict(top_k=40), dict(top_p=0.95, min_p=0.02, top_k=50),
+                                     dict(top_p=0.5, top_k=3, min_p=0.9, min_keep=5)])
+def test_filters_match_plain(V, params):
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(3, V, generator=g) * 3
+    logits[1, : V // 2] = logits[1, V // 2: 2 * (V // 2)]           # many equal values: ties at every threshold
+    logits[2] = torch.round(logits[2])
+    got = _mask(logits, **params)
+    for r in range(3):
+        want = ps.apply_filters(logits[r].tolist(), **params)
+        diff = [i for i in range(V) if bool(got[r, i]) != want[i]]
+        if diff and "top_p" in params:
+            # the running mass is summed in 32-bit here and in 64-bit there: a token whose
+            # mass lands within rounding of the threshold may fall on either side
+            lp = ps.log_softmax(logits[r].tolist())
+            order = sorted(range(V), key=lambda i: lp[i])
+            run, cum = 0.0, {}
+            import math
+            for i in order:
+                run += math.exp(lp[i])
+                cum[i] = run
+            assert all(abs(cum[i] - (1 - params["top_p"])) < 1e-5 for i in diff) and "top_k" not in params, (r, diff[:5])
+        else:
+            assert not diff, (r, diff[:5])
+
+
+def test_large_vocabulary_top_k_and_top_p():
+    V = 128256
+    logits = torch.randn(2, V, generator=torch.Generator().manual_seed(1)) * 2
+    got = _mask(logits, top_k=50)
+    for r in range(2):
+        assert sorted(torch.nonzero(got[r]).flatten().tolist()) == sorted(torch.topk(logits[r], 50).indices.tolist())
+    got = _mask(logits, top_p=0.9)
+    for r in range(2):
+        p = torch.softmax(logits[r].double(), 0)
+        kept = p[got[r].bool()]
+        assert kept.sum() >= 0.9 - 1e-4 and kept.sum() - kept.min() <= 0.9 + 1e-4      # the smallest set reaching top_p
+        assert p[~got[r].bool()].max() <= kept.min()
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="the reference checkout is not present")
+def test_processors_match_the_reference_fixture():
+    with open(os.path.join(REF, "compute", "testdata", "logits_processors.json")) as f:
+        cases = json.load(f)
+    from fastmlx_b200.engine.loading import make_runtime
+    from fastmlx_b200.sampling import Sampler, SamplingParams
+    sampler = Sampler(make_runtime("float32"))
+    for case in cases:
+        p = case["params"]
+        sp = SamplingParams(temperature=0.0, logit_bias={int(a): b for a, b in (p.get("logit_bias") or {}).items()},
+                            repetition_penalty=p.get("repetition_penalty", 1.0),
+                            presence_penalty=p.get("presence_penalty", 0.0),
+                            frequency_penalty=p.get("frequency_penalty", 0.0),
+                            repetition_context_size=p.get("repetition_context_size", 20),
+                            presence_context_size=p.get("presence_context_size", 20),
+                            frequency_context_size=p.get("frequency_context_size", 20))
+        logits = torch.tensor([case["logits"]], dtype=torch.float32, device=DEV)
+        tok = sampler.sample(logits, [(sp, 0, 0, case["tokens"])])
+        assert logits[0].cpu().tolist() == pytest.approx(case["expected"], abs=1e-6), case["label"]
+        assert int(tok[0]) == max(range(len(case["expected"])), key=lambda i: (case["expected"][i], -i)), case["label"]
+
+
+def test_processors_match_plain_on_random_rows():
+    from fastmlx_b200.engine.loading import make_runtime
+    from fastmlx_b200.sampling import Sampler, SamplingParams
+    sampler = Sampler(make_runtime("float32"))
+    g = torch.Generator().manual_seed(3)
+    V = 97
+    logits = torch.randn(4, V, generator=g) * 2
+    hist = [torch.randint(0, 12, (n,), generator=g).tolist() for n in (0, 5, 30, 64)]
+    sps = [SamplingParams(temperature=0.0, repetition_penalty=1.3),
+           SamplingParams(temperature=0.0, presence_penalty=0.5, frequency_penalty=0.25, frequency_context_size=3),
+           SamplingParams(temperature=0.0, repetition_penalty=0.8, presence_penalty=-0.2, frequency_penalty=0.1,
+                          repetition_context_size=7, presence_context_size=40, logit_bias={3: 2.0, 96: -1.0}),
+           SamplingParams(temperature=0.0)]
+    dev = logits.clone().to(DEV)
+    sampler.sample(dev, [(sp, 0, 0, h) for sp, h in zip(sps, hist)])
+    for r, (sp, h) in enumerate(zip(sps, hist)):
+        want = ps.apply_processors(h, logits[r].tolist(), sp.logit_bias, sp.repetition_penalty if sp.repetition_penalty != 1 else None,
+                                   sp.presence_penalty, sp.frequency_penalty, sp.repetition_context_size,
+                                   sp.presence_context_size, sp.frequency_context_size)
+        assert dev[r].cpu().tolist() == pytest.approx(want, abs=1e-6), r
+
+
+def test_draws_depend_on_the_seed_and_index_not_on_the_batch():
+    from fastmlx_b200.engine.loading import make_runtime
+    from fastmlx_b200.sampling import Sampler, SamplingParams
+    sampler = Sampler(make_runtime("float32"))
+    V = 320
+    logits = (torch.randn(5, V, generator=torch.Generator().manual_seed(4)) * 2).to(DEV)
+    sp = SamplingParams(temperature=0.7, top_p=0.9, top_k=20)
+    rows = [(sp, 11 + r, 3 * r, []) for r in range(5)]
+    together = sampler.sample(logits.clone(), rows).tolist()
+    alone = [int(sampler.sample(logits[r:r + 1].clone(), [rows[r]])[0]) for r in range(5)]
+    reordered = sampler.sample(logits.flip(0).contiguous(), rows[::-1]).tolist()[::-1]
+    assert together == alone == reordered
+    mixed = sampler.sample(logits.clone(), [(SamplingParams(temperature=0.0), 0, 0, [])] + rows[1:]).tolist()
+    assert mixed[0] == int(torch.argmax(logits[0])) and mixed[1:] == together[1:]
