@@ -1,0 +1,522 @@
+// Paged grouped-query attention in bfloat16 on the tensor cores, for one head size
+// (compile with -DFMX_HD=<head size>, a multiple of 16 up to 256).
+//
+// Two kernels over the same paged cache [page, 2 (k|v), nkv, page_size, hd]:
+//
+//  * prefill: a block owns 64 "packed" query rows of one request and one kv head.  Packed
+//    row i stands for (token i / rep, query head g*rep + i % rep), rep = nh / nkv, so all
+//    rows of a block read the same keys and values; each has its own causal limit.  Keys
+//    and values stream through shared memory in tiles of 64 keys (cp.async, three stages);
+//    scores, running maximum and sum, and the output accumulator are 32-bit (flash-style
+//    online softmax).  It takes any mix of rows: portions of prompts and single tokens.
+//
+//  * decode: every row brings one token.  A block owns (a split of the keys, a kv head, a
+//    row); its four warps take 16 keys each of every 64-key tile for the same <=16 query
+//    heads, merge at the end and write either the output or an unnormalised partial
+//    (maximum, sum, accumulator) that a second kernel combines.  Nothing waits on another
+//    block: there is no spin and nothing to hang.
+//
+// Keys out of sight (beyond a row's position, before its window, or in no page) are
+// zero-filled in shared memory and masked, never read from the cache.
+#include <math.h>
+#include "common.cuh"
+
+#ifndef FMX_HD
+#error "compile with -DFMX_HD=<head size>"
+#endif
+
+namespace {
+constexpr int HD = FMX_HD;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16, at most 256");
+constexpr int KSTEPS = HD / 16;          // k-steps of Q.K^T
+constexpr int NT_O = HD / 8;             // 8-wide column tiles of the output
+constexpr int BN = 64;                   // keys per tile
+constexpr int BM = 64;                   // packed query rows per prefill block
+constexpr int ROW = HD + 8;              // padded shared-memory row (elements): conflict-free ldmatrix
+constexpr int CHUNKS = HD / 8;           // 16-byte chunks per row
+constexpr int TILE = BN * ROW;           // elements of one K (or V) tile
+constexpr int THREADS = 128;
+constexpr int PREFILL_STAGES = HD <= 128 ? 3 : 2;
+constexpr int DECODE_STAGES = HD <= 128 ? 4 : 2;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct Cache {
+  const bf16* kv;
+  const int* bt;          // this row's block table
+  int bt_len;
+  int nkv, page_size;
+  long long num_pages;
+};
+
+// Bring keys [k0, k0 + BN) of kv head g (plane 0 = keys, 1 = values) into a shared tile;
+// keys outside [kbeg, kend) or without a page become zeros.
+__device__ __forceinline__ void load_tile(bf16* dst, const Cache& c, int g, int plane, int k0, int kbeg, int kend,
+                                          int* status, int where) {
+  for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += THREADS) {
+    const int r = idx / CHUNKS, ch = idx - r * CHUNKS;
+    const int key = k0 + r;
+    bool valid = key >= kbeg && key < kend;
+    const bf16* src = c.kv;
+    if (valid) {
+      const int blk = key / c.page_size;
+      const int page = blk < c.bt_len ? c.bt[blk] : -1;
+      if (page < 0 || page >= c.num_pages) {
+        fmx_set_status(status, FMX_BAD_PAGE, page, where);
+        valid = false;
+      } else {
+        src = c.kv + ((((long long)page * 2 + plane) * c.nkv + g) * c.page_size + (key - blk * c.page_size)) * HD + ch * 8;
+      }
+    }
+    cp_async16(dst + r * ROW + ch * 8, src, valid);
+  }
+}
+
+// S[16 x 8*NT] += Q[16 x HD] . K^T for the key rows [key_row0, key_row0 + 8*NT) of a shared tile.
+template <int NT>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const unsigned (&q)[KSTEPS][4], const bf16* ks, int key_row0) {
+  const int lane = threadIdx.x & 31;
+  const int mi = lane >> 3, ri = lane & 7;
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+#pragma unroll
+    for (int jp = 0; jp < NT / 2; ++jp) {
+      unsigned b0, b1, b2, b3;
+      // matrices: (keys 16jp.., hd 16k), (same keys, hd 16k+8), (keys 16jp+8.., hd 16k), (.., hd 16k+8)
+      const bf16* p = ks + (key_row0 + 16 * jp + (mi >> 1) * 8 + ri) * ROW + 16 * k + (mi & 1) * 8;
+      ldmatrix_x4(b0, b1, b2, b3, p);
+      mma_bf16(s[2 * jp], q[k], b0, b1);
+      mma_bf16(s[2 * jp + 1], q[k], b2, b3);
+    }
+  }
+}
+
+// O[16 x HD] += P[16 x 16*KT] . V for the key rows [key_row0, ...) of a shared tile; P comes
+// as the score fragments of 2*KT column tiles.
+template <int KT>
+__device__ __forceinline__ void pv_tile(float (&o)[NT_O][4], const float (&p)[2 * KT][4], const bf16* vs, int key_row0) {
+  const int lane = threadIdx.x & 31;
+  const int mi = lane >> 3, ri = lane & 7;
+#pragma unroll
+  for (int kk = 0; kk < KT; ++kk) {
+    unsigned a[4];
+    a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+    a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+    a[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+    a[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+#pragma unroll
+    for (int np = 0; np < NT_O / 2; ++np) {
+      unsigned b0, b1, b2, b3;
+      // matrices: (keys 16kk.., hd 16np), (keys 16kk+8.., hd 16np), (keys 16kk.., hd 16np+8), (keys 16kk+8.., hd 16np+8)
+      const bf16* ptr = vs + (key_row0 + 16 * kk + (mi & 1) * 8 + ri) * ROW + 16 * np + (mi >> 1) * 8;
+      ldmatrix_x4_trans(b0, b1, b2, b3, ptr);
+      mma_bf16(o[2 * np], a, b0, b1);
+      mma_bf16(o[2 * np + 1], a, b2, b3);
+    }
+  }
+}
+
+// Mask, then one step of the online softmax over NT column tiles for the two rows (g, g+8)
+// a thread holds.  Scores arrive raw; sl2 = scale * log2(e).  m is kept in the scaled
+// log2 domain.  `lim[x]`, `lo[x]`: last and first visible key of row x.
+template <int NT>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&alpha)[2], float sl2,
+                                             int key0, const int (&lim)[2], const int (&lo)[2]) {
+  const int t = threadIdx.x & 3;
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int x = e >> 1;
+      const int key = key0 + 8 * j + 2 * t + (e & 1);
+      const float v = (key <= lim[x] && key >= lo[x]) ? s[j][e] * sl2 : -INFINITY;
+      s[j][e] = v;
+      mx[x] = fmaxf(mx[x], v);
+    }
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 1));
+    mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 2));
+    const float m_new = fmaxf(m[x], mx[x]);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    alpha[x] = exp2f(m[x] - m_use);
+    m[x] = m_new;
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const float p0 = exp2f(s[j][2 * x] - m_use), p1 = exp2f(s[j][2 * x + 1] - m_use);
+      s[j][2 * x] = p0;
+      s[j][2 * x + 1] = p1;
+      sum += p0 + p1;
+    }
+    l[x] = l[x] * alpha[x] + sum;          // this thread's share; the quad is summed at the end
+  }
+}
+
+// ------------------------------------------------------------------------------------ prefill
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kv,
+                    const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ row_start,
+                    const int* __restrict__ row_ctx, bf16* __restrict__ out, int nh, int nkv, int page_size,
+                    long long num_pages, float scale, int window, int* status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+  const int r = blockIdx.z, g = blockIdx.y, tile = blockIdx.x;
+  const int rep = nh / nkv;
+  const int t0 = row_start[r], q_len = row_start[r + 1] - t0, ctx = row_ctx[r];
+  const int n_packed = q_len * rep;
+  const int prow0 = tile * BM;
+  if (prow0 >= n_packed || ctx < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages};
+
+  // the two packed rows of this thread
+  int prow[2], tok[2], head[2], lim[2], lo[2];
+  bool rvalid[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    prow[x] = prow0 + warp * 16 + gq + 8 * x;
+    rvalid[x] = prow[x] < n_packed;
+    const int pr = rvalid[x] ? prow[x] : n_packed - 1;
+    tok[x] = pr / rep;
+    head[x] = g * rep + pr - tok[x] * rep;
+    lim[x] = rvalid[x] ? ctx + tok[x] : -1;
+    lo[x] = window > 0 ? max(0, ctx + tok[x] - window + 1) : 0;
+  }
+  // query fragments, straight from global memory
+  unsigned qf[KSTEPS][4];
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k)
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const bf16* qp = q + (long long)(t0 + tok[x]) * q_stride + (long long)head[x] * HD + 16 * k + 2 * tq;
+      qf[k][x] = rvalid[x] ? *reinterpret_cast<const unsigned*>(qp) : 0u;
+      qf[k][x + 2] = rvalid[x] ? *reinterpret_cast<const unsigned*>(qp + 8) : 0u;
+    }
+
+  // keys this block needs: from the first row's window start to the last row's position
+  const int first_tok = prow0 / rep;
+  const int last_tok = (min(prow0 + BM, n_packed) - 1) / rep;
+  const int kbeg = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
+  const int kend = ctx + last_tok + 1;
+  const int n_tiles = (kend - kbeg + BN - 1) / BN;
+  const float sl2 = scale * LOG2E;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[NT_O][4];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+
+  auto stage_k = [&](int s) { return smem + (size_t)s * 2 * TILE; };
+  auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
+#pragma unroll
+  for (int s = 0; s < PREFILL_STAGES - 1; ++s) {
+    if (s < n_tiles) {
+      load_tile(stage_k(s), c, g, 0, kbeg + s * BN, kbeg, kend, status, r);
+      load_tile(stage_v(s), c, g, 1, kbeg + s * BN, kbeg, kend, status, r);
+    }
+    cp_async_commit();
+  }
+  for (int it = 0; it < n_tiles; ++it) {
+    cp_async_wait<PREFILL_STAGES - 2>();
+    __syncthreads();
+    const int nx = it + PREFILL_STAGES - 1;
+    if (nx < n_tiles) {
+      load_tile(stage_k(nx % PREFILL_STAGES), c, g, 0, kbeg + nx * BN, kbeg, kend, status, r);
+      load_tile(stage_v(nx % PREFILL_STAGES), c, g, 1, kbeg + nx * BN, kbeg, kend, status, r);
+    }
+    cp_async_commit();
+    const bf16* ks = stage_k(it % PREFILL_STAGES);
+    const bf16* vs = stage_v(it % PREFILL_STAGES);
+    float s[BN / 8][4];
+#pragma unroll
+    for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+    qk_tile<BN / 8>(s, qf, ks, 0);
+    float alpha[2];
+    softmax_step<BN / 8>(s, m, l, alpha, sl2, kbeg + it * BN, lim, lo);
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+      o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+    pv_tile<BN / 16>(o, s, vs, 0);
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
+    l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
+    if (!rvalid[x]) continue;
+    const float inv = l[x] > 0.f ? 1.0f / l[x] : 0.f;
+    bf16* op = out + ((long long)(t0 + tok[x]) * nh + head[x]) * HD + 2 * tq;
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n)
+      *reinterpret_cast<unsigned*>(op + 8 * n) = pack_bf16(o[n][2 * x] * inv, o[n][2 * x + 1] * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------ decode
+// part_o: [R, nkv, splits, 16, HD] float; part_ml: [R, nkv, splits, 16, 2] float (max in the
+// scaled log2 domain, sum).  With one split the output is written directly.
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kv,
+                   const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ row_start,
+                   const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, int nh, int nkv, int page_size, long long num_pages, float scale,
+                   int window, int* status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+  const int split = blockIdx.x, splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
+  const int rep = nh / nkv;
+  const int t = row_start[r];
+  const int pos = positions[t];                      // -1 for a padding row: no keys at all
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages};
+
+  const int lo_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int n_keys = max(0, pos + 1 - lo_key);
+  int per = (n_keys + splits - 1) / splits;
+  per = (per + BN - 1) / BN * BN;
+  const int kbeg = lo_key + split * per;
+  const int kend = min(pos + 1, kbeg + per);
+  const int n_tiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
+
+  unsigned qf[KSTEPS][4];
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k)
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const int hrow = gq + 8 * x;
+      const bool ok = hrow < rep;
+      const bf16* qp = q + (long long)t * q_stride + (long long)(g * rep + (ok ? hrow : 0)) * HD + 16 * k + 2 * tq;
+      qf[k][x] = ok ? *reinterpret_cast<const unsigned*>(qp) : 0u;
+      qf[k][x + 2] = ok ? *reinterpret_cast<const unsigned*>(qp + 8) : 0u;
+    }
+  const int lim[2] = {kend - 1, kend - 1};
+  const int lo[2] = {kbeg, kbeg};
+  const float sl2 = scale * LOG2E;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[NT_O][4];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+
+  auto stage_k = [&](int s) { return smem + (size_t)s * 2 * TILE; };
+  auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
+#pragma unroll
+  for (int s = 0; s < DECODE_STAGES - 1; ++s) {
+    if (s < n_tiles) {
+      load_tile(stage_k(s), c, g, 0, kbeg + s * BN, kbeg, kend, status, r);
+      load_tile(stage_v(s), c, g, 1, kbeg + s * BN, kbeg, kend, status, r);
+    }
+    cp_async_commit();
+  }
+  for (int it = 0; it < n_tiles; ++it) {
+    cp_async_wait<DECODE_STAGES - 2>();
+    __syncthreads();
+    const int nx = it + DECODE_STAGES - 1;
+    if (nx < n_tiles) {
+      load_tile(stage_k(nx % DECODE_STAGES), c, g, 0, kbeg + nx * BN, kbeg, kend, status, r);
+      load_tile(stage_v(nx % DECODE_STAGES), c, g, 1, kbeg + nx * BN, kbeg, kend, status, r);
+    }
+    cp_async_commit();
+    const bf16* ks = stage_k(it % DECODE_STAGES);
+    const bf16* vs = stage_v(it % DECODE_STAGES);
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+    qk_tile<2>(s, qf, ks, warp * 16);
+    float alpha[2];
+    softmax_step<2>(s, m, l, alpha, sl2, kbeg + it * BN + warp * 16, lim, lo);
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+      o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+    pv_tile<1>(o, s, vs, warp * 16);
+  }
+  cp_async_wait<0>();
+  __syncthreads();                                   // the tiles are done with; reuse the memory
+
+  // merge the four warps: each leaves (m, l, o) of its 16 rows
+  float* mo = reinterpret_cast<float*>(smem_raw);    // [4][16][HD]
+  float* mml = mo + 4 * 16 * HD;                     // [4][16][2]
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
+    l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
+    const int row = gq + 8 * x;
+    float* dst = mo + ((size_t)warp * 16 + row) * HD + 2 * tq;
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+      dst[8 * n] = o[n][2 * x];
+      dst[8 * n + 1] = o[n][2 * x + 1];
+    }
+    if (tq == 0) {
+      mml[(warp * 16 + row) * 2] = m[x];
+      mml[(warp * 16 + row) * 2 + 1] = l[x];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rep * HD; idx += THREADS) {
+    const int row = idx / HD, d = idx - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + row) * 2]);
+    const float Mu = M == -INFINITY ? 0.f : M;
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(mml[(w * 16 + row) * 2] - Mu);
+      L += f * mml[(w * 16 + row) * 2 + 1];
+      acc += f * mo[((size_t)w * 16 + row) * HD + d];
+    }
+    if (splits == 1) {
+      out[((long long)t * nh + g * rep + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const long long pi = (((long long)r * nkv + g) * splits + split) * 16 + row;
+      part_o[pi * HD + d] = acc;
+      if (d == 0) {
+        part_ml[pi * 2] = M;
+        part_ml[pi * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const int* __restrict__ row_start, bf16* __restrict__ out, int nh, int nkv,
+                                    int splits) {
+  const int h = blockIdx.x, r = blockIdx.y;
+  const int rep = nh / nkv, g = h / rep, row = h - g * rep;
+  const int t = row_start[r];
+  const long long base = (((long long)r * nkv + g) * splits) * 16 + row;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + (long long)s * 16) * 2]);
+  const float Mu = M == -INFINITY ? 0.f : M;
+  float L = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const long long pi = base + (long long)s * 16;
+    L += exp2f(part_ml[pi * 2] - Mu) * part_ml[pi * 2 + 1];
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const long long pi = base + (long long)s * 16;
+      acc += exp2f(part_ml[pi * 2] - Mu) * part_o[pi * HD + d];
+    }
+    out[((long long)t * nh + h) * HD + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+constexpr size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * TILE * sizeof(bf16); }
+constexpr size_t decode_smem() {
+  const size_t pipe = (size_t)DECODE_STAGES * 2 * TILE * sizeof(bf16);
+  const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+  return pipe > merge ? pipe : merge;
+}
+}  // namespace
+
+FMX_EXPORT int fmx_attn_head_dim() { return HD; }
+
+// Floats of scratch the decode entry needs for (rows, nkv, splits): partial outputs, then
+// their maxima and sums.
+FMX_EXPORT long long fmx_attn_decode_scratch_floats(int rows, int nkv, int splits) {
+  return splits <= 1 ? 0 : (long long)rows * nkv * splits * 16 * (HD + 2);
+}
+
+FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* kv, const int* block_tables,
+                                int bt_stride, const int* row_start, const int* row_ctx, void* out, int rows,
+                                int max_q_len, int nh, int nkv, int page_size, long long num_pages, float scale,
+                                int window, int* status, cudaStream_t stream) {
+  if (rows == 0 || max_q_len == 0) return 0;
+  if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0)
+    return fmx_fail("fmx_attn_prefill: bad sizes rows=%d nh=%d nkv=%d page=%d", rows, nh, nkv, page_size);
+  if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_prefill: too many rows or kv heads for one launch");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)prefill_smem());
+    if (e != cudaSuccess) return fmx_fail("fmx_attn_prefill: shared memory of %zu bytes refused: %s", prefill_smem(),
+                                          cudaGetErrorString(e));
+    configured = true;
+  }
+  const int rep = nh / nkv;
+  dim3 grid(((long long)max_q_len * rep + BM - 1) / BM, nkv, rows);
+  attn_prefill_kernel<<<grid, THREADS, prefill_smem(), stream>>>(
+      (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv,
+      page_size, num_pages, scale, window, status);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
+FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv, const int* block_tables,
+                               int bt_stride, const int* row_start, const int* positions, void* out, float* scratch,
+                               long long scratch_floats, int rows, int splits, int nh, int nkv, int page_size,
+                               long long num_pages, float scale, int window, int* status, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || splits <= 0)
+    return fmx_fail("fmx_attn_decode: bad sizes rows=%d nh=%d nkv=%d page=%d splits=%d", rows, nh, nkv, page_size, splits);
+  if (nh / nkv > 16) return fmx_fail("fmx_attn_decode: %d query heads per kv head is above 16", nh / nkv);
+  if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_decode: too many rows or kv heads for one launch");
+  const long long need = fmx_attn_decode_scratch_floats(rows, nkv, splits);
+  if (need > 0 && (scratch == nullptr || scratch_floats < need))
+    return fmx_fail("fmx_attn_decode: scratch of %lld floats given, %lld needed", scratch_floats, need);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)decode_smem());
+    if (e != cudaSuccess) return fmx_fail("fmx_attn_decode: shared memory of %zu bytes refused: %s", decode_smem(),
+                                          cudaGetErrorString(e));
+    configured = true;
+  }
+  float* part_o = scratch;
+  float* part_ml = scratch ? scratch + (long long)rows * nkv * splits * 16 * HD : nullptr;
+  dim3 grid(splits, nkv, rows);
+  attn_decode_kernel<<<grid, THREADS, decode_smem(), stream>>>(
+      (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
+      part_ml, nh, nkv, page_size, num_pages, scale, window, status);
+  FMX_LAUNCH_CHECK();
+  if (splits > 1) {
+    attn_combine_kernel<<<dim3(nh, rows), HD < 128 ? 64 : 128, 0, stream>>>(part_o, part_ml, row_start, (bf16*)out, nh,
+                                                                           nkv, splits);
+    FMX_LAUNCH_CHECK();
+  }
+  return 0;
+}

@@ -20,10 +20,25 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 GROUPS = {
-    # name: (directory, extra include dirs)
+    # name: directory of its sources.  A name like "attn_hd64" is the group "attn" compiled
+    # with -DFMX_HD=64: one library per head size, built when a model of that size is met.
     "common": "common",
     "bf16": "bf16",
+    "attn": "attn",
 }
+HEAD_DIMS = tuple(range(16, 257, 16))
+
+
+def _split(group: str) -> tuple[str, list[str]]:
+    """'attn_hd64' -> ('attn', ['-DFMX_HD=64']); other names stand for themselves."""
+    if group.startswith("attn_hd"):
+        hd = int(group[len("attn_hd"):])
+        if hd not in HEAD_DIMS:
+            raise BuildError(f"the tiled attention kernels take head sizes in steps of 16 up to 256, not {hd}")
+        return "attn", [f"-DFMX_HD={hd}"]
+    if group not in GROUPS:
+        raise BuildError(f"unknown kernel group {group!r}")
+    return group, []
 
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -45,17 +60,22 @@ def find_nvcc() -> str:
 
 
 def sources(group: str) -> list[str]:
-    d = os.path.join(HERE, GROUPS[group])
-    return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(".cu"))
+    d = os.path.join(HERE, GROUPS[_split(group)[0]])
+    if not os.path.isdir(d):
+        return []
+    srcs = sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(".cu"))
+    if srcs and _split(group)[0] != "common":
+        srcs.append(os.path.join(HERE, "common", "error.cu"))     # every library carries its own error text
+    return srcs
 
 
 def _digest(group: str) -> str:
-    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    h = hashlib.sha256(" ".join(NVCC_FLAGS + _split(group)[1]).replace(HERE, ".").encode())
     files = sources(group)
     for d in {os.path.dirname(f) for f in files} | {os.path.join(HERE, "common")}:
         files += [os.path.join(d, f) for f in os.listdir(d) if f.endswith((".cuh", ".h"))]
     for f in sorted(set(files)):
-        h.update(f.encode())
+        h.update(os.path.relpath(f, HERE).encode())        # the same tree elsewhere needs no rebuild
         with open(f, "rb") as fh:
             h.update(fh.read())
     return h.hexdigest()[:16]
@@ -124,7 +144,8 @@ def build(group: str, force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(src):
         obj = os.path.join(bdir, f"{group}_{os.path.basename(src)[:-3]}.o")
-        _run_with_heartbeat([nvcc, *NVCC_FLAGS, *extra, "-c", src, "-o", obj], os.path.basename(src))
+        _run_with_heartbeat([nvcc, *NVCC_FLAGS, *_split(group)[1], *extra, "-c", src, "-o", obj],
+                            os.path.basename(src))
         return obj
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs), os.cpu_count() or 1)) as ex:
@@ -139,8 +160,11 @@ def build(group: str, force: bool = False, verbose: bool = False) -> str:
     return lib
 
 
-def build_all(force: bool = False, verbose: bool = False) -> list[str]:
-    return [build(g, force, verbose) for g in GROUPS if sources(g)]
+def build_all(force: bool = False, verbose: bool = False, head_dims=HEAD_DIMS) -> list[str]:
+    """Every library: the plain groups and the attention kernels of every head size."""
+    groups = [g for g in GROUPS if g != "attn" and sources(g)] + [f"attn_hd{hd}" for hd in head_dims]
+    with ThreadPoolExecutor(max_workers=max(1, (os.cpu_count() or 2) // 2)) as ex:
+        return list(ex.map(lambda g: build(g, force, verbose), groups))
 
 
 if __name__ == "__main__":

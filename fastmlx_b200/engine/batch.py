@@ -53,10 +53,41 @@ class StepContext:
     scratch: dict = field(default_factory=dict)
 
 
+class StaticBuffers:
+    """The fixed device buffer of a captured decode graph (the same layout every step, so the
+    graph's kernels always read the same addresses) and a small ring of pinned host buffers
+    that feed it.  The host may run several steps ahead of the device: a host buffer is
+    written again only after the copy that last read it has finished."""
+
+    def __init__(self, ints: int, device, ring: int = 4):
+        self.dev = torch.zeros(ints, dtype=torch.int32, device=device)
+        self.hosts = [torch.zeros(ints, dtype=torch.int32).pin_memory() for _ in range(ring)]
+        self.events = [None] * ring
+        self.at = 0
+
+    def next_host(self) -> torch.Tensor:
+        self.at = (self.at + 1) % len(self.hosts)
+        ev = self.events[self.at]
+        if ev is not None:
+            ev.synchronize()
+        return self.hosts[self.at]
+
+    def upload(self) -> torch.Tensor:
+        self.dev.copy_(self.hosts[self.at], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[self.at] = ev
+        return self.dev
+
+
 def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_blocks: int = 0,
-                  pinned: bool = True) -> StepContext:
+                  pad_want: bool = False, static: StaticBuffers | None = None, pinned: bool = True) -> StepContext:
     """Lay the entries out as one flat batch.  Pages for the new tokens must have been
-    reserved already.  One host buffer carries every integer array to the device."""
+    reserved already.  One host buffer carries every integer array to the device.
+
+    `pad_rows` / `pad_blocks` / `pad_want` fix the sizes (rows, block-table width, one
+    wanted place per row) for a captured graph: padding rows bring one token at position
+    -1 that is stored nowhere and sees no key."""
     R = len(entries)
     q_lens = [len(e.tokens) for e in entries]
     T = sum(q_lens)
@@ -75,6 +106,10 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
                 raise ValueError(f"wanted place {w} lies outside the {q} tokens of the entry")
             want.append(off + w)
         off += q
+    if pad_want:
+        if any(q != 1 for q in q_lens):
+            raise ValueError("a padded batch holds one token per row")
+        want = list(range(Tp))
 
     # layout of the packed int32 buffer
     sizes = {"tokens": Tp, "positions": Tp, "token_row": Tp, "row_start": Rp + 1, "row_ctx": Rp,
@@ -87,7 +122,13 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
         total = (total + 3) // 4 * 4   # 16-byte alignment of every array
         offs[k] = total
         total += n
-    host = np.zeros(total, dtype=np.int32)
+    if static is not None:
+        if static.dev.numel() != total:
+            raise ValueError("the static buffers were made for another layout")
+        host = static.next_host().numpy()
+        host[:] = 0
+    else:
+        host = np.zeros(total, dtype=np.int32)
 
     def view(k):
         return host[offs[k]: offs[k] + sizes[k]]
@@ -103,6 +144,7 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
         off += q
     for r in range(R, Rp):             # padding rows: one token, no context, stored nowhere
         trow[off] = r
+        pos[off] = -1
         rstart[r], rctx[r], rslot[r] = off, 0, 0
         off += 1
     rstart[Rp] = off
@@ -120,13 +162,16 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
             sm[off: off + q] = np.asarray(pages, dtype=np.int64)[p // ps] * ps + p % ps
             off += q
 
-    t = torch.from_numpy(host)
-    if device is not None and torch.device(device).type == "cuda":
-        if pinned:
-            t = t.pin_memory()
-        dev = t.to(device, non_blocking=True)
+    if static is not None:
+        dev = static.upload()
     else:
-        dev = t
+        t = torch.from_numpy(host)
+        if device is not None and torch.device(device).type == "cuda":
+            if pinned:
+                t = t.pin_memory()
+            dev = t.to(device, non_blocking=True)
+        else:
+            dev = t
 
     def dview(k):
         return dev[offs[k]: offs[k] + sizes[k]]
@@ -141,4 +186,4 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
         logit_rows=dview("want"), status=status, groups=groups, caches=manager.entries,
         h_row_start=rstart.tolist(), h_row_ctx=rctx.tolist(), h_row_slot=rslot.tolist(),
         max_q_len=max(q_lens + [1]), max_ctx_after=max([c + q for c, q in zip(ctxs, q_lens)] + [1]),
-        all_decode=all(q == 1 for q in q_lens), scratch={"h2d_bytes": host.nbytes})
+        all_decode=all(q == 1 for q in q_lens), scratch={"h2d_bytes": host.nbytes, "layout_ints": total})

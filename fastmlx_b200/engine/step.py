@@ -6,14 +6,18 @@ offsets, whole left-padded prompts, or one sequence at a time: compute/batch_gen
 178-195) and never a portion of a prompt beside a decoded token.  Here a step is one flat
 ragged batch over a paged cache: any mix, cut anywhere.  An error leaves no state
 advanced, as there (batch_generator.go:187-191).
+
+Steps in which every request brings exactly one token are launch-bound, so they run as
+CUDA graphs: one graph per (rows rounded up to a power of two, block-table width rounded
+up to a power of two), captured at first use, fed through fixed buffers.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
-from ..cache.pages import OutOfPages
-from .batch import StepContext, StepEntry, build_context
+from .batch import StaticBuffers, StepContext, StepEntry, build_context
 
 
 class StepError(RuntimeError):
@@ -25,22 +29,82 @@ _STATUS_TEXT = {1: "a token id outside the vocabulary", 2: "a cache slot outside
                 3: "a block-table entry that holds no page", 4: "a row index outside the batch"}
 
 
+def _pow2_at_least(n: int, floor: int = 1) -> int:
+    p = floor
+    while p < n:
+        p *= 2
+    return p
+
+
+class _DecodeGraph:
+    """One captured decode step for `rows` rows and block tables `width` pages wide."""
+
+    def __init__(self, fn: "StepFunction", rows: int, width: int, entries):
+        self.rows, self.width = rows, width
+        rt, manager = fn.rt, fn.manager
+        probe = build_context(entries, manager, None, fn.status, pad_rows=rows, pad_blocks=width, pad_want=True)
+        n = probe.scratch["layout_ints"]
+        self.static = StaticBuffers(n, rt.device)
+        ctx = self._context(fn, entries)
+        # warm up outside the capture (library handles, lazily built kernels), then capture
+        side = torch.cuda.Stream(device=rt.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn.model.forward(ctx)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        count = getattr(rt.k, "launch_count", lambda: 0)
+        before = count()
+        with torch.cuda.graph(self.graph):
+            self.logits = fn.model.forward(ctx)
+        self.kernel_launches = count() - before        # launches of this package's kernels per replay
+        self.ctx = ctx
+
+    def _context(self, fn, entries) -> StepContext:
+        ctx = build_context(entries, fn.manager, fn.rt.device, fn.status, pad_rows=self.rows, pad_blocks=self.width,
+                            pad_want=True, static=self.static)
+        ctx.max_ctx_after = self.width * fn.manager.page_size      # fixed, so that the split count is
+        ctx.max_q_len = 1
+        return ctx
+
+    def run(self, fn, entries) -> tuple[torch.Tensor, StepContext]:
+        ctx = self._context(fn, entries)
+        self.graph.replay()
+        return self.logits, ctx
+
+
 class StepFunction:
-    def __init__(self, model, manager: CacheManager, rt, cuda_graphs: bool = False):
+    def __init__(self, model, manager: CacheManager, rt, cuda_graphs: bool = False, max_graph_rows: int = 256):
         self.model, self.manager, self.rt = model, manager, rt
-        self.cuda_graphs = bool(cuda_graphs) and rt.device.type == "cuda"
+        self.cuda_graphs = bool(cuda_graphs) and rt.device.type == "cuda" and bool(getattr(model, "graph_safe", False))
+        self.max_graph_rows = max_graph_rows
+        self.graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self.graph_replays = 0
+        self.graph_kernel_launches = 0
         self.last_h2d_bytes = 0
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=rt.device)
         self.steps = 0
         self.tokens_run = 0
         self.last_ctx: StepContext | None = None
+        if self.cuda_graphs:
+            # the split decode attention's workspace must not grow once a graph holds its address
+            k = rt.k
+            need = 0
+            for g in manager.groups:
+                rows = 1
+                while rows <= max_graph_rows:
+                    s = k.decode_splits(rows, g.spec.num_kv_heads, 1 << 30)
+                    need = max(need, k.attn_decode_scratch_floats(rows, g.spec.num_kv_heads, s, g.spec.head_dim))
+                    rows *= 2
+            k.attention_scratch(rt.device, need)
 
     def run(self, entries: list[StepEntry], reserved: bool = False, check: bool = True) -> torch.Tensor:
         """-> float32 logits [sum(len(e.want)), vocab] on the device, in the order of the
         entries and of their `want`.  `reserved`: the caller (the scheduler) has taken the
         pages already and commits or rolls back itself.  `check=False` leaves the read of
-        the kernels' status word to the caller, who reads results from the device anyway."""
+        the kernels' status word to the caller, who reads results from the device anyway.
+        The tensor may be a view of a graph's output: use it before the next step."""
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -59,8 +123,7 @@ class StepFunction:
                 for e in entries:
                     self.manager.reserve(e.request, len(e.tokens))
                     taken.append(e.request)
-            ctx = build_context(entries, self.manager, self.rt.device, self.status)
-            logits = self.model.forward(ctx)
+            logits, ctx = self._forward(entries)
             if check:
                 self.check_status()
         except BaseException:
@@ -74,6 +137,29 @@ class StepFunction:
         self.tokens_run += ctx.T
         self.last_ctx = ctx
         return logits
+
+    def _forward(self, entries):
+        if self.cuda_graphs and len(entries) <= self.max_graph_rows and all(len(e.tokens) == 1 for e in entries):
+            ps = self.manager.page_size
+            rows = _pow2_at_least(len(entries))
+            blocks = max(-(-(e.request.length + 1) // ps) for e in entries)
+            width = _pow2_at_least(blocks, 16)
+            key = (rows, width)
+            g = self.graphs.get(key)
+            if g is None:
+                g = self.graphs[key] = _DecodeGraph(self, rows, width, entries)
+            logits, ctx = g.run(self, entries)
+            self.graph_replays += 1
+            self.graph_kernel_launches += g.kernel_launches
+            # one wanted place per row in the graph; give back what was asked for
+            picks = [i for i, e in enumerate(entries) if e.want]
+            if len(picks) == len(entries):
+                return logits[:len(entries)], ctx
+            if not picks:
+                return logits[:0], ctx
+            return logits[torch.as_tensor(picks, device=logits.device)], ctx
+        ctx = build_context(entries, self.manager, self.rt.device, self.status)
+        return self.model.forward(ctx), ctx
 
     def check_status(self) -> None:
         """Kernels never trap on a bad index: they skip the access and leave a code."""

@@ -10,7 +10,13 @@ from __future__ import annotations
 
 import torch
 
+from . import lib as _lib
 from .lib import KernelError, call, load, loaded_libraries
+
+
+def launch_count() -> int:
+    """Calls into the package's CUDA libraries so far (a graph replay is counted by its owner)."""
+    return _lib.launches
 
 F32, BF16 = 0, 1
 BAD_TOKEN, BAD_SLOT, BAD_PAGE, BAD_ROW = 1, 2, 3, 4
@@ -127,11 +133,72 @@ def paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> t
     return out
 
 
+NUM_SMS = 148
+MAX_SPLITS = 32
+_scratch: dict = {}
+
+
+def attention_scratch(device, floats: int) -> torch.Tensor:
+    """The workspace of the split decode attention (partial outputs, maxima and sums), one
+    per device, grown on demand.  A CUDA graph must not grow it: size it before capture."""
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < floats:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the attention workspace must be sized before a CUDA graph is captured")
+        buf = torch.empty(max(floats, 1), dtype=torch.float32, device=device)
+        _scratch[device] = buf
+    return buf
+
+
+def decode_splits(rows: int, nkv: int, max_ctx: int) -> int:
+    """Enough blocks to fill the GPU about twice over, at least 256 keys to a split."""
+    want = max(1, (2 * NUM_SMS) // max(1, rows * nkv))
+    return max(1, min(MAX_SPLITS, want, -(-max_ctx // 256)))
+
+
+def attn_decode_scratch_floats(rows: int, nkv: int, splits: int, hd: int) -> int:
+    return 0 if splits <= 1 else rows * nkv * splits * 16 * (hd + 2)
+
+
+def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, splits=None) -> torch.Tensor:
+    """Every row brings one token: split over the keys, all query heads of a kv head together."""
+    T = qkv.shape[0]
+    R = ctx.R
+    out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    if splits is None:
+        splits = getattr(ctx, "n_splits", 0) or decode_splits(R, nkv, max(1, ctx.max_ctx_after))
+    need = attn_decode_scratch_floats(R, nkv, splits, hd)
+    scratch = attention_scratch(qkv.device, need) if need else None
+    bt = group.block_tables
+    call(f"attn_hd{hd}", "fmx_attn_decode", qkv.data_ptr(), qkv.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
+         ctx.row_start.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), _ptr(scratch),
+         scratch.numel() if scratch is not None else 0, R, splits, nh, nkv, kv.shape[3], kv.shape[0], float(scale),
+         int(window), _ptr(ctx.status), _stream())
+    return out
+
+
+def paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Tensor:
+    """Any mix of rows, tiled over 64 packed query rows and 64 keys."""
+    T = qkv.shape[0]
+    out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    bt = group.block_tables
+    call(f"attn_hd{hd}", "fmx_attn_prefill", qkv.data_ptr(), qkv.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
+         ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), out.data_ptr(), ctx.R, int(ctx.max_q_len), nh, nkv,
+         kv.shape[3], kv.shape[0], float(scale), int(window), _ptr(ctx.status), _stream())
+    return out
+
+
 def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Tensor:
     """Attention of every token of the step over the pages of its own request.
-    qkv[T, >= nh*hd] holds the (rotated) queries first; -> [T, nh*hd]."""
+    qkv[T, >= nh*hd] holds the (rotated) queries first; -> [T, nh*hd].  bfloat16 with a head
+    size in steps of 16 (at most 256) runs on the tensor cores; everything else, and all
+    of the 32-bit path, on the one-warp-per-query kernel."""
     _need_cuda(qkv, kv)
     assert kv.is_contiguous() and kv.dtype == qkv.dtype and qkv.stride(1) == 1
+    if qkv.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0:
+        if ctx.all_decode and nh // nkv <= 16:
+            return paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
+        return paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
     return paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
 
 

@@ -32,9 +32,14 @@ _SIGNATURES = {
         "fmx_logit_bias": [_P, _L, _I, _P, _P, _P, _I, _P],
     },
     "bf16": {},
+    "attn": {
+        "fmx_attn_prefill": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
+        "fmx_attn_decode": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
+    },
 }
 
 _libs: dict[str, ctypes.CDLL] = {}
+launches = 0          # entry-point calls so far; each launches at least one kernel of this package
 
 
 def load(group: str) -> ctypes.CDLL:
@@ -46,8 +51,11 @@ def load(group: str) -> ctypes.CDLL:
         lib = ctypes.CDLL(path)
     except (OSError, _build.BuildError) as e:
         raise KernelError(f"the CUDA library of group {group!r} is not available: {e}") from None
+    if group.startswith("attn_hd"):
+        lib.fmx_attn_decode_scratch_floats.argtypes = [_I, _I, _I]
+        lib.fmx_attn_decode_scratch_floats.restype = c_longlong
     lib.fmx_last_error.restype = ctypes.c_char_p
-    for name, args in _SIGNATURES[group].items():
+    for name, args in _SIGNATURES["attn" if group.startswith("attn_hd") else group].items():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = c_int
@@ -56,6 +64,8 @@ def load(group: str) -> ctypes.CDLL:
 
 
 def call(group: str, name: str, *args) -> None:
+    global launches
+    launches += 1
     lib = load(group)
     rc = getattr(lib, name)(*args)
     if rc != 0:

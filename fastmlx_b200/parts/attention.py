@@ -18,6 +18,8 @@ class GQAAttention(Mixer):
     schedule entry it is pointed at.
     """
 
+    supports_cuda_graph = True
+
     def __init__(self, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  pos: PositionEncoding, name: str, bias: bool = False, scale: float | None = None,
                  window: int = 0, share_kv: bool = False,

@@ -104,6 +104,10 @@ def to_f32_vector(t: torch.Tensor, rt: Runtime) -> torch.Tensor:
 class Mixer(Part):
     """Token mixer of a block (attention here).  forward(x[T, d], ctx, cache) -> [T, d_out]."""
 
+    # A mixer whose forward only launches kernels that read the step's device arrays may be
+    # captured in a CUDA graph; one that loops over rows on the host may not.
+    supports_cuda_graph = False
+
     def cache_spec(self) -> PagedKVSpec | None:
         return None
 

@@ -21,6 +21,11 @@ class PreNormBlock(Part):
     def state_spec(self):
         return self.mixer.state_spec()
 
+    @property
+    def supports_cuda_graph(self):
+        return bool(getattr(self.mixer, "supports_cuda_graph", False)) and \
+            bool(getattr(self.ffn, "supports_cuda_graph", True))
+
     def forward(self, delta, residual, ctx, cache):
         x, residual = self.norm1.forward(delta, residual)
         a = self.mixer.forward(x, ctx, cache)

@@ -49,6 +49,11 @@ class Model(Part):
             out.append((kv, layer.state_spec(), run.cache_from))
         return out
 
+    @property
+    def graph_safe(self) -> bool:
+        """May a decode step of this model be captured in a CUDA graph?"""
+        return all(getattr(layer, "supports_cuda_graph", False) for layer in self.layers)
+
     # ---- weights
     def check_weights(self, tensors: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
         """One error that lists every missing tensor, every unexpected one and every wrong

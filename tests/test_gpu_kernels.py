@@ -22,7 +22,7 @@ def status():
     return torch.zeros(4, dtype=torch.int32, device=DEV)
 
 
-def close(got, ref, dtype, what="", scale=None):
+def close(got, ref, dtype, what="", scale=None, extra=0.0):
     """32-bit: a few units of float32 rounding of the result's scale.  bfloat16: the same
     value may round to the neighbouring bfloat16 (one unit in the last place = 2^-7
     relative at worst) when 32-bit and 64-bit arithmetic land on different sides."""
@@ -33,8 +33,8 @@ def close(got, ref, dtype, what="", scale=None):
         tol = 2e-6 * s
         bad = (got - ref).abs() > tol + 2e-6 * ref.abs()
     else:
-        bad = (got - ref).abs() > 2.0 ** -7 * ref.abs() + 1e-3 * s
-    assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} off, worst {(got - ref).abs().max().item():.3e} (scale {s:.3e})"
+        bad = (got - ref).abs() > 2.0 ** -7 * ref.abs() + 1e-3 * s + extra
+    assert not bad.any(), f"{what} (extra {extra:.2e}): {int(bad.sum())} of {bad.numel()} off, worst {(got - ref).abs().max().item():.3e} (scale {s:.3e})"
 
 
 def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
@@ -279,6 +279,112 @@ def test_paged_attention_never_reads_unseen_keys():
     ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, 0)
     assert torch.isfinite(got).all()
     close(got, ref, torch.float32, "attention", scale=1.0)
+
+
+def _full_ctx(rows, ctx, grp):
+    """A device step context with the row arrays the tiled kernels read."""
+    starts, at = [], 0
+    for _, ql in rows:
+        starts.append(at)
+        at += ql
+    starts.append(at)
+    d, g = _to_dev(ctx, grp)
+    d.row_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    d.row_ctx = torch.tensor([c for c, _ in rows], dtype=torch.int32, device=DEV)
+    d.max_q_len = max(ql for _, ql in rows)
+    d.max_ctx_after = max(c + ql for c, ql in rows)
+    d.all_decode = all(ql == 1 for _, ql in rows)
+    d.R = len(rows)
+    d.n_splits = 0
+    return d, g
+
+
+# The tiled kernels hand the probabilities to the tensor cores in bfloat16: each p_j carries a
+# relative error of 2^-9, so sum_j p_j v_j is off by at most 2^-9 * max|v| on top of the
+# rounding of the result itself.
+P_ROUNDING = 2.0 ** -9
+
+TILED_SHAPES = [(4, 2, 16, 16), (6, 3, 32, 16), (5, 1, 48, 8), (8, 8, 64, 32), (32, 8, 64, 16), (12, 4, 128, 64),
+                (24, 8, 128, 16), (3, 3, 80, 16), (2, 1, 256, 16), (16, 1, 96, 128)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES)
+@pytest.mark.parametrize("window", [0, 24, 100])
+def test_tiled_prefill_attention_mixed_rows(nh, nkv, hd, page_size, window):
+    """Portions of prompts with and without earlier context, single tokens, tiles that end in
+    the middle of a portion, rows that span several 64-row and 64-key tiles."""
+    rows = [(0, 37), (90, 1), (31, 2), (0, 1), (15, 17), (64, 1), (200, 130), (0, 64), (63, 65)]
+    q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, window)
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, window)
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    got = k().paged_attention_prefill(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, window)
+    assert dctx.status.tolist()[0] == 0
+    close(got, ref, torch.bfloat16, "tiled prefill attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES)
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+def test_split_decode_attention(nh, nkv, hd, page_size, window, splits):
+    rows = [(0, 1), (1, 1), (63, 1), (64, 1), (65, 1), (300, 1), (1000, 1), (127, 1)]
+    q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, window)
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, window)
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    got = k().paged_attention_decode(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, window, splits=splits)
+    assert dctx.status.tolist()[0] == 0
+    close(got, ref, torch.bfloat16, "split decode attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
+
+
+def test_decode_padding_rows_read_nothing():
+    """A padding row (position -1, block table of -1) gives zeros and no status code."""
+    nh, nkv, hd, page_size = 8, 2, 64, 16
+    rows = [(100, 1), (0, 1)]
+    q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows)
+    ctx.positions[1] = -1
+    grp.block_tables[1] = -1
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    got = k().paged_attention_decode(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, 0, splits=3)
+    assert dctx.status.tolist()[0] == 0 and float(got[1].abs().sum()) == 0.0 and torch.isfinite(got).all()
+
+
+@pytest.mark.parametrize("kernel", ["prefill", "decode"])
+@pytest.mark.parametrize("key_pos", [0, 15, 16, 63, 64, 65, 127, 128, 511, 512, 700])
+def test_tiled_attention_far_key_stands_out(kernel, key_pos):
+    """One key among 701 dominates for one head: a tile edge, a page edge or a split edge
+    that loses it shows at once."""
+    nh, nkv, hd, page_size = 8, 2, 64, 16
+    rows = [(700, 1), (0, 5)] if kernel == "prefill" else [(700, 1), (4, 1)]
+    q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, spike=(0, key_pos, 5))
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, 1.0, 0)
+    assert (ref[0, 5 * hd:6 * hd].float() - 7.0).abs().max() < 0.1
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    if kernel == "prefill":
+        got = k().paged_attention_prefill(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, 1.0, 0)
+    else:
+        got = k().paged_attention_decode(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, 1.0, 0, splits=4)
+    close(got, ref, torch.bfloat16, "dominant key", scale=7.0)
+
+
+@pytest.mark.parametrize("kernel", ["prefill", "decode"])
+def test_tiled_attention_window_edge_and_unseen_keys(kernel):
+    """The key just outside the window must not count, the one just inside must; and pages
+    hold NaN wherever a key is out of sight."""
+    nh, nkv, hd, page_size, window = 4, 1, 64, 16, 40
+    for key_pos, inside in ((100 - 40, False), (100 - 39, True)):
+        rows = [(100, 1), (7, 1)]
+        q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, window, spike=(0, key_pos, 1))
+        ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, 1.0, window)
+        assert ((ref[0, hd:2 * hd].float() - 7.0).abs().max() < 0.1) == inside
+        poisoned = torch.full_like(kv, float("nan"))
+        for r, (c, ql) in enumerate(rows):
+            for j in range(max(0, c - window + 1), c + ql):
+                p = int(grp.block_tables[r, j // page_size])
+                poisoned[p, :, :, j % page_size] = kv[p, :, :, j % page_size]
+        dctx, dgrp = _full_ctx(rows, ctx, grp)
+        fn = k().paged_attention_prefill if kernel == "prefill" else k().paged_attention_decode
+        got = fn(q.to(DEV), poisoned.to(DEV), dctx, dgrp, nh, nkv, hd, 1.0, window)
+        assert torch.isfinite(got).all()
+        close(got, ref, torch.bfloat16, "window edge", scale=7.0)
 
 
 # ----------------------------------------------------------------------------- sampling
