@@ -37,7 +37,7 @@ constexpr int CHUNKS = HD / 8;           // 16-byte chunks per row
 constexpr int TILE = BN * ROW;           // elements of one K (or V) tile
 constexpr int THREADS = 128;
 constexpr int PREFILL_STAGES = HD <= 128 ? 3 : 2;
-constexpr int DECODE_STAGES = HD <= 128 ? 4 : 2;
+constexpr int DECODE_STAGES = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -74,12 +74,50 @@ struct Cache {
   int bt_len;
   int nkv, page_size;
   long long num_pages;
+  int page_shift;         // log2(page_size) when it is a power of two >= 4, else -1
 };
 
-// Bring keys [k0, k0 + BN) of kv head g (plane 0 = keys, 1 = values) into a shared tile;
-// keys outside [kbeg, kend) or without a page become zeros.
-__device__ __forceinline__ void load_tile(bf16* dst, const Cache& c, int g, int plane, int k0, int kbeg, int kend,
-                                          int* status, int where) {
+__device__ __forceinline__ int page_shift_of(int page_size) {
+  return (page_size >= 4 && (page_size & (page_size - 1)) == 0) ? 31 - __clz(page_size) : -1;
+}
+
+// Bring keys [k0, k0 + BN) of kv head g into a shared K tile and a shared V tile; keys
+// outside [kbeg, kend) or without a page become zeros.  k0 is a multiple of 4.  When the
+// page size is a power of two (>= 4), four consecutive keys share a page: one block-table
+// read serves eight 16-byte copies.
+__device__ __forceinline__ void load_tiles(bf16* kdst, bf16* vdst, const Cache& c, int g, int k0, int kbeg, int kend,
+                                           int* status, int where) {
+  const long long plane = (long long)c.nkv * c.page_size * HD;          // k plane -> v plane
+  const long long page_stride = 2 * plane;
+  const bf16* base = c.kv + (long long)g * c.page_size * HD;
+  if (c.page_shift >= 0) {
+    for (int item = threadIdx.x; item < (BN / 4) * CHUNKS; item += THREADS) {
+      const int rg = item / CHUNKS, ch = item - rg * CHUNKS;
+      const int key0 = k0 + 4 * rg;
+      const bool any = key0 + 3 >= kbeg && key0 < kend;
+      const bf16* src = c.kv;
+      bool have = false;
+      if (any) {
+        const int blk = key0 >> c.page_shift;
+        const int page = blk < c.bt_len ? c.bt[blk] : -1;
+        if (page < 0 || page >= c.num_pages) {
+          fmx_set_status(status, FMX_BAD_PAGE, page, where);
+        } else {
+          have = true;
+          src = base + page * page_stride + (long long)(key0 & (c.page_size - 1)) * HD + ch * 8;
+        }
+      }
+      bf16* kd = kdst + (4 * rg) * ROW + ch * 8;
+      bf16* vd = vdst + (4 * rg) * ROW + ch * 8;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool valid = have && key0 + i >= kbeg && key0 + i < kend;
+        cp_async16(kd + i * ROW, valid ? src + i * HD : c.kv, valid);
+        cp_async16(vd + i * ROW, valid ? src + i * HD + plane : c.kv, valid);
+      }
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += THREADS) {
     const int r = idx / CHUNKS, ch = idx - r * CHUNKS;
     const int key = k0 + r;
@@ -92,10 +130,11 @@ __device__ __forceinline__ void load_tile(bf16* dst, const Cache& c, int g, int 
         fmx_set_status(status, FMX_BAD_PAGE, page, where);
         valid = false;
       } else {
-        src = c.kv + ((((long long)page * 2 + plane) * c.nkv + g) * c.page_size + (key - blk * c.page_size)) * HD + ch * 8;
+        src = base + page * page_stride + (long long)(key - blk * c.page_size) * HD + ch * 8;
       }
     }
-    cp_async16(dst + r * ROW + ch * 8, src, valid);
+    cp_async16(kdst + r * ROW + ch * 8, src, valid);
+    cp_async16(vdst + r * ROW + ch * 8, valid ? src + plane : c.kv, valid);
   }
 }
 
@@ -146,7 +185,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[NT_O][4], const float (&p)[2 
 // Mask, then one step of the online softmax over NT column tiles for the two rows (g, g+8)
 // a thread holds.  Scores arrive raw; sl2 = scale * log2(e).  m is kept in the scaled
 // log2 domain.  `lim[x]`, `lo[x]`: last and first visible key of row x.
-template <int NT>
+template <int NT, bool MASK>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&alpha)[2], float sl2,
                                              int key0, const int (&lim)[2], const int (&lo)[2]) {
   const int t = threadIdx.x & 3;
@@ -157,7 +196,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
     for (int e = 0; e < 4; ++e) {
       const int x = e >> 1;
       const int key = key0 + 8 * j + 2 * t + (e & 1);
-      const float v = (key <= lim[x] && key >= lo[x]) ? s[j][e] * sl2 : -INFINITY;
+      const float v = (!MASK || (key <= lim[x] && key >= lo[x])) ? s[j][e] * sl2 : -INFINITY;
       s[j][e] = v;
       mx[x] = fmaxf(mx[x], v);
     }
@@ -196,7 +235,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
   const int prow0 = tile * BM;
   if (prow0 >= n_packed || ctx < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages};
+  const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
+                page_shift_of(page_size)};
 
   // the two packed rows of this thread
   int prow[2], tok[2], head[2], lim[2], lo[2];
@@ -227,8 +267,15 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
   const int last_tok = (min(prow0 + BM, n_packed) - 1) / rep;
   const int kbeg = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
   const int kend = ctx + last_tok + 1;
-  const int n_tiles = (kend - kbeg + BN - 1) / BN;
+  const int kstart = kbeg & ~3;                       // tiles start on a multiple of 4 keys
+  const int n_tiles = (kend - kstart + BN - 1) / BN;
   const float sl2 = scale * LOG2E;
+  // what every row of this warp sees for sure: keys from the last row's window start up to
+  // the first row's position; tiles inside that span need no mask
+  const int wfirst = min(prow0 + warp * 16, n_packed - 1) / rep, wlast = min(prow0 + warp * 16 + 15, n_packed - 1) / rep;
+  const bool warp_full = prow0 + warp * 16 + 15 < n_packed;
+  const int sure_lo = window > 0 ? max(0, ctx + wlast - window + 1) : 0;
+  const int sure_hi = ctx + wfirst;
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[NT_O][4];
@@ -241,20 +288,15 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
   auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
 #pragma unroll
   for (int s = 0; s < PREFILL_STAGES - 1; ++s) {
-    if (s < n_tiles) {
-      load_tile(stage_k(s), c, g, 0, kbeg + s * BN, kbeg, kend, status, r);
-      load_tile(stage_v(s), c, g, 1, kbeg + s * BN, kbeg, kend, status, r);
-    }
+    if (s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
     cp_async_commit();
   }
   for (int it = 0; it < n_tiles; ++it) {
     cp_async_wait<PREFILL_STAGES - 2>();
     __syncthreads();
     const int nx = it + PREFILL_STAGES - 1;
-    if (nx < n_tiles) {
-      load_tile(stage_k(nx % PREFILL_STAGES), c, g, 0, kbeg + nx * BN, kbeg, kend, status, r);
-      load_tile(stage_v(nx % PREFILL_STAGES), c, g, 1, kbeg + nx * BN, kbeg, kend, status, r);
-    }
+    if (nx < n_tiles)
+      load_tiles(stage_k(nx % PREFILL_STAGES), stage_v(nx % PREFILL_STAGES), c, g, kstart + nx * BN, kbeg, kend, status, r);
     cp_async_commit();
     const bf16* ks = stage_k(it % PREFILL_STAGES);
     const bf16* vs = stage_v(it % PREFILL_STAGES);
@@ -265,7 +307,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
     qk_tile<BN / 8>(s, qf, ks, 0);
     float alpha[2];
-    softmax_step<BN / 8>(s, m, l, alpha, sl2, kbeg + it * BN, lim, lo);
+    const int tk0 = kstart + it * BN;
+    if (warp_full && tk0 >= sure_lo && tk0 + BN - 1 <= sure_hi)
+      softmax_step<BN / 8, false>(s, m, l, alpha, sl2, tk0, lim, lo);
+    else
+      softmax_step<BN / 8, true>(s, m, l, alpha, sl2, tk0, lim, lo);
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) {
       o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
@@ -303,7 +349,8 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
   const int t = row_start[r];
   const int pos = positions[t];                      // -1 for a padding row: no keys at all
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages};
+  const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
+                page_shift_of(page_size)};
 
   const int lo_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int n_keys = max(0, pos + 1 - lo_key);
@@ -311,7 +358,8 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
   per = (per + BN - 1) / BN * BN;
   const int kbeg = lo_key + split * per;
   const int kend = min(pos + 1, kbeg + per);
-  const int n_tiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
+  const int kstart = kbeg & ~3;
+  const int n_tiles = kend > kbeg ? (kend - kstart + BN - 1) / BN : 0;
 
   unsigned qf[KSTEPS][4];
 #pragma unroll
@@ -338,20 +386,15 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
   auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
 #pragma unroll
   for (int s = 0; s < DECODE_STAGES - 1; ++s) {
-    if (s < n_tiles) {
-      load_tile(stage_k(s), c, g, 0, kbeg + s * BN, kbeg, kend, status, r);
-      load_tile(stage_v(s), c, g, 1, kbeg + s * BN, kbeg, kend, status, r);
-    }
+    if (s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
     cp_async_commit();
   }
   for (int it = 0; it < n_tiles; ++it) {
     cp_async_wait<DECODE_STAGES - 2>();
     __syncthreads();
     const int nx = it + DECODE_STAGES - 1;
-    if (nx < n_tiles) {
-      load_tile(stage_k(nx % DECODE_STAGES), c, g, 0, kbeg + nx * BN, kbeg, kend, status, r);
-      load_tile(stage_v(nx % DECODE_STAGES), c, g, 1, kbeg + nx * BN, kbeg, kend, status, r);
-    }
+    if (nx < n_tiles)
+      load_tiles(stage_k(nx % DECODE_STAGES), stage_v(nx % DECODE_STAGES), c, g, kstart + nx * BN, kbeg, kend, status, r);
     cp_async_commit();
     const bf16* ks = stage_k(it % DECODE_STAGES);
     const bf16* vs = stage_v(it % DECODE_STAGES);
@@ -362,7 +405,11 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
     qk_tile<2>(s, qf, ks, warp * 16);
     float alpha[2];
-    softmax_step<2>(s, m, l, alpha, sl2, kbeg + it * BN + warp * 16, lim, lo);
+    const int wk0 = kstart + it * BN + warp * 16;
+    if (wk0 >= kbeg && wk0 + 15 < kend)
+      softmax_step<2, false>(s, m, l, alpha, sl2, wk0, lim, lo);
+    else
+      softmax_step<2, true>(s, m, l, alpha, sl2, wk0, lim, lo);
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) {
       o[n][0] *= alpha[0]; o[n][1] *= alpha[0];

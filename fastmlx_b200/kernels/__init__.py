@@ -134,7 +134,7 @@ def paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> t
 
 
 NUM_SMS = 148
-MAX_SPLITS = 32
+MAX_SPLITS = 64
 _scratch: dict = {}
 
 
@@ -151,9 +151,9 @@ def attention_scratch(device, floats: int) -> torch.Tensor:
 
 
 def decode_splits(rows: int, nkv: int, max_ctx: int) -> int:
-    """Enough blocks to fill the GPU about twice over, at least 256 keys to a split."""
-    want = max(1, (2 * NUM_SMS) // max(1, rows * nkv))
-    return max(1, min(MAX_SPLITS, want, -(-max_ctx // 256)))
+    """Enough blocks to fill the GPU about four times over, at least 128 keys to a split."""
+    want = max(1, (4 * NUM_SMS) // max(1, rows * nkv))
+    return max(1, min(MAX_SPLITS, want, -(-max_ctx // 128)))
 
 
 def attn_decode_scratch_floats(rows: int, nkv: int, splits: int, hd: int) -> int:
