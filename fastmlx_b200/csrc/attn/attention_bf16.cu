@@ -567,3 +567,75 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
   }
   return 0;
 }
+
+// ------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate: the workspace is a fixed
+// array of this module.  See attention_noalloc.h for the contract.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[FMX_ATTN_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// In host code the array's name stands for the symbol, not for a device address: a kernel
+// must be given what cudaGetSymbolAddress returns for the current device.
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+
+int noalloc_setup(float** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fmx_fail("fmx_attn_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fmx_fail("fmx_attn_decode_noalloc: device %d is out of range", dev);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fmx_fail("fmx_attn_decode_noalloc: cudaGetSymbolAddress on device %d: %s", dev, cudaGetErrorString(e));
+    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem());
+    if (e != cudaSuccess)
+      return fmx_fail("fmx_attn_decode_noalloc: shared memory of %zu bytes refused: %s", decode_smem(),
+                      cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  *ptr = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+FMX_EXPORT long long fmx_attn_decode_noalloc_floats(int rows, int nkv, int splits) {
+  return splits <= 1 ? 0 : (long long)rows * nkv * splits * 16 * (HD + 2);
+}
+
+FMX_EXPORT long long fmx_attn_decode_noalloc_max_floats(void) { return FMX_ATTN_NOALLOC_MAX_FLOATS; }
+
+FMX_EXPORT int fmx_attn_decode_noalloc(const void* q, long long q_stride, const void* kv, const int* block_tables,
+                                       int bt_stride, const int* row_start, const int* positions, void* out, int rows,
+                                       int splits, int nh, int nkv, int page_size, long long num_pages, float scale,
+                                       int window, int* status, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || splits <= 0)
+    return fmx_fail("fmx_attn_decode_noalloc: bad sizes rows=%d nh=%d nkv=%d page=%d splits=%d", rows, nh, nkv,
+                    page_size, splits);
+  if (nh / nkv > 16) return fmx_fail("fmx_attn_decode_noalloc: %d query heads per kv head is above 16", nh / nkv);
+  if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_decode_noalloc: too many rows or kv heads for one launch");
+  const long long need = fmx_attn_decode_noalloc_floats(rows, nkv, splits);
+  if (need > FMX_ATTN_NOALLOC_MAX_FLOATS)
+    return fmx_fail("fmx_attn_decode_noalloc: rows=%d nkv=%d splits=%d head_dim=%d need %lld floats of workspace, the "
+                    "built-in array holds %d; use fewer splits or fmx_attn_decode with a workspace of your own",
+                    rows, nkv, splits, HD, need, FMX_ATTN_NOALLOC_MAX_FLOATS);
+  float* scratch = nullptr;
+  if (noalloc_setup(&scratch) != 0) return 1;
+  float* part_o = scratch;
+  float* part_ml = scratch + (long long)rows * nkv * splits * 16 * HD;
+  dim3 grid(splits, nkv, rows);
+  attn_decode_kernel<<<grid, THREADS, decode_smem(), stream>>>(
+      (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
+      part_ml, nh, nkv, page_size, num_pages, scale, window, status);
+  FMX_LAUNCH_CHECK();
+  if (splits > 1) {
+    attn_combine_kernel<<<dim3(nh, rows), HD < 128 ? 64 : 128, 0, stream>>>(part_o, part_ml, row_start, (bf16*)out, nh,
+                                                                           nkv, splits);
+    FMX_LAUNCH_CHECK();
+  }
+  return 0;
+}
