@@ -52,6 +52,69 @@ __global__ void rope_kv_write_kernel(T* qkv, const int* __restrict__ positions, 
   }
 }
 
+// bfloat16, half-split pairing, rot/2 and hd multiples of 8, 16-byte aligned rows: sine and
+// cosine once per (token, pair) in shared memory, eight pairs per thread with 16-byte
+// accesses, and the rotated k (and v) written to the page in the same pass.
+__global__ void __launch_bounds__(128)
+rope_kv_write_bf16_vec_kernel(bf16* qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                              const long long* __restrict__ slot_mapping, bf16* kv, int nh, int nkv, int hd, int rot,
+                              int page_size, long long num_pages, long long row_stride, int* status) {
+  extern __shared__ float sc[];                 // [half] sines, [half] cosines
+  const int t = blockIdx.x;
+  bf16* row = qkv + (long long)t * row_stride;
+  const int half = rot / 2;
+  const float pos = (float)positions[t];
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sc[j], &sc[half + j]);
+  long long slot = (kv != nullptr && slot_mapping != nullptr && nkv > 0) ? slot_mapping[t] : -1;
+  if (slot >= num_pages * page_size) {
+    if (threadIdx.x == 0) fmx_set_status(status, FMX_BAD_SLOT, slot, t);
+    slot = -1;
+  }
+  const long long page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? (int)(slot - page * page_size) : 0;
+  __syncthreads();
+  const int hv = half / 8;                      // vector items per head for the rotated part
+  const int pv = (hd - rot) / 8;                // and for the part that is not rotated
+  const int per_head = hv + pv;
+  const int items = (nh + nkv) * per_head + nkv * (hd / 8);
+  for (int it = threadIdx.x; it < items; it += blockDim.x) {
+    if (it < (nh + nkv) * per_head) {
+      const int h = it / per_head, c = it - h * per_head;
+      bf16* p = row + (long long)h * hd;
+      bf16* dst = nullptr;
+      if (h >= nh && slot >= 0) dst = kv + ((((page * 2 + 0) * nkv + (h - nh)) * page_size + off) * (long long)hd);
+      if (c < hv) {
+        uint4 a = *reinterpret_cast<uint4*>(p + 8 * c), b = *reinterpret_cast<uint4*>(p + half + 8 * c);
+        __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&a);
+        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
+          const int j = 8 * c + 2 * e;
+          const float s0 = sc[j], c0 = sc[half + j], s1 = sc[j + 1], c1 = sc[half + j + 1];
+          a2[e] = __floats2bfloat162_rn(fa.x * c0 - fb.x * s0, fa.y * c1 - fb.y * s1);
+          b2[e] = __floats2bfloat162_rn(fb.x * c0 + fa.x * s0, fb.y * c1 + fa.y * s1);
+        }
+        *reinterpret_cast<uint4*>(p + 8 * c) = a;
+        *reinterpret_cast<uint4*>(p + half + 8 * c) = b;
+        if (dst) {
+          *reinterpret_cast<uint4*>(dst + 8 * c) = a;
+          *reinterpret_cast<uint4*>(dst + half + 8 * c) = b;
+        }
+      } else if (dst) {
+        const int e0 = rot + 8 * (c - hv);
+        *reinterpret_cast<uint4*>(dst + e0) = *reinterpret_cast<const uint4*>(p + e0);
+      }
+    } else if (slot >= 0) {
+      const int iv = it - (nh + nkv) * per_head;
+      const int g = iv / (hd / 8), c = iv - g * (hd / 8);
+      const bf16* src = row + (long long)(nh + nkv + g) * hd + 8 * c;
+      bf16* dst = kv + ((((page * 2 + 1) * nkv + g) * page_size + off) * (long long)hd) + 8 * c;
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    }
+  }
+}
+
 FMX_EXPORT int fmx_rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const long long* slot_mapping,
                                  void* kv, int T, int nh, int nkv, int hd, int rot, int interleaved, int page_size,
                                  long long num_pages, long long row_stride, int dtype, int* status,
@@ -66,10 +129,18 @@ FMX_EXPORT int fmx_rope_kv_write(void* qkv, const int* positions, const float* i
     rope_kv_write_kernel<float><<<T, block, 0, stream>>>((float*)qkv, positions, inv_freq, slot_mapping, (float*)kv, nh,
                                                         nkv, hd, rot, interleaved, page_size, num_pages, row_stride,
                                                         status);
-  else if (dtype == FMX_BF16)
-    rope_kv_write_kernel<bf16><<<T, block, 0, stream>>>((bf16*)qkv, positions, inv_freq, slot_mapping, (bf16*)kv, nh,
-                                                       nkv, hd, rot, interleaved, page_size, num_pages, row_stride,
-                                                       status);
+  else if (dtype == FMX_BF16) {
+    const bool vec = !interleaved && rot > 0 && rot % 16 == 0 && hd % 8 == 0 && row_stride % 8 == 0 &&
+                     ((uintptr_t)qkv & 15) == 0 && (kv == nullptr || ((uintptr_t)kv & 15) == 0);
+    if (vec)
+      rope_kv_write_bf16_vec_kernel<<<T, block, (size_t)rot * sizeof(float), stream>>>(
+          (bf16*)qkv, positions, inv_freq, slot_mapping, (bf16*)kv, nh, nkv, hd, rot, page_size, num_pages, row_stride,
+          status);
+    else
+      rope_kv_write_kernel<bf16><<<T, block, 0, stream>>>((bf16*)qkv, positions, inv_freq, slot_mapping, (bf16*)kv, nh,
+                                                         nkv, hd, rot, interleaved, page_size, num_pages, row_stride,
+                                                         status);
+  }
   else
     return fmx_fail("fmx_rope_kv_write: unknown dtype %d", dtype);
   FMX_LAUNCH_CHECK();
