@@ -72,12 +72,13 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML from a thread while a region is
-    timed (reading only; nothing is set).  Spawning nvidia-smi for this slowed the timed
-    steps several times over; the library call does not."""
+    """Samples SM clocks and throttle reasons through NVML from a thread, five times a second,
+    while a region is timed (reading only; nothing is set).  Each query stalls kernel launches
+    for a moment (spawning nvidia-smi, or polling every 20 ms, slowed the timed steps by a
+    third), so the default run times enough steps for the region to last about a second."""
     REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, period: float = 0.02):
+    def __init__(self, period: float = 0.2):
         self.period, self.samples, self.max_mhz = period, [], None
         self._stop, self._thread, self._h = None, None, None
         try:
@@ -245,7 +246,7 @@ def prefill_once(engine, tokens: int, vocab: int, repeats: int = 3) -> float:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration's 16")
@@ -306,7 +307,7 @@ def main() -> int:
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            pt = decode_point(b, min(steps, 32), False, None)
+            pt = decode_point(b, min(steps, 64), False, None)
             points[f"decode_b{b}"] = round(b / (pt["ms"] / 1e3), 1)
 
     ms = main_pt["ms"]

@@ -15,6 +15,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..parts.base import PagedKVSpec, StateSpec
@@ -94,6 +95,9 @@ class CacheManager:
                 self.entries.append(EntryCache(None, -1, False, st))
         self._free_slots = list(range(self.max_requests - 1, -1, -1))
         self.requests: dict[object, RequestCache] = {}
+        # block tables by slot, as the step's batch builder wants them: one array per group,
+        # -1 where there is no page; widened on demand
+        self.table_mirror = [np.full((self.max_requests, 16), -1, dtype=np.int32) for _ in self.groups]
 
     # ------------------------------------------------------------------ sizes
     def bytes_per_token(self) -> int:
@@ -148,15 +152,19 @@ class CacheManager:
             for g, pages in zip(self.groups, taken):
                 g.pool.give(pages)
             raise
-        for bt, pages in zip(req.tables, taken):
-            bt.pages.extend(pages)
+        for gi, (bt, pages) in enumerate(zip(req.tables, taken)):
+            if pages:
+                at = len(bt.pages)
+                bt.pages.extend(pages)
+                self._mirror_set(gi, req.slot, at, pages)
         req.reserved, req._new_pages = n_new, taken
 
     def rollback(self, req: RequestCache) -> None:
         """Undo `reserve` after a step that failed: no state has advanced."""
-        for g, bt, pages in zip(self.groups, req.tables, req._new_pages):
+        for gi, (g, bt, pages) in enumerate(zip(self.groups, req.tables, req._new_pages)):
             if pages:
                 del bt.pages[len(bt.pages) - len(pages):]
+                self.table_mirror[gi][req.slot, len(bt.pages): len(bt.pages) + len(pages)] = -1
                 g.pool.give(pages)
         req.reserved, req._new_pages = 0, []
 
@@ -165,7 +173,7 @@ class CacheManager:
         passed go back to the pool."""
         req.length += req.reserved
         req.reserved, req._new_pages = 0, []
-        for g, bt in zip(self.groups, req.tables):
+        for gi, (g, bt) in enumerate(zip(self.groups, req.tables)):
             w = g.spec.window
             if w <= 0:
                 continue
@@ -174,15 +182,25 @@ class CacheManager:
             while bt.first_live < len(bt.pages) and (bt.first_live + 1) * self.page_size <= first_needed:
                 g.pool.give([bt.pages[bt.first_live]])
                 bt.pages[bt.first_live] = -1
+                self.table_mirror[gi][req.slot, bt.first_live] = -1
                 bt.first_live += 1
 
     def free(self, request_id) -> None:
         """Give back everything the request holds (finished, aborted or preempted)."""
         req = self.requests.pop(request_id)
-        for g, bt in zip(self.groups, req.tables):
+        for gi, (g, bt) in enumerate(zip(self.groups, req.tables)):
             g.pool.give(bt.live())
             bt.pages, bt.first_live = [], 0
+            self.table_mirror[gi][req.slot, :] = -1
         self._free_slots.append(req.slot)
+
+    def _mirror_set(self, gi: int, slot: int, at: int, pages) -> None:
+        m = self.table_mirror[gi]
+        if at + len(pages) > m.shape[1]:
+            wider = np.full((m.shape[0], max(2 * m.shape[1], at + len(pages))), -1, dtype=np.int32)
+            wider[:, :m.shape[1]] = m
+            self.table_mirror[gi] = m = wider
+        m[slot, at: at + len(pages)] = pages
 
     def free_all(self) -> None:
         for rid in list(self.requests):
@@ -201,6 +219,12 @@ class CacheManager:
             assert len(held) == len(set(held)), "a page is in two block tables"
             assert all(0 <= p < g.pool.num_pages for p in held)
             assert len(held) == g.pool.used_pages, "pages held by no request"
+            m = self.table_mirror[gi]
+            for r in self.requests.values():
+                n = len(r.tables[gi].pages)
+                assert m[r.slot, :n].tolist() == r.tables[gi].pages and (m[r.slot, n:] == -1).all(), "mirror out of step"
+            free = [s for s in self._free_slots]
+            assert (m[free] == -1).all(), "a free slot still has pages in the mirror"
         slots = [r.slot for r in self.requests.values()]
         assert len(set(slots)) == len(slots)
         assert sorted(slots + self._free_slots) == list(range(self.max_requests)), "a slot is lost"

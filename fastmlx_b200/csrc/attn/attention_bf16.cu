@@ -337,15 +337,15 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
 // part_o: [R, nkv, splits, 16, HD] float; part_ml: [R, nkv, splits, 16, 2] float (max in the
 // scaled log2 domain, sum).  With one split the output is written directly.
 __global__ void __launch_bounds__(THREADS)
-attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kv,
-                   const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ row_start,
-                   const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
-                   float* __restrict__ part_ml, int nh, int nkv, int page_size, long long num_pages, float scale,
+attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int* block_tables, int bt_stride,
+                   const int* row_start, const int* positions, bf16* out, float* part_o, float* part_ml, int nh, int nkv, int page_size, long long num_pages, float scale,
                    int window, int* status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   const int split = blockIdx.x, splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
   const int rep = nh / nkv;
+  pdl_trigger();
+  pdl_wait();
   const int t = row_start[r];
   const int pos = positions[t];                      // -1 for a padding row: no keys at all
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
@@ -466,11 +466,12 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
   }
 }
 
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    const int* __restrict__ row_start, bf16* __restrict__ out, int nh, int nkv,
-                                    int splits) {
+__global__ void attn_combine_kernel(const float* part_o, const float* part_ml, const int* row_start, bf16* out,
+                                    int nh, int nkv, int splits) {
   const int h = blockIdx.x, r = blockIdx.y;
   const int rep = nh / nkv, g = h / rep, row = h - g * rep;
+  pdl_trigger();
+  pdl_wait();
   const int t = row_start[r];
   const long long base = (((long long)r * nkv + g) * splits) * 16 + row;
   float M = -INFINITY;
@@ -556,13 +557,13 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (long long)rows * nkv * splits * 16 * HD : nullptr;
   dim3 grid(splits, nkv, rows);
-  attn_decode_kernel<<<grid, THREADS, decode_smem(), stream>>>(
+  fmx_launch(attn_decode_kernel, grid, dim3(THREADS), decode_smem(), stream,
       (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
       part_ml, nh, nkv, page_size, num_pages, scale, window, status);
   FMX_LAUNCH_CHECK();
   if (splits > 1) {
-    attn_combine_kernel<<<dim3(nh, rows), HD < 128 ? 64 : 128, 0, stream>>>(part_o, part_ml, row_start, (bf16*)out, nh,
-                                                                           nkv, splits);
+    fmx_launch(attn_combine_kernel, dim3(nh, rows), dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)part_o,
+               (const float*)part_ml, row_start, (bf16*)out, nh, nkv, splits);
     FMX_LAUNCH_CHECK();
   }
   return 0;

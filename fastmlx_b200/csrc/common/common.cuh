@@ -57,6 +57,37 @@ template <int BLOCK> __device__ __forceinline__ float block_sum(float v) {
   return r;
 }
 
+// Programmatic dependent launch.  A kernel launched through fmx_launch may be scheduled
+// while the kernel before it in the stream is still draining: it calls pdl_trigger() as its
+// first statement (letting the one after it be scheduled in turn), does what needs no input
+// from its predecessor (index arithmetic, reading weights), and calls pdl_wait() before it
+// reads or writes anything a predecessor may still touch.  pdl_wait() returns once every
+// earlier kernel has finished and its writes are visible.  Without the launch attribute both
+// are no-ops.  What a predecessor writes must not be read through the read-only data path
+// (__ldg, or a const __restrict__ pointer, which lets the compiler choose that path): such
+// loads count as invariant and may be moved above the wait.  Kernels launched this way
+// therefore take their activations through plain pointers.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool fmx_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t fmx_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = fmx_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Host side: the last error text of this thread, and the launch check every entry ends with.
 const char* fmx_set_error(const char* msg);
 int fmx_fail(const char* fmt, ...);

@@ -4,8 +4,10 @@
 
 // out[t, :] = table[ids[t], :].  A bad id leaves a status code and a row of zeros.
 template <typename T>
-__global__ void gather_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
+__global__ void gather_rows_kernel(const T* table, const int* ids, T* out,
                                    int d, long long nrows, int* status, int code) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const long long id = ids[t];
   T* dst = out + (long long)t * d;
@@ -34,7 +36,8 @@ FMX_EXPORT int fmx_gather_rows(const void* table, const int* ids, void* out, int
   if (dtype == FMX_F32)
     gather_rows_kernel<float><<<n, block, 0, stream>>>((const float*)table, ids, (float*)out, d, nrows, status, code);
   else if (dtype == FMX_BF16)
-    gather_rows_kernel<bf16><<<n, block, 0, stream>>>((const bf16*)table, ids, (bf16*)out, d, nrows, status, code);
+    fmx_launch(gather_rows_kernel<bf16>, dim3(n), dim3(block), 0, stream, (const bf16*)table, ids, (bf16*)out, d, nrows,
+               status, code);
   else
     return fmx_fail("fmx_gather_rows: unknown dtype %d", dtype);
   FMX_LAUNCH_CHECK();
@@ -72,8 +75,9 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
 // squares runs over a thread's elements in index order, then over the block in a fixed tree.
 template <int BLOCK, int CH>
 __global__ void __launch_bounds__(BLOCK)
-add_rmsnorm_bf16_vec_kernel(const bf16* __restrict__ x, bf16* residual, const float* __restrict__ w,
-                            bf16* __restrict__ out, int d, float eps) {
+add_rmsnorm_bf16_vec_kernel(const bf16* x, bf16* residual, const float* __restrict__ w, bf16* out, int d, float eps) {
+  pdl_trigger();
+  pdl_wait();
   const long long row = blockIdx.x;
   const int nvec = d / 8;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
@@ -143,11 +147,14 @@ FMX_EXPORT int fmx_add_rmsnorm(const void* x, void* residual, const float* w, vo
   else if (dtype == FMX_BF16) {
     const bool vec = d % 8 == 0 && aligned16(x) && aligned16(out) && aligned16(w) && (!residual || aligned16(residual));
     if (vec && d <= 128 * 8)
-      add_rmsnorm_bf16_vec_kernel<128, 1><<<rows, 128, 0, stream>>>((const bf16*)x, (bf16*)residual, w, (bf16*)out, d, eps);
+      fmx_launch(add_rmsnorm_bf16_vec_kernel<128, 1>, dim3(rows), dim3(128), 0, stream, (const bf16*)x, (bf16*)residual, w,
+                 (bf16*)out, d, eps);
     else if (vec && d <= 256 * 8)
-      add_rmsnorm_bf16_vec_kernel<256, 1><<<rows, 256, 0, stream>>>((const bf16*)x, (bf16*)residual, w, (bf16*)out, d, eps);
+      fmx_launch(add_rmsnorm_bf16_vec_kernel<256, 1>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, (bf16*)residual, w,
+                 (bf16*)out, d, eps);
     else if (vec && d <= 256 * 8 * 4)
-      add_rmsnorm_bf16_vec_kernel<256, 4><<<rows, 256, 0, stream>>>((const bf16*)x, (bf16*)residual, w, (bf16*)out, d, eps);
+      fmx_launch(add_rmsnorm_bf16_vec_kernel<256, 4>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, (bf16*)residual, w,
+                 (bf16*)out, d, eps);
     else
       add_rmsnorm_kernel<bf16, 256><<<rows, 256, 0, stream>>>((const bf16*)x, (bf16*)residual, w, (bf16*)out, d, eps);
   } else
@@ -171,7 +178,9 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
 }
 
 // bfloat16 with I a multiple of 8: eight elements per thread, 16-byte loads and stores.
-__global__ void silu_mul_bf16_vec_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I) {
+__global__ void silu_mul_bf16_vec_kernel(const bf16* gu, bf16* out, int I) {
+  pdl_trigger();
+  pdl_wait();
   const long long t = blockIdx.y;
   const int nvec = I / 8;
   const uint4* gp = reinterpret_cast<const uint4*>(gu + t * 2 * I);
@@ -203,7 +212,8 @@ FMX_EXPORT int fmx_silu_mul(const void* gu, void* out, int rows, int I, int dtyp
   else if (dtype == FMX_BF16) {
     if (I % 8 == 0 && aligned16(gu) && aligned16(out) && rows <= 65535) {
       const int bx = (I / 8 + block - 1) / block;
-      silu_mul_bf16_vec_kernel<<<dim3(bx < 64 ? bx : 64, rows), block, 0, stream>>>((const bf16*)gu, (bf16*)out, I);
+      fmx_launch(silu_mul_bf16_vec_kernel, dim3(bx < 64 ? bx : 64, rows), dim3(block), 0, stream, (const bf16*)gu,
+                 (bf16*)out, I);
     } else {
       silu_mul_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, I);
     }

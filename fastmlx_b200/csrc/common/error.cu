@@ -2,6 +2,7 @@
 // leaving a message here; the Python side raises it.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include "common.cuh"
 
 static thread_local char g_error[512] = "";
@@ -18,6 +19,18 @@ int fmx_fail(const char* fmt, ...) {
   va_end(ap);
   return 1;
 }
+
+// FASTMLX_PDL=0 turns programmatic dependent launch off (every kernel then waits for the one
+// before it to finish before it is scheduled).
+static int g_pdl = -1;
+bool fmx_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("FASTMLX_PDL");
+    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl == 1;
+}
+FMX_EXPORT void fmx_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 FMX_EXPORT const char* fmx_last_error() { return g_error; }
 

@@ -56,10 +56,12 @@ __global__ void rope_kv_write_kernel(T* qkv, const int* __restrict__ positions, 
 // cosine once per (token, pair) in shared memory, eight pairs per thread with 16-byte
 // accesses, and the rotated k (and v) written to the page in the same pass.
 __global__ void __launch_bounds__(128)
-rope_kv_write_bf16_vec_kernel(bf16* qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                              const long long* __restrict__ slot_mapping, bf16* kv, int nh, int nkv, int hd, int rot,
+rope_kv_write_bf16_vec_kernel(bf16* qkv, const int* positions, const float* __restrict__ inv_freq,
+                              const long long* slot_mapping, bf16* kv, int nh, int nkv, int hd, int rot,
                               int page_size, long long num_pages, long long row_stride, int* status) {
   extern __shared__ float sc[];                 // [half] sines, [half] cosines
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   bf16* row = qkv + (long long)t * row_stride;
   const int half = rot / 2;
@@ -133,7 +135,7 @@ FMX_EXPORT int fmx_rope_kv_write(void* qkv, const int* positions, const float* i
     const bool vec = !interleaved && rot > 0 && rot % 16 == 0 && hd % 8 == 0 && row_stride % 8 == 0 &&
                      ((uintptr_t)qkv & 15) == 0 && (kv == nullptr || ((uintptr_t)kv & 15) == 0);
     if (vec)
-      rope_kv_write_bf16_vec_kernel<<<T, block, (size_t)rot * sizeof(float), stream>>>(
+      fmx_launch(rope_kv_write_bf16_vec_kernel, dim3(T), dim3(block), (size_t)rot * sizeof(float), stream,
           (bf16*)qkv, positions, inv_freq, slot_mapping, (bf16*)kv, nh, nkv, hd, rot, page_size, num_pages, row_stride,
           status);
     else

@@ -82,9 +82,10 @@ __device__ float block_scan(float v, float* total) {
 }
 
 __global__ void __launch_bounds__(SBLOCK)
-sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
-              const float* __restrict__ uniform, const unsigned char* __restrict__ keep, long long keep_ld,
-              int* __restrict__ out) {
+sample_kernel(const float* logits, long long ld, int V, const float* temperature, const float* uniform,
+              const unsigned char* keep, long long keep_ld, int* out) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (long long)r * ld;
   const unsigned char* kp = keep ? keep + (long long)r * keep_ld : nullptr;
@@ -135,7 +136,7 @@ FMX_EXPORT int fmx_sample(const float* logits, long long ld, int rows, int V, co
   if (rows == 0) return 0;
   if (rows < 0 || V <= 0 || ld < V) return fmx_fail("fmx_sample: bad sizes rows=%d V=%d ld=%lld", rows, V, ld);
   if (temperature != nullptr && uniform == nullptr) return fmx_fail("fmx_sample: a temperature needs uniform numbers");
-  sample_kernel<<<rows, SBLOCK, 0, stream>>>(logits, ld, V, temperature, uniform, keep, keep_ld, out);
+  fmx_launch(sample_kernel, dim3(rows), dim3(SBLOCK), 0, stream, logits, ld, V, temperature, uniform, keep, keep_ld, out);
   FMX_LAUNCH_CHECK();
   return 0;
 }

@@ -84,6 +84,7 @@ class Engine:
         self.sampler = Sampler(self.rt)
         self._ids = itertools.count()
         self._pending_outputs: list[RequestOutput] = []
+        self._host_out = None
         self._requests: dict[str, Request] = {}
         self.counters = {"steps": 0, "prompt_tokens": 0, "generated_tokens": 0, "preemptions": 0, "h2d_bytes": 0,
                          "d2h_bytes": 0}
@@ -123,10 +124,11 @@ class Engine:
             return outs
         try:
             logits = self.step_fn.run(plan.entries, reserved=True, check=False)
-            rows = [(req.sampling, req.seed, len(req.output_token_ids), req.all_token_ids)
+            rows = [(req.sampling, req.seed, len(req.output_token_ids), req.tail(req.sampling.history_needed))
                     for req, s in zip(plan.requests, plan.samples) if s]
-            tokens = self.sampler.sample(logits, rows).tolist() if rows else []
-            self.step_fn.check_status()
+            tokens = self._read_back(self.sampler.sample(logits, rows)) if rows else []
+            if not rows:
+                self.step_fn.check_status()
         except (StepError, RuntimeError) as e:
             outs.extend(self.scheduler.step_failed(plan, str(e)))
             for req in plan.requests:
@@ -145,6 +147,23 @@ class Engine:
             if out.finished:
                 self._requests.pop(out.request_id, None)
         return outs
+
+    def _read_back(self, sampled: torch.Tensor) -> list[int]:
+        """Sampled ids and the kernels' status word in one wait: two small copies into pinned
+        memory, one synchronisation."""
+        n = sampled.numel()
+        if self.rt.device.type != "cuda":
+            self.step_fn.check_status()
+            return sampled.tolist()
+        if self._host_out is None or self._host_out.numel() < n + 4:
+            self._host_out = torch.empty(max(n + 4, 260), dtype=torch.int32).pin_memory()
+        self._host_out[:n].copy_(sampled, non_blocking=True)
+        self._host_out[n:n + 4].copy_(self.step_fn.status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        vals = self._host_out[:n + 4].tolist()
+        if vals[n]:
+            self.step_fn.check_status()          # raises with the code's meaning and clears the word
+        return vals[:n]
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts, sampling: SamplingParams | list[SamplingParams] | None = None) -> list[RequestOutput]:

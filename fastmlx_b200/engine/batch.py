@@ -135,21 +135,44 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
 
     tok, pos, trow = view("tokens"), view("positions"), view("token_row")
     rstart, rctx, rslot = view("row_start"), view("row_ctx"), view("row_slot")
+    one_each = T == R
+    slots = [e.request.slot for e in entries]
+    if one_each:
+        # one token per row: no per-row loop, the block tables come from the manager's mirror
+        tok[:R] = [e.tokens[0] for e in entries]
+        pos[:R] = ctxs
+        trow[:Rp] = np.arange(Rp, dtype=np.int32)
+        pos[R:Rp] = -1
+        rstart[:Rp + 1] = np.arange(Rp + 1, dtype=np.int32)
+        rctx[:R] = ctxs
+        rslot[:R] = slots
+        view("want")[:] = want
+        ctx_np = np.asarray(ctxs, dtype=np.int64)
+        for g in range(ngroups):
+            mirror = manager.table_mirror[g]
+            w = min(max_blocks, mirror.shape[1])
+            bt = view(f"bt{g}").reshape(Rp, max_blocks)
+            bt[:] = -1
+            bt[:R, :w] = mirror[slots, :w]
+            sm = view(f"sm{g}").view(np.int64)
+            sm[:] = -1
+            sm[:R] = bt[np.arange(R), ctx_np // ps].astype(np.int64) * ps + ctx_np % ps
     off = 0
-    for r, (e, q, c) in enumerate(zip(entries, q_lens, ctxs)):
+    for r, (e, q, c) in enumerate(zip(entries, q_lens, ctxs) if not one_each else ()):
         tok[off: off + q] = e.tokens
         pos[off: off + q] = np.arange(c, c + q, dtype=np.int32)
         trow[off: off + q] = r
         rstart[r], rctx[r], rslot[r] = off, c, e.request.slot
         off += q
-    for r in range(R, Rp):             # padding rows: one token, no context, stored nowhere
+    for r in range(R, Rp) if not one_each else ():   # padding rows: one token, no context, stored nowhere
         trow[off] = r
         pos[off] = -1
         rstart[r], rctx[r], rslot[r] = off, 0, 0
         off += 1
-    rstart[Rp] = off
-    view("want")[:] = want
-    for g in range(ngroups):
+    if not one_each:
+        rstart[Rp] = off
+        view("want")[:] = want
+    for g in range(ngroups) if not one_each else ():
         bt = view(f"bt{g}").reshape(Rp, max_blocks)
         bt[:] = -1
         sm = view(f"sm{g}").view(np.int64)

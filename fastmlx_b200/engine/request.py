@@ -51,6 +51,28 @@ class Request:
         return len(self.prompt_token_ids) + len(self.output_token_ids)
 
     @property
+    def last_token(self) -> int:
+        return self.output_token_ids[-1] if self.output_token_ids else self.prompt_token_ids[-1]
+
+    def tokens_from(self, start: int, n: int) -> list[int]:
+        """Tokens [start, start + n) of prompt + output without joining the two lists."""
+        np_ = len(self.prompt_token_ids)
+        if start + n <= np_:
+            return self.prompt_token_ids[start:start + n]
+        if start >= np_:
+            return self.output_token_ids[start - np_: start - np_ + n]
+        return self.prompt_token_ids[start:] + self.output_token_ids[: start + n - np_]
+
+    def tail(self, n: int) -> list[int]:
+        """The last n tokens of prompt + output (for the penalties' window)."""
+        if n <= 0:
+            return []
+        out = self.output_token_ids[-n:]
+        if len(out) < n:
+            out = self.prompt_token_ids[-(n - len(out)):] + out
+        return out
+
+    @property
     def finish_reason(self) -> str:
         return FINISH_REASON.get(self.status, "")
 

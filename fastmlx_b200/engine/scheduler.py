@@ -120,7 +120,7 @@ class Scheduler:
                     if victim is req:
                         break
             if req.status == RequestStatus.RUNNING and req.cache is not None and req.cache.reserved:
-                self._add(plan, req, [req.all_token_ids[-1]], True, scheduled)
+                self._add(plan, req, [req.last_token], True, scheduled)
                 budget -= 1
                 i += 1
             # else: req left `running` (preempted or finished); the same index holds the next one
@@ -164,8 +164,8 @@ class Scheduler:
         return req.status == RequestStatus.RUNNING and req.num_computed == req.num_tokens - 1
 
     def _schedule_portion(self, req: Request, room: int, plan: Plan, scheduled) -> int:
-        toks = req.all_token_ids
-        left = len(toks) - req.num_computed
+        total = req.num_tokens
+        left = total - req.num_computed
         n = min(left, room)
         if n <= 0:
             return 0
@@ -179,8 +179,8 @@ class Scheduler:
                 self.manager.reserve(req.cache, n)
             except OutOfPages:
                 return 0
-        last = req.num_computed + n == len(toks)
-        self._add(plan, req, toks[req.num_computed: req.num_computed + n], last, scheduled)
+        last = req.num_computed + n == total
+        self._add(plan, req, req.tokens_from(req.num_computed, n), last, scheduled)
         return n
 
     def _room_in_pages(self, req: Request) -> int:

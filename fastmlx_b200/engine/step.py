@@ -98,6 +98,8 @@ class StepFunction:
                     need = max(need, k.attn_decode_scratch_floats(rows, g.spec.num_kv_heads, s, g.spec.head_dim))
                     rows *= 2
             k.attention_scratch(rt.device, need)
+            if hasattr(k, "skinny_workspace"):
+                k.skinny_workspace(rt.device)
 
     def run(self, entries: list[StepEntry], reserved: bool = False, check: bool = True) -> torch.Tensor:
         """-> float32 logits [sum(len(e.want)), vocab] on the device, in the order of the

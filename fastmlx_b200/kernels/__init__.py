@@ -19,6 +19,7 @@ def launch_count() -> int:
     return _lib.launches
 
 F32, BF16 = 0, 1
+NUM_SMS = 148
 BAD_TOKEN, BAD_SLOT, BAD_PAGE, BAD_ROW = 1, 2, 3, 4
 
 
@@ -90,11 +91,61 @@ def gemm_simple(x, w, bias, out_dtype) -> torch.Tensor:
     return out
 
 
+SKINNY_MAX_ROWS = 8          # beyond this the library product is faster
+
+
+SKINNY_WS_FLOATS = 1 << 20       # 4 MiB of split-K partials
+SKINNY_TICKETS = 1 << 14
+_skinny_ws: dict = {}
+
+
+def skinny_workspace(device):
+    """Partials and tickets of the split-K skinny product, one pair per device, made once (a
+    CUDA graph holds their addresses).  The tickets start at zero and every launch leaves
+    them at zero.  Launches sharing them run on one stream."""
+    ws = _skinny_ws.get(device)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the skinny product's workspace must exist before a CUDA graph is captured")
+        ws = (torch.empty(SKINNY_WS_FLOATS, dtype=torch.float32, device=device),
+              torch.zeros(SKINNY_TICKETS, dtype=torch.int32, device=device))
+        _skinny_ws[device] = ws
+    return ws
+
+
+def skinny_splits(M: int, N: int, K: int) -> int:
+    """Split K over blocks until the grid fills the GPU about three times, keeping at least
+    512 of K per block and the partials inside the workspace."""
+    tiles = -(-N // 16)
+    s = max(1, min(round(4 * NUM_SMS / tiles), K // 512))
+    while s > 1 and (tiles * s * 128 * (1 if M <= 8 else 2) > SKINNY_WS_FLOATS or tiles > SKINNY_TICKETS):
+        s -= 1
+    return s
+
+
+def skinny_gemm(x, w, bias, out_dtype, splits=None) -> torch.Tensor:
+    """The decode-step product: at most 16 rows of x against a weight matrix streamed once."""
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if splits is None:
+        splits = skinny_splits(M, N, K)
+    ws, tickets = skinny_workspace(x.device) if splits > 1 else (None, None)
+    call("bf16", "fmx_skinny_gemm", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), out.data_ptr(),
+         out.stride(0), M, N, K, _dt(out), splits, _ptr(ws), ws.numel() if ws is not None else 0, _ptr(tickets),
+         tickets.numel() if tickets is not None else 0, _stream())
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
     """x[M, K] @ w[N, K]^T (+ bias) -> [M, N] in `out_dtype`, accumulated in 32-bit."""
     _need_cuda(x, w, bias)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
     assert x.stride(1) == 1 and w.stride(1) == 1
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_MAX_ROWS \
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32):
+        return skinny_gemm(x, w, bias, out_dtype)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0:
         wt = w.t()
         if bias is not None:
@@ -133,7 +184,6 @@ def paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> t
     return out
 
 
-NUM_SMS = 148
 MAX_SPLITS = 64
 _scratch: dict = {}
 

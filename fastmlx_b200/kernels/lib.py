@@ -31,7 +31,9 @@ _SIGNATURES = {
         "fmx_penalties": [_P, _L, _I, _I, _P, _I, _P, _P, _P, _P, _P],
         "fmx_logit_bias": [_P, _L, _I, _P, _P, _P, _I, _P],
     },
-    "bf16": {},
+    "bf16": {
+        "fmx_skinny_gemm": [_P, _L, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _L, _P],
+    },
     "attn": {
         "fmx_attn_prefill": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
         "fmx_attn_decode": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],

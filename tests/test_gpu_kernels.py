@@ -124,6 +124,30 @@ def test_linear_bf16(M, N, K, out_dtype, bias):
     close(got, ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32, "linear", scale=ref.abs().max().item() * 8)
 
 
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 32), (64, 64), (131, 80), (3072, 2048), (2048, 8192), (50, 8), (320, 192), (17, 1000)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_skinny_gemm(M, N, K, out_dtype):
+    """The weight-streaming product of decode steps: every row count up to 16, widths that are
+    no multiple of the 32-wide k block or of the 16-row tile, with and without a bias."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=11), rnd(N, K, dtype=torch.bfloat16, seed=12, scale=0.05)
+    b = rnd(N, seed=13) if N % 2 else None
+    ref = plain_ops.linear(x, w, b, torch.float64)
+    got = k().skinny_gemm(x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None, out_dtype)
+    close(got, ref, out_dtype, "skinny gemm", scale=ref.abs().max().item() * 8 if out_dtype == torch.float32 else None)
+    # a row's result does not depend on how many rows share the step
+    alone = k().skinny_gemm(x[M - 1:].contiguous().to(DEV), w.to(DEV), b.to(DEV) if b is not None else None, out_dtype)
+    assert torch.equal(alone[0], got[M - 1])
+    # K split over blocks: the same values up to the order of the partial sums, twice in a row
+    # over the same workspace and tickets
+    for splits in (2, 3, 7):
+        for _ in range(2):
+            sp = k().skinny_gemm(x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None, out_dtype, splits=splits)
+            close(sp, ref, out_dtype, f"skinny gemm, {splits} splits",
+                  scale=ref.abs().max().item() * 8 if out_dtype == torch.float32 else None)
+    assert int(k().skinny_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
+
+
 @pytest.mark.parametrize("ta,tw,tc", [(torch.bfloat16, torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32, torch.float32),
                                       (torch.bfloat16, torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16)])
 def test_gemm_simple_mixed_types(ta, tw, tc):
