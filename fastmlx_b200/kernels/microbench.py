@@ -1,0 +1,106 @@
+"""Times one kernel alone on synthetic inputs (CUDA events around a captured graph of
+launches), for tuning and for profiler captures on a small case.
+
+    python -m fastmlx_b200.kernels.microbench --kernel attn_decode --batch 8 --ctx 8192
+    python -m fastmlx_b200.kernels.microbench --kernel attn_prefill --batch 1 --qlen 2048
+    python -m fastmlx_b200.kernels.microbench --kernel skinny_gemm --M 8 --N 2048 --K 8192
+"""
+from __future__ import annotations
+
+import argparse
+from types import SimpleNamespace
+
+import torch
+
+from .. import kernels as k
+
+DEV = "cuda"
+
+
+def _time_graph(fn, launches: int, replays: int) -> float:
+    """Microseconds per call of fn, from a CUDA graph holding `launches` calls."""
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(launches):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (replays * launches) * 1e3
+
+
+def _attention_inputs(a, qlen):
+    B, ctx_len, nh, nkv, hd, ps = a.batch, a.ctx, a.nh, a.nkv, a.hd, a.page
+    per = -(-(ctx_len + qlen) // ps)
+    num_pages = B * per + 8
+    kv = torch.randn(num_pages, 2, nkv, ps, hd, device=DEV, dtype=torch.bfloat16)
+    bt = torch.randperm(num_pages, device=DEV)[:B * per].int().view(B, per).contiguous()
+    T = B * qlen
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV, dtype=torch.bfloat16)
+    pos = torch.cat([torch.arange(ctx_len, ctx_len + qlen) for _ in range(B)]).int().to(DEV)
+    ctx = SimpleNamespace(positions=pos, token_row=torch.arange(B).repeat_interleave(qlen).int().to(DEV),
+                          status=torch.zeros(4, dtype=torch.int32, device=DEV),
+                          row_start=(torch.arange(B + 1) * qlen).int().to(DEV),
+                          row_ctx=torch.full((B,), ctx_len, dtype=torch.int32, device=DEV), R=B, max_q_len=qlen,
+                          max_ctx_after=ctx_len + qlen, all_decode=qlen == 1, n_splits=0, scratch={})
+    return qkv, kv, ctx, SimpleNamespace(block_tables=bt)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "skinny_gemm"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=8192, help="tokens already in the cache")
+    ap.add_argument("--qlen", type=int, default=2048, help="tokens per row (attn_prefill)")
+    ap.add_argument("--nh", type=int, default=32)
+    ap.add_argument("--nkv", type=int, default=8)
+    ap.add_argument("--hd", type=int, default=64)
+    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--splits", type=int, default=0, help="0: the engine's own choice")
+    ap.add_argument("--M", type=int, default=8)
+    ap.add_argument("--N", type=int, default=2048)
+    ap.add_argument("--K", type=int, default=8192)
+    ap.add_argument("--launches", type=int, default=10, help="kernel launches per graph")
+    ap.add_argument("--replays", type=int, default=5)
+    a = ap.parse_args(argv)
+    if a.kernel == "attn_decode":
+        qkv, kv, ctx, grp = _attention_inputs(a, 1)
+        splits = a.splits or k.decode_splits(a.batch, a.nkv, a.ctx + 1)
+        us = _time_graph(lambda: k.paged_attention_decode(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, 0,
+                                                          splits=splits), a.launches, a.replays)
+        nbytes = a.batch * (a.ctx + 1) * a.nkv * a.hd * 2 * 2
+        print(f"attn_decode B={a.batch} ctx={a.ctx} nh={a.nh} nkv={a.nkv} hd={a.hd} page={a.page} splits={splits}: "
+              f"{us:.1f} us, {nbytes / us / 1e3:.0f} GB/s of K and V")
+    elif a.kernel == "attn_prefill":
+        a.ctx = a.ctx if a.ctx != 8192 else 0
+        qkv, kv, ctx, grp = _attention_inputs(a, a.qlen)
+        us = _time_graph(lambda: k.paged_attention_prefill(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, 0),
+                         a.launches, a.replays)
+        flops = 4 * a.nh * a.hd * a.batch * (a.qlen * a.ctx + a.qlen * (a.qlen + 1) / 2)
+        print(f"attn_prefill B={a.batch} ctx={a.ctx} qlen={a.qlen} nh={a.nh} nkv={a.nkv} hd={a.hd}: {us:.1f} us, "
+              f"{flops / us / 1e6:.0f} TFLOP/s")
+    else:
+        copies = max(1, int(300e6 // (a.N * a.K * 2)) + 1)        # more weight than L2 holds
+        ws = [torch.randn(a.N, a.K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(a.M, a.K, device=DEV, dtype=torch.bfloat16)
+        at = [0]
+
+        def f():
+            at[0] = (at[0] + 1) % copies
+            return k.skinny_gemm(x, ws[at[0]], None, torch.bfloat16, splits=a.splits or None)
+        us = _time_graph(f, a.launches, a.replays)
+        print(f"skinny_gemm M={a.M} N={a.N} K={a.K} splits={a.splits or k.skinny_splits(a.M, a.N, a.K)}: {us:.1f} us, "
+              f"{a.N * a.K * 2 / us / 1e3:.0f} GB/s of weights")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
