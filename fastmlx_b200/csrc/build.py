@@ -25,6 +25,7 @@ GROUPS = {
     "common": "common",
     "bf16": "bf16",
     "attn": "attn",
+    "tc": "tc",
 }
 HEAD_DIMS = tuple(range(16, 257, 16))
 

@@ -163,31 +163,34 @@ FMX_EXPORT int fmx_add_rmsnorm(const void* x, void* residual, const float* w, vo
   return 0;
 }
 
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(g) = g / (1 + exp(-g)), in 32-bit.
+// out[t, i] = silu(gate_i) * up_i, silu(g) = g / (1 + exp(-g)), in 32-bit.  A row of gu holds
+// 2 I values in blocks: `blk` gates, then their `blk` ups, and so on; blk = I is the plain
+// layout [all gates | all ups].
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int I) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int I, int blk) {
   const long long n = rows * I;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long t = idx / I;
     const int i = (int)(idx - t * I);
-    const float g = to_f(gu[t * 2 * I + i]);
-    const float u = to_f(gu[t * 2 * I + I + i]);
+    const int b = i / blk, j = i - b * blk;
+    const float g = to_f(gu[t * 2 * I + (long long)b * 2 * blk + j]);
+    const float u = to_f(gu[t * 2 * I + (long long)b * 2 * blk + blk + j]);
     out[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
   }
 }
 
 // bfloat16 with I a multiple of 8: eight elements per thread, 16-byte loads and stores.
-__global__ void silu_mul_bf16_vec_kernel(const bf16* gu, bf16* out, int I) {
+__global__ void silu_mul_bf16_vec_kernel(const bf16* gu, bf16* out, int I, int blk) {
   pdl_trigger();
   pdl_wait();
   const long long t = blockIdx.y;
-  const int nvec = I / 8;
+  const int nvec = I / 8, bvec = blk / 8;
   const uint4* gp = reinterpret_cast<const uint4*>(gu + t * 2 * I);
-  const uint4* up = reinterpret_cast<const uint4*>(gu + t * 2 * I + I);
   uint4* op = reinterpret_cast<uint4*>(out + t * I);
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gridDim.x * blockDim.x) {
-    const uint4 g4 = gp[i], u4 = up[i];
+    const int b = i / bvec, j = i - b * bvec;
+    const uint4 g4 = gp[b * 2 * bvec + j], u4 = gp[b * 2 * bvec + bvec + j];
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
     uint4 r;
@@ -201,21 +204,22 @@ __global__ void silu_mul_bf16_vec_kernel(const bf16* gu, bf16* out, int I) {
   }
 }
 
-FMX_EXPORT int fmx_silu_mul(const void* gu, void* out, int rows, int I, int dtype, cudaStream_t stream) {
+FMX_EXPORT int fmx_silu_mul(const void* gu, void* out, int rows, int I, int blk, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (rows < 0 || I <= 0) return fmx_fail("fmx_silu_mul: bad sizes rows=%d I=%d", rows, I);
+  if (blk <= 0 || I % blk) return fmx_fail("fmx_silu_mul: %d is no multiple of the block size %d", I, blk);
   const long long n = (long long)rows * I;
   const int block = 256;
   const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
   if (dtype == FMX_F32)
-    silu_mul_kernel<float><<<grid, block, 0, stream>>>((const float*)gu, (float*)out, rows, I);
+    silu_mul_kernel<float><<<grid, block, 0, stream>>>((const float*)gu, (float*)out, rows, I, blk);
   else if (dtype == FMX_BF16) {
-    if (I % 8 == 0 && aligned16(gu) && aligned16(out) && rows <= 65535) {
+    if (I % 8 == 0 && blk % 8 == 0 && aligned16(gu) && aligned16(out) && rows <= 65535) {
       const int bx = (I / 8 + block - 1) / block;
       fmx_launch(silu_mul_bf16_vec_kernel, dim3(bx < 64 ? bx : 64, rows), dim3(block), 0, stream, (const bf16*)gu,
-                 (bf16*)out, I);
+                 (bf16*)out, I, blk);
     } else {
-      silu_mul_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, I);
+      silu_mul_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, I, blk);
     }
   } else
     return fmx_fail("fmx_silu_mul: unknown dtype %d", dtype);

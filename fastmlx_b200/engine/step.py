@@ -26,7 +26,8 @@ class StepError(RuntimeError):
 
 STATUS_WORDS = 4
 _STATUS_TEXT = {1: "a token id outside the vocabulary", 2: "a cache slot outside the pool",
-                3: "a block-table entry that holds no page", 4: "a row index outside the batch"}
+                3: "a block-table entry that holds no page", 4: "a row index outside the batch",
+                5: "a wait inside a kernel that ran out of time"}
 
 
 def _pow2_at_least(n: int, floor: int = 1) -> int:
@@ -84,6 +85,8 @@ class StepFunction:
         self.graph_kernel_launches = 0
         self.last_h2d_bytes = 0
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=rt.device)
+        if hasattr(rt.k, "set_status_word") and rt.device.type == "cuda":
+            rt.k.set_status_word(rt.device, self.status)
         self.steps = 0
         self.tokens_run = 0
         self.last_ctx: StepContext | None = None

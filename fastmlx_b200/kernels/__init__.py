@@ -72,12 +72,15 @@ def add_rmsnorm(x: torch.Tensor, residual, weight: torch.Tensor, eps: float):
     return out, (residual if residual is not None else x)
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+def silu_mul(gate_up: torch.Tensor, block: int | None = None) -> torch.Tensor:
+    """silu(gate) * up over rows of 2 I values laid out in blocks of `block` gates followed by
+    their `block` ups (block = I, the default: all gates, then all ups)."""
     _need_cuda(gate_up)
     assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
     rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
     out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
-    call("common", "fmx_silu_mul", gate_up.data_ptr(), out.data_ptr(), rows, inter, _dt(gate_up), _stream())
+    call("common", "fmx_silu_mul", gate_up.data_ptr(), out.data_ptr(), rows, inter, int(block or inter), _dt(gate_up),
+         _stream())
     return out
 
 
@@ -89,6 +92,30 @@ def gemm_simple(x, w, bias, out_dtype) -> torch.Tensor:
     call("common", "fmx_gemm_simple", x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
          x.stride(0), w.stride(0), out.stride(0), _dt(x), _dt(w), _dt(out), _stream())
     return out
+
+
+import os as _os
+
+_USE_TC = _os.environ.get("FASTMLX_GEMM", "tcgen05") != "cublas"      # "cublas": library products for prefill
+_tc_status: dict = {}
+
+
+def _dev_index(device) -> int:
+    device = torch.device(device)
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def set_status_word(device, status: torch.Tensor) -> None:
+    """The word in which kernels called through `linear` report trouble (a bounded wait that
+    ran out): the engine registers its own, so that one read after a step covers them."""
+    _tc_status[_dev_index(device)] = status
+
+
+def _status_word(device):
+    st = _tc_status.get(_dev_index(device))
+    if st is None:
+        st = _tc_status[_dev_index(device)] = torch.zeros(4, dtype=torch.int32, device=device)
+    return st
 
 
 SKINNY_MAX_ROWS = 8          # beyond this the library product is faster
@@ -137,6 +164,43 @@ def skinny_gemm(x, w, bias, out_dtype, splits=None) -> torch.Tensor:
     return out
 
 
+EPI_PLAIN, EPI_SILU_MUL, EPI_RESIDUAL = 0, 1, 2
+
+
+GATE_UP_BLOCK = 128          # gate/up rows of a fused weight alternate in blocks of this many
+TC_MIN_ROWS = 128            # from this many rows on, products run on the tcgen05 kernel
+
+
+def tc_enabled() -> bool:
+    return _USE_TC
+
+
+def tile_width(M: int, N: int) -> int:
+    """The tile width (of 128, 192, 256) whose tiles fill the SMs' rounds best; wider wins ties."""
+    best, best_eff = 256, -1.0
+    for bn in (256, 192, 128):
+        tiles = -(-M // 128) * -(-N // bn)
+        eff = tiles / (-(-tiles // NUM_SMS) * NUM_SMS) * (N / (-(-N // bn) * bn)) * (0.8 if bn == 128 else 1.0)
+        if eff > best_eff + 1e-9:
+            best, best_eff = bn, eff
+    return best
+
+
+def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn: int | None = None) -> torch.Tensor:
+    """x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory).
+    epilogue EPI_SILU_MUL: w's rows come in blocks of bn/2 gate rows then bn/2 up rows, and the
+    result is silu(gate) * up, [M, N/2]; EPI_RESIDUAL: residual + product."""
+    M, K = x.shape
+    N = w.shape[0]
+    if bn is None:
+        bn = 2 * GATE_UP_BLOCK if epilogue == EPI_SILU_MUL else tile_width(M, N)
+    out = torch.empty((M, N // 2 if epilogue == EPI_SILU_MUL else N), dtype=torch.bfloat16, device=x.device)
+    call("tc", "fmx_gemm_tcgen05", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+         _ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, bn, epilogue, NUM_SMS,
+         _ptr(status), _stream())
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
     """x[M, K] @ w[N, K]^T (+ bias) -> [M, N] in `out_dtype`, accumulated in 32-bit."""
     _need_cuda(x, w, bias)
@@ -146,6 +210,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32):
         return skinny_gemm(x, w, bias, out_dtype)
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] >= TC_MIN_ROWS and bias is None \
+            and out_dtype == torch.bfloat16 and _USE_TC and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 \
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+        return gemm_tcgen05(x, w, _status_word(x.device))
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0:
         wt = w.t()
         if bias is not None:

@@ -22,7 +22,7 @@ _SIGNATURES = {
     "common": {
         "fmx_gather_rows": [_P, _P, _P, _I, _I, _L, _I, _P, _I, _P],
         "fmx_add_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
-        "fmx_silu_mul": [_P, _P, _I, _I, _I, _P],
+        "fmx_silu_mul": [_P, _P, _I, _I, _I, _I, _P],
         "fmx_gemm_simple": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
         "fmx_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _L, _I, _P, _P],
         "fmx_paged_attention_simple": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P],
@@ -33,6 +33,9 @@ _SIGNATURES = {
     },
     "bf16": {
         "fmx_skinny_gemm": [_P, _L, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _L, _P],
+    },
+    "tc": {
+        "fmx_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     },
     "attn": {
         "fmx_attn_prefill": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],

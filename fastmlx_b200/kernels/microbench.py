@@ -56,7 +56,7 @@ def _attention_inputs(a, qlen):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "skinny_gemm"])
+    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "skinny_gemm", "gemm"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192, help="tokens already in the cache")
     ap.add_argument("--qlen", type=int, default=2048, help="tokens per row (attn_prefill)")
@@ -87,6 +87,17 @@ def main(argv=None) -> int:
         flops = 4 * a.nh * a.hd * a.batch * (a.qlen * a.ctx + a.qlen * (a.qlen + 1) / 2)
         print(f"attn_prefill B={a.batch} ctx={a.ctx} qlen={a.qlen} nh={a.nh} nkv={a.nkv} hd={a.hd}: {us:.1f} us, "
               f"{flops / us / 1e6:.0f} TFLOP/s")
+    elif a.kernel == "gemm":
+        w = torch.randn(a.N, a.K, device=DEV, dtype=torch.bfloat16) * 0.02
+        x = torch.randn(a.M, a.K, device=DEV, dtype=torch.bfloat16)
+        st = torch.zeros(4, dtype=torch.int32, device=DEV)
+        flops = 2.0 * a.M * a.N * a.K
+        for name, f in (("cublas", lambda: torch.mm(x, w.t())),
+                        ("tcgen05 bn128", lambda: k.gemm_tcgen05(x, w, st, bn=128)),
+                        ("tcgen05 bn256", lambda: k.gemm_tcgen05(x, w, st, bn=256))):
+            us = _time_graph(f, a.launches, a.replays)
+            print(f"gemm M={a.M} N={a.N} K={a.K} {name}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+        print("status", st.tolist())
     else:
         copies = max(1, int(300e6 // (a.N * a.K * 2)) + 1)        # more weight than L2 holds
         ws = [torch.randn(a.N, a.K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]

@@ -12,11 +12,18 @@ class Linear(Part):
     gate/up run as one matrix product (tamnd/fastmlx runs them one by one,
     compute/models/llama.go:403-405,426-427, through compute/models/qwen3_forward.go:111-115)."""
 
-    def __init__(self, in_features: int, names, bias: bool = False):
+    def __init__(self, in_features: int, names, bias: bool = False, interleave: int = 0):
+        """`interleave` = b > 0 (two matrices of equal height, a multiple of b): their rows are
+        stacked in alternating blocks of b, so that a tile of 2b output columns holds b rows
+        of the first and the matching b rows of the second."""
         self.in_features = int(in_features)
         self.names = [(n, int(o)) for n, o in names]
         self.out_features = sum(o for _, o in self.names)
         self.has_bias = bool(bias)
+        self.interleave = int(interleave)
+        if self.interleave and (len(self.names) != 2 or self.names[0][1] != self.names[1][1]
+                                or self.names[0][1] % self.interleave):
+            raise ValueError("interleaving takes two matrices of equal height, a multiple of the block")
         self.weight = None
         self.bias = None
 
@@ -30,9 +37,15 @@ class Linear(Part):
         ws = [to_compute(tensors[n + ".weight"], rt) for n, _ in self.names]
         if len({w.dtype for w in ws}) > 1:
             ws = [w.float() for w in ws]
-        self.weight = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
-        if self.has_bias:
-            self.bias = torch.cat([to_f32_vector(tensors[n + ".bias"], rt) for n, _ in self.names]).contiguous()
+        bs = [to_f32_vector(tensors[n + ".bias"], rt) for n, _ in self.names] if self.has_bias else None
+        if self.interleave:
+            b = self.interleave
+            ws = [torch.stack([w.view(-1, b, self.in_features) for w in ws], dim=1).reshape(-1, self.in_features)]
+            if bs is not None:
+                bs = [torch.stack([v.view(-1, b) for v in bs], dim=1).reshape(-1)]
+        self.weight = ws[0].contiguous() if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
+        if bs is not None:
+            self.bias = torch.cat(bs).contiguous()
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()

@@ -1,6 +1,8 @@
 """Dense gated feed-forward."""
 from __future__ import annotations
 
+import torch
+
 from .base import FeedForward
 from .linear import Linear
 
@@ -10,16 +12,27 @@ class SwiGLU(FeedForward):
     compute/models/llama.go:426-428, compute/models/qwen3_forward.go:229-239).  gate and
     up run as one product whose output is [gate | up]."""
 
+    BLOCK = 128          # gate and up rows alternate in blocks of this many when the width allows
+
     def __init__(self, width: int, intermediate: int, name: str, bias: bool = False,
                  proj_names=("gate_proj", "up_proj", "down_proj")):
         self.width, self.intermediate = int(width), int(intermediate)
         g, u, d = (f"{name}.{p}" for p in proj_names)
-        self.gate_up = Linear(width, [(g, intermediate), (u, intermediate)], bias)
+        # In blocks, a 256-wide tile of the product holds 128 gates and their 128 ups: the
+        # tensor-core kernel then applies SiLU-and-multiply in its epilogue and the [T, 2I]
+        # intermediate is never written.
+        self.block = self.BLOCK if intermediate % self.BLOCK == 0 else 0
+        self.gate_up = Linear(width, [(g, intermediate), (u, intermediate)], bias, interleave=self.block)
         self.down = Linear(intermediate, [(d, width)], bias)
 
     def children(self):
         return (self.gate_up, self.down)
 
     def forward(self, x, ctx):
-        gu = self.gate_up.forward(x)
-        return self.down.forward(self.rt.k.silu_mul(gu))
+        k, w = self.rt.k, self.gate_up.weight
+        if self.block and self.gate_up.bias is None and x.dtype == w.dtype == torch.bfloat16 \
+                and x.shape[0] >= getattr(k, "TC_MIN_ROWS", 1 << 30) and getattr(k, "tc_enabled", lambda: False)():
+            act = k.gemm_tcgen05(x, w, ctx.status if ctx is not None else None, epilogue=k.EPI_SILU_MUL)
+        else:
+            act = k.silu_mul(self.gate_up.forward(x), self.block or None)
+        return self.down.forward(act)

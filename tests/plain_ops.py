@@ -34,9 +34,11 @@ def add_rmsnorm(x, residual, weight, eps):
     return out.to(x.dtype), residual
 
 
-def silu_mul(gate_up):
+def silu_mul(gate_up, block=None):
     inter = gate_up.shape[1] // 2
-    g, u = gate_up[:, :inter].to(F64), gate_up[:, inter:].to(F64)
+    b = block or inter
+    v = gate_up.reshape(gate_up.shape[0], inter // b, 2, b).to(F64)
+    g, u = v[:, :, 0, :].reshape(-1, inter), v[:, :, 1, :].reshape(-1, inter)
     return (g * torch.sigmoid(g) * u).to(gate_up.dtype)
 
 

@@ -124,6 +124,42 @@ def test_linear_bf16(M, N, K, out_dtype, bias):
     close(got, ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32, "linear", scale=ref.abs().max().item() * 8)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 64), (256, 256, 512), (2048, 3072, 2048), (300, 200, 136),
+                                   (1, 320, 192), (100, 8, 8), (129, 385, 72), (640, 2048, 8192)])
+@pytest.mark.parametrize("bn", [128, 192, 256])
+def test_gemm_tcgen05(M, N, K, bn):
+    """The tensor-memory product against the plain one: tiles cut by every edge (rows, columns
+    and k that are no multiples of 128 / bn / 64), all three tile widths."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=21), rnd(N, K, dtype=torch.bfloat16, seed=22, scale=0.05)
+    st = status()
+    got = k().gemm_tcgen05(x.to(DEV), w.to(DEV), st, bn=bn)
+    assert st.tolist()[0] == 0
+    close(got, plain_ops.linear(x, w, None, torch.float64), torch.bfloat16, f"tcgen05 product, tile width {bn}")
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 384, 136), (2048, 1024, 512), (5, 256, 64)])
+def test_gemm_tcgen05_epilogues(M, I, K):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=31)
+    wg, wu = rnd(I, K, dtype=torch.bfloat16, seed=32, scale=0.1), rnd(I, K, dtype=torch.bfloat16, seed=33, scale=0.1)
+    blk = k().GATE_UP_BLOCK
+    w = torch.stack([wg.view(-1, blk, K), wu.view(-1, blk, K)], dim=1).reshape(2 * I, K).contiguous()
+    st = status()
+    got = k().gemm_tcgen05(x.to(DEV), w.to(DEV), st, epilogue=k().EPI_SILU_MUL)
+    # as the unfused path: both products rounded to bfloat16, then silu(gate) * up
+    g = plain_ops.linear(x, wg, None, torch.bfloat16)
+    u = plain_ops.linear(x, wu, None, torch.bfloat16)
+    ref = plain_ops.silu_mul(torch.cat([g, u], dim=1))
+    assert got.shape == (M, I) and st.tolist()[0] == 0
+    close(got, ref, torch.bfloat16, "fused SiLU-mul epilogue", extra=2.0 ** -8 * ref.abs().max().item())
+    # the same weight through the unfused kernels
+    gu = k().linear(x.to(DEV), w.to(DEV), None, torch.bfloat16)
+    close(k().silu_mul(gu, blk), ref, torch.bfloat16, "blocked SiLU-mul", extra=2.0 ** -8 * ref.abs().max().item())
+    res = rnd(M, 2 * I, dtype=torch.bfloat16, seed=34)
+    got = k().gemm_tcgen05(x.to(DEV), w.to(DEV), st, epilogue=k().EPI_RESIDUAL, residual=res.to(DEV))
+    ref = (plain_ops.linear(x, w, None, torch.bfloat16).double() + res.double())
+    close(got, ref, torch.bfloat16, "residual epilogue", extra=2.0 ** -8 * ref.abs().max().item())
+
+
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(16, 32), (64, 64), (131, 80), (3072, 2048), (2048, 8192), (50, 8), (320, 192), (17, 1000)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
