@@ -37,7 +37,7 @@ constexpr int CHUNKS = HD / 8;           // 16-byte chunks per row
 constexpr int TILE = BN * ROW;           // elements of one K (or V) tile
 constexpr int THREADS = 128;
 constexpr int PREFILL_STAGES = HD <= 128 ? 3 : 2;
-constexpr int DECODE_STAGES = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
+constexpr int DECODE_STAGES = HD <= 128 ? 3 : 2;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -338,8 +338,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
 // scaled log2 domain, sum).  With one split the output is written directly.
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int* block_tables, int bt_stride,
-                   const int* row_start, const int* positions, bf16* out, float* part_o, float* part_ml, int nh, int nkv, int page_size, long long num_pages, float scale,
-                   int window, int* status) {
+                   const int* row_start, const int* positions, bf16* out, float* part_o, float* part_ml, int nh, int nkv,
+                   int page_size, long long num_pages, float scale, int window, int* status, int* tickets) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   const int split = blockIdx.x, splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
@@ -457,13 +457,39 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
       out[((long long)t * nh + g * rep + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     } else {
       const long long pi = (((long long)r * nkv + g) * splits + split) * 16 + row;
-      part_o[pi * HD + d] = acc;
+      __stcg(&part_o[pi * HD + d], acc);
       if (d == 0) {
-        part_ml[pi * 2] = M;
-        part_ml[pi * 2 + 1] = L;
+        __stcg(&part_ml[pi * 2], M);
+        __stcg(&part_ml[pi * 2 + 1], L);
       }
     }
   }
+  if (splits == 1 || tickets == nullptr) return;
+  // The block that draws the last ticket of this (row, kv head) combines the splits, in split
+  // order.  Nobody waits: the others are done once their partial is written.
+  __shared__ int drew_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) drew_last = atomicAdd(&tickets[r * nkv + g], 1) == splits - 1;
+  __syncthreads();
+  if (!drew_last) return;
+  __threadfence();
+  const long long base = (((long long)r * nkv + g) * splits) * 16;
+  for (int idx = threadIdx.x; idx < rep * HD; idx += THREADS) {
+    const int row = idx / HD, d = idx - row * HD;
+    float M = -INFINITY;
+    for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, __ldcg(&part_ml[(base + (long long)sp * 16 + row) * 2]));
+    const float Mu = M == -INFINITY ? 0.f : M;
+    float L = 0.f, acc = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+      const long long pi = base + (long long)sp * 16 + row;
+      const float f = exp2f(__ldcg(&part_ml[pi * 2]) - Mu);
+      L += f * __ldcg(&part_ml[pi * 2 + 1]);
+      acc += f * __ldcg(&part_o[pi * HD + d]);
+    }
+    out[((long long)t * nh + g * rep + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+  if (threadIdx.x == 0) tickets[r * nkv + g] = 0;      // ready for the next launch
 }
 
 __global__ void attn_combine_kernel(const float* part_o, const float* part_ml, const int* row_start, bf16* out,
@@ -534,10 +560,14 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
   return 0;
 }
 
+// tickets: rows * nkv ints, zero before the first call (every call leaves them zero); with
+// tickets the last block of each (row, kv head) combines the splits itself, without them a
+// second kernel does.  Calls that share scratch or tickets must not overlap on the GPU.
 FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv, const int* block_tables,
                                int bt_stride, const int* row_start, const int* positions, void* out, float* scratch,
-                               long long scratch_floats, int rows, int splits, int nh, int nkv, int page_size,
-                               long long num_pages, float scale, int window, int* status, cudaStream_t stream) {
+                               long long scratch_floats, int* tickets, int rows, int splits, int nh, int nkv,
+                               int page_size, long long num_pages, float scale, int window, int* status,
+                               cudaStream_t stream) {
   if (rows == 0) return 0;
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || splits <= 0)
     return fmx_fail("fmx_attn_decode: bad sizes rows=%d nh=%d nkv=%d page=%d splits=%d", rows, nh, nkv, page_size, splits);
@@ -559,9 +589,9 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
   dim3 grid(splits, nkv, rows);
   fmx_launch(attn_decode_kernel, grid, dim3(THREADS), decode_smem(), stream,
       (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
-      part_ml, nh, nkv, page_size, num_pages, scale, window, status);
+      part_ml, nh, nkv, page_size, num_pages, scale, window, status, tickets);
   FMX_LAUNCH_CHECK();
-  if (splits > 1) {
+  if (splits > 1 && tickets == nullptr) {
     fmx_launch(attn_combine_kernel, dim3(nh, rows), dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)part_o,
                (const float*)part_ml, row_start, (bf16*)out, nh, nkv, splits);
     FMX_LAUNCH_CHECK();
@@ -631,7 +661,7 @@ FMX_EXPORT int fmx_attn_decode_noalloc(const void* q, long long q_stride, const 
   dim3 grid(splits, nkv, rows);
   attn_decode_kernel<<<grid, THREADS, decode_smem(), stream>>>(
       (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
-      part_ml, nh, nkv, page_size, num_pages, scale, window, status);
+      part_ml, nh, nkv, page_size, num_pages, scale, window, status, (int*)nullptr);
   FMX_LAUNCH_CHECK();
   if (splits > 1) {
     attn_combine_kernel<<<dim3(nh, rows), HD < 128 ? 64 : 128, 0, stream>>>(part_o, part_ml, row_start, (bf16*)out, nh,

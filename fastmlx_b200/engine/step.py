@@ -97,10 +97,12 @@ class StepFunction:
             for g in manager.groups:
                 rows = 1
                 while rows <= max_graph_rows:
-                    s = k.decode_splits(rows, g.spec.num_kv_heads, 1 << 30)
+                    s = k.decode_splits(rows, g.spec.num_kv_heads, 1 << 30, g.spec.head_dim)
                     need = max(need, k.attn_decode_scratch_floats(rows, g.spec.num_kv_heads, s, g.spec.head_dim))
                     rows *= 2
             k.attention_scratch(rt.device, need)
+            if hasattr(k, "attention_tickets"):
+                k.attention_tickets(rt.device)
             if hasattr(k, "skinny_workspace"):
                 k.skinny_workspace(rt.device)
 

@@ -268,10 +268,27 @@ def attention_scratch(device, floats: int) -> torch.Tensor:
     return buf
 
 
-def decode_splits(rows: int, nkv: int, max_ctx: int) -> int:
-    """Enough blocks to fill the GPU about four times over, at least 128 keys to a split."""
-    want = max(1, (4 * NUM_SMS) // max(1, rows * nkv))
-    return max(1, min(MAX_SPLITS, want, -(-max_ctx // 128)))
+ATTN_TICKETS = 1 << 16
+_tickets: dict = {}
+
+
+def attention_tickets(device) -> torch.Tensor:
+    """Tickets of the split decode attention (one per row and kv head), zero between launches."""
+    t = _tickets.get(_dev_index(device))
+    if t is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the attention tickets must exist before a CUDA graph is captured")
+        t = _tickets[_dev_index(device)] = torch.zeros(ATTN_TICKETS, dtype=torch.int32, device=device)
+    return t
+
+
+def decode_splits(rows: int, nkv: int, max_ctx: int, hd: int = 64) -> int:
+    """As many splits as keep the whole grid resident at once (a second, partial round of
+    blocks costs more than it brings), with at least 512 keys to a split."""
+    stages = 3 if hd <= 128 else 2
+    smem = stages * 2 * 64 * (hd + 8) * 2
+    resident = NUM_SMS * max(1, min(5, (227 * 1024) // smem))
+    return max(1, min(MAX_SPLITS, resident // max(1, rows * nkv), -(-max_ctx // 512)))
 
 
 def attn_decode_scratch_floats(rows: int, nkv: int, splits: int, hd: int) -> int:
@@ -284,14 +301,15 @@ def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, spli
     R = ctx.R
     out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
     if splits is None:
-        splits = getattr(ctx, "n_splits", 0) or decode_splits(R, nkv, max(1, ctx.max_ctx_after))
+        splits = getattr(ctx, "n_splits", 0) or decode_splits(R, nkv, max(1, ctx.max_ctx_after), hd)
     need = attn_decode_scratch_floats(R, nkv, splits, hd)
     scratch = attention_scratch(qkv.device, need) if need else None
+    tickets = attention_tickets(qkv.device) if need and R * nkv <= ATTN_TICKETS else None
     bt = group.block_tables
     call(f"attn_hd{hd}", "fmx_attn_decode", qkv.data_ptr(), qkv.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
          ctx.row_start.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), _ptr(scratch),
-         scratch.numel() if scratch is not None else 0, R, splits, nh, nkv, kv.shape[3], kv.shape[0], float(scale),
-         int(window), _ptr(ctx.status), _stream())
+         scratch.numel() if scratch is not None else 0, _ptr(tickets), R, splits, nh, nkv, kv.shape[3], kv.shape[0],
+         float(scale), int(window), _ptr(ctx.status), _stream())
     return out
 
 

@@ -73,7 +73,7 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     if a.kernel == "attn_decode":
         qkv, kv, ctx, grp = _attention_inputs(a, 1)
-        splits = a.splits or k.decode_splits(a.batch, a.nkv, a.ctx + 1)
+        splits = a.splits or k.decode_splits(a.batch, a.nkv, a.ctx + 1, a.hd)
         us = _time_graph(lambda: k.paged_attention_decode(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, 0,
                                                           splits=splits), a.launches, a.replays)
         nbytes = a.batch * (a.ctx + 1) * a.nkv * a.hd * 2 * 2
