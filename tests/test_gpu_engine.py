@@ -166,3 +166,35 @@ def test_command_line_generate(dirs, tmp_path):
     assert res.returncode == 0, res.stderr[-2000:]
     lines = [json.loads(l) for l in res.stdout.strip().splitlines()]
     assert len(lines) == 2 and all(l["completion_tokens"] == 3 for l in lines)
+
+
+def test_real_layer_sizes_bfloat16_against_32_bit(tmp_path):
+    """Two layers with the layer sizes of Llama-3.2-1B (width 2048, 32/8 heads of 64, 8192
+    intermediate, llama3-scaled rotary) and a vocabulary cut to 4,000: the bfloat16 engine
+    (tensor-memory products for the prompt, weight-streaming products and split attention
+    for the decoded tokens, CUDA graphs) against the 32-bit engine, on a prompt of 300
+    tokens fed in portions beside another request's decoded tokens."""
+    from fastmlx_b200.engine.replay import Replayer
+    import traces
+    cfg = {"model_type": "llama", "num_hidden_layers": 2, "hidden_size": 2048, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 4000,
+           "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 4096,
+           "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192}}
+    d = tiny.make_model_dir(tmp_path, cfg, seed=5)
+    prompts = {"long": tiny.rand_tokens(300, 4000, 1), "short": tiny.rand_tokens(40, 4000, 2),
+               "mid": tiny.rand_tokens(150, 4000, 3)}
+    steps = traces.mixed(prompts, chunk=(129, 64, 33, 2, 128), decode_after=0.8)
+    want_last = [dict(s, entries=[dict(e, want=e["want"][-1:]) for e in s["entries"]]) for s in steps]
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        rp = Replayer(d, dtype, 1024, page_size=16)
+        outs[dtype] = traces.collect(want_last, [rp.step(s) for s in want_last])
+        rp.manager.check()
+    import numpy as np
+    worst = 0.0
+    for rid in prompts:
+        for pos, ref in outs["float32"][rid].items():
+            got = outs["bfloat16"][rid][pos]
+            worst = max(worst, float(np.abs(got - ref).max() / np.abs(ref).max()))
+    assert worst < 3e-2, worst
