@@ -201,6 +201,37 @@ def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn
     return out
 
 
+def can_fuse_skinny(x, w, bias=None) -> bool:
+    """May this product run on the fused skinny kernel (norm prologue, residual / SiLU-mul epilogue)?"""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and bias is None
+            and 0 < x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.stride(1) == 1 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def skinny_fused(x, w, out_dtype=torch.bfloat16, norm=None, residual=None, block: int = 0, out=None, splits=None):
+    """x[M <= 8, K] @ w[N, K]^T with its neighbours folded in.  norm = (weight float32 [K], eps):
+    the rows of x are RMS-normalised on the fly.  residual [M, n_out] is added to the product
+    (out may be the residual itself).  block > 0: w's rows alternate in blocks of `block` gate
+    rows and their up rows, and the result is silu(gate) * up, [M, N/2]."""
+    M, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if block else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+    tiles = N // 32 if block else -(-N // 16)
+    if splits is None:
+        splits = max(1, min(round(4 * NUM_SMS / tiles), K // 512))
+        while splits > 1 and (tiles * splits * (256 if block else 128) > SKINNY_WS_FLOATS or tiles > SKINNY_TICKETS):
+            splits -= 1
+    ws, tickets = skinny_workspace(x.device) if splits > 1 else (None, None)
+    nw, eps = norm if norm is not None else (None, 0.0)
+    call("bf16", "fmx_skinny_fused", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+         M, N, K, _dt(out), _ptr(nw), float(eps), _ptr(residual), residual.stride(0) if residual is not None else 0,
+         int(block), splits, _ptr(ws), ws.numel() if ws is not None else 0, _ptr(tickets),
+         tickets.numel() if tickets is not None else 0, _stream())
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
     """x[M, K] @ w[N, K]^T (+ bias) -> [M, N] in `out_dtype`, accumulated in 32-bit."""
     _need_cuda(x, w, bias)

@@ -45,8 +45,9 @@ class GQAAttention(Mixer):
         return PagedKVSpec(self.nkv, self.hd, self.window)
 
     def forward(self, x, ctx, cache):
-        qkv = self.qkv.forward(x)
+        return self.o.forward(self._attend(self.qkv.forward(x), ctx, cache))
+
+    def _attend(self, qkv, ctx, cache):
         self.pos.apply_and_store(qkv, ctx, cache, self.nh, 0 if self.share_kv else self.nkv, self.hd)
-        a = self.rt.k.paged_attention(qkv, cache.kv, ctx, ctx.groups[cache.group],
-                                      self.nh, self.nkv, self.hd, self.scale, self.window)
-        return self.o.forward(a)
+        return self.rt.k.paged_attention(qkv, cache.kv, ctx, ctx.groups[cache.group],
+                                         self.nh, self.nkv, self.hd, self.scale, self.window)

@@ -117,6 +117,17 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
+    def forward_in_block(self, delta, residual, norm: "Norm", ctx, cache):
+        """What a block calls: (delta, residual) in, (delta', residual') out, where the stream
+        is residual + delta (either may be None).  The default normalises and calls `forward`;
+        a part that can fold the norm into its first kernel and the residual sum into its last
+        overrides this and returns (None, stream).  (The skinny product has both folds,
+        `kernels.skinny_fused`; for this architecture's sizes the norm fold costs more than the
+        small norm kernel it saves, since every block has to read whole rows, so the stock
+        parts keep the default.)"""
+        x, residual = norm.forward(delta, residual)
+        return self.forward(x, ctx, cache), residual
+
 
 class FeedForward(Part):
     """forward(x[T, d], ctx) -> [T, d]; dense here, a routed one has the same face."""
@@ -124,10 +135,16 @@ class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
+    def forward_in_block(self, delta, residual, norm: "Norm", ctx):
+        """See Mixer.forward_in_block."""
+        x, residual = norm.forward(delta, residual)
+        return self.forward(x, ctx), residual
+
 
 class Norm(Part):
-    """forward(x, residual) -> (normed, residual'): residual' = residual + x (or x when
-    residual is None), summed in 32-bit and rounded once; normed = norm(residual')."""
+    """forward(x, residual) -> (normed, residual'): residual' = residual + x (or whichever of
+    the two is given when the other is None), summed in 32-bit and rounded once; normed =
+    norm(residual')."""
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None):  # pragma: no cover
         raise NotImplementedError

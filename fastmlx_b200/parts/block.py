@@ -27,7 +27,5 @@ class PreNormBlock(Part):
             bool(getattr(self.ffn, "supports_cuda_graph", True))
 
     def forward(self, delta, residual, ctx, cache):
-        x, residual = self.norm1.forward(delta, residual)
-        a = self.mixer.forward(x, ctx, cache)
-        y, residual = self.norm2.forward(a, residual)
-        return self.ffn.forward(y, ctx), residual
+        delta, residual = self.mixer.forward_in_block(delta, residual, self.norm1, ctx, cache)
+        return self.ffn.forward_in_block(delta, residual, self.norm2, ctx)

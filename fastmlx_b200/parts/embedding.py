@@ -51,3 +51,8 @@ class LMHead(Part):
     def forward(self, x):
         w = self.tied.weight if self.tied is not None else self.weight
         return self.rt.k.linear(x, w, None, torch.float32)
+
+    def forward_after(self, delta, residual, norm):
+        """Final norm, then logits."""
+        x, _ = norm.forward(delta, residual)
+        return self.forward(x)

@@ -92,8 +92,8 @@ class Model(Part):
             delta, residual = self.layers[run.layer].forward(delta, residual, ctx, ctx.caches[pos])
         k = self.rt.k
         if ctx.logit_rows is not None:
-            delta = k.gather_rows(delta, ctx.logit_rows, ctx.status)
+            if delta is not None:
+                delta = k.gather_rows(delta, ctx.logit_rows, ctx.status)
             if residual is not None:
                 residual = k.gather_rows(residual, ctx.logit_rows, ctx.status)
-        x, _ = self.final_norm.forward(delta, residual)
-        return self.head.forward(x)
+        return self.head.forward_after(delta, residual, self.final_norm)

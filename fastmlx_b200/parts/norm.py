@@ -22,4 +22,10 @@ class RMSNorm(Norm):
         return self.weight.numel() * 4
 
     def forward(self, x, residual):
+        if x is None:
+            x, residual = residual, None
         return self.rt.k.add_rmsnorm(x, residual, self.weight, self.eps)
+
+    def fold(self):
+        """(weight, eps) for a kernel that normalises its input rows itself."""
+        return (self.weight, self.eps)

@@ -184,6 +184,47 @@ def test_skinny_gemm(M, N, K, out_dtype):
     assert int(k().skinny_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
 
 
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(64, 64), (3072, 2048), (2048, 8192), (144, 200), (256, 72)])
+def test_skinny_fused_norm_and_residual(M, N, K):
+    """Norm folded into the product, residual folded into its epilogue (in place), against the
+    unfused chain with its roundings."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=41, scale=2.0)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=42, scale=0.05)
+    nw = 1 + rnd(K, seed=43, scale=0.1)
+    res = rnd(M, N, dtype=torch.bfloat16, seed=44)
+    normed, _ = plain_ops.add_rmsnorm(x.clone(), None, nw, 1e-5)
+    ref = plain_ops.linear(normed, w, None, torch.float64)
+    for splits in (None, 1, 3):
+        got = k().skinny_fused(x.to(DEV), w.to(DEV), norm=(nw.to(DEV), 1e-5), splits=splits)
+        close(got, ref, torch.bfloat16, "norm prologue", extra=2.0 ** -8 * ref.abs().max().item())
+        got32 = k().skinny_fused(x.to(DEV), w.to(DEV), torch.float32, norm=(nw.to(DEV), 1e-5), splits=splits)
+        close(got32.bfloat16(), ref, torch.bfloat16, "norm prologue, float out", extra=2.0 ** -8 * ref.abs().max().item())
+        stream = res.clone().to(DEV)
+        out = k().skinny_fused(x.to(DEV), w.to(DEV), residual=stream, out=stream, splits=splits)
+        assert out.data_ptr() == stream.data_ptr()
+        want = plain_ops.linear(x, w, None, torch.bfloat16).double() + res.double()
+        close(stream, want, torch.bfloat16, "residual epilogue", extra=2.0 ** -8 * want.abs().max().item())
+    assert int(k().skinny_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("M", [1, 8])
+@pytest.mark.parametrize("I,K,blk", [(128, 64, 128), (8192, 2048, 128), (384, 200, 128), (64, 72, 32)])
+def test_skinny_fused_gate_up(M, I, K, blk):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=51, scale=2.0)
+    wg, wu = rnd(I, K, dtype=torch.bfloat16, seed=52, scale=0.1), rnd(I, K, dtype=torch.bfloat16, seed=53, scale=0.1)
+    w = torch.stack([wg.view(-1, blk, K), wu.view(-1, blk, K)], dim=1).reshape(2 * I, K).contiguous()
+    nw = 1 + rnd(K, seed=54, scale=0.1)
+    normed, _ = plain_ops.add_rmsnorm(x.clone(), None, nw, 1e-6)
+    g = plain_ops.linear(normed, wg, None, torch.bfloat16)
+    u = plain_ops.linear(normed, wu, None, torch.bfloat16)
+    ref = plain_ops.silu_mul(torch.cat([g, u], dim=1))
+    for splits in (None, 1, 2):
+        got = k().skinny_fused(x.to(DEV), w.to(DEV), norm=(nw.to(DEV), 1e-6), block=blk, splits=splits)
+        assert got.shape == (M, I)
+        close(got, ref, torch.bfloat16, "gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
+
+
 @pytest.mark.parametrize("ta,tw,tc", [(torch.bfloat16, torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32, torch.float32),
                                       (torch.bfloat16, torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16)])
 def test_gemm_simple_mixed_types(ta, tw, tc):
