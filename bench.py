@@ -153,12 +153,13 @@ def fill(engine, batch: int, prompt_len: int, vocab: int, seed: int) -> list[str
     from fastmlx_b200 import SamplingParams
     sp = SamplingParams(max_tokens=1 << 20, temperature=0.0, ignore_eos=True)
     ids = [engine.submit(rand_prompt(prompt_len, vocab, seed + i), sp) for i in range(batch)]
-    while any(r.num_computed < len(r.prompt_token_ids) for r in engine._requests.values()):
+    while any(r.num_computed < len(r.prompt_token_ids) or not r.output_token_ids for r in engine._requests.values()):
         engine.step()
     return ids
 
 
 def drain(engine, ids) -> None:
+    engine.flush()
     for rid in ids:
         engine.abort(rid)
     while engine.has_unfinished():
@@ -174,6 +175,7 @@ def device_decode(engine, steps: int, warmup: int, sampler: ClockSampler | None 
     kernels in one region)."""
     import torch
     from fastmlx_b200.engine.batch import StepEntry
+    engine.flush()
     reqs = list(engine.scheduler.running)
     fn = engine.step_fn
 

@@ -36,6 +36,7 @@ class EngineConfig:
     prefill_chunk: int = 0
     seed: int = 0
     cuda_graphs: bool = True
+    lookahead: bool = True                    # run one decode step ahead of the host
     device: str = "cuda"
 
 
@@ -85,6 +86,9 @@ class Engine:
         self._ids = itertools.count()
         self._pending_outputs: list[RequestOutput] = []
         self._host_out = None
+        self._side = None
+        self._ahead = None                      # a step launched whose ids have not been read yet
+        self.lookahead = bool(ec.lookahead) and self.rt.device.type == "cuda"
         self._requests: dict[str, Request] = {}
         self.counters = {"steps": 0, "prompt_tokens": 0, "generated_tokens": 0, "preemptions": 0, "h2d_bytes": 0,
                          "d2h_bytes": 0}
@@ -108,11 +112,21 @@ class Engine:
         self.scheduler.abort(request_id)
 
     def has_unfinished(self) -> bool:
-        return bool(self._pending_outputs) or self.scheduler.has_unfinished()
+        return bool(self._pending_outputs) or self._ahead is not None or self.scheduler.has_unfinished()
 
     # ------------------------------------------------------------------ one iteration
     def step(self) -> list[RequestOutput]:
+        """Advance by one model step and report what is known by then.  In steady decoding the
+        engine runs one step ahead of the host: it launches step N+1 (whose token ids are
+        copied on the device from step N's samples) before it waits for step N's ids, so the
+        host's book-keeping hides behind the device's work.  The outputs of a step then come
+        back one call later; the tokens are the same."""
         outs, self._pending_outputs = self._pending_outputs, []
+        if self._ahead is not None:
+            prev = self._ahead
+            self._ahead = self._launch_ahead(prev)
+            outs.extend(self._finish(prev))
+            return outs
         if not self.scheduler.has_unfinished():
             return outs
         plan = self.scheduler.schedule()
@@ -122,25 +136,77 @@ class Engine:
         self.counters["preemptions"] = self.scheduler.num_preemptions
         if not plan.entries:
             return outs
+        launched = self._launch(plan, None, outs)
+        if launched is None:
+            return outs
+        if self.lookahead and self.step_fn.graphable(plan.entries) and all(plan.samples):
+            self._ahead = launched                       # its outputs come with the next call
+        else:
+            outs.extend(self._finish(launched))
+        return outs
+
+    def flush(self) -> list[RequestOutput]:
+        """Wait for the step that is still in flight, if any, and report it."""
+        outs, self._pending_outputs = self._pending_outputs, []
+        if self._ahead is not None:
+            prev, self._ahead = self._ahead, None
+            outs.extend(self._finish(prev))
+        return outs
+
+    def _launch(self, plan, tokens_from, outs):
+        """Put a planned step on the device.  -> (plan, sampled ids on the device, readiness
+        event) or None after reporting a failure."""
         try:
-            logits = self.step_fn.run(plan.entries, reserved=True, check=False)
-            rows = [(req.sampling, req.seed, len(req.output_token_ids), req.tail(req.sampling.history_needed))
+            logits = self.step_fn.run(plan.entries, reserved=True, check=False, tokens_from=tokens_from)
+            ahead = 1 if tokens_from is not None else 0
+            rows = [(req.sampling, req.seed, len(req.output_token_ids) + ahead,
+                     req.tail(req.sampling.history_needed) if not ahead else [])
                     for req, s in zip(plan.requests, plan.samples) if s]
-            tokens = self._read_back(self.sampler.sample(logits, rows)) if rows else []
-            if not rows:
+            sampled = self.sampler.sample(logits, rows) if rows else None
+        except (StepError, RuntimeError) as e:
+            outs.extend(self.scheduler.step_failed(plan, str(e)))
+            for req in plan.requests:
+                self._requests.pop(req.request_id, None)
+            return None
+        ready = None
+        if self.rt.device.type == "cuda":
+            ready = torch.cuda.Event()
+            ready.record()
+        for req, entry in zip(plan.requests, plan.entries):
+            n_prompt = len(req.prompt_token_ids)
+            self.counters["prompt_tokens"] += max(0, min(n_prompt, req.num_computed + len(entry.tokens))
+                                                  - min(n_prompt, req.num_computed))
+        self.scheduler.step_launched(plan)
+        self.counters["steps"] += 1
+        self.counters["h2d_bytes"] += self.step_fn.last_h2d_bytes
+        return plan, sampled, ready
+
+    def _launch_ahead(self, prev):
+        plan = self.scheduler.plan_ahead(prev[0]) if self.lookahead else None
+        if plan is None:
+            return None
+        outs: list[RequestOutput] = []
+        launched = self._launch(plan, prev[1], outs)
+        self._pending_outputs.extend(outs)
+        return launched
+
+    def _finish(self, launched) -> list[RequestOutput]:
+        """Wait for a launched step's ids and let the scheduler digest them."""
+        plan, sampled, ready = launched
+        outs: list[RequestOutput] = []
+        try:
+            tokens = self._read_back(sampled, ready) if sampled is not None else []
+            if sampled is None:
                 self.step_fn.check_status()
         except (StepError, RuntimeError) as e:
             outs.extend(self.scheduler.step_failed(plan, str(e)))
             for req in plan.requests:
                 self._requests.pop(req.request_id, None)
+            if self._ahead is not None:                  # what was launched on top of it is void too
+                outs.extend(self.scheduler.step_failed(self._ahead[0], str(e)))
+                self._ahead = None
             return outs
-        self.counters["steps"] += 1
-        self.counters["h2d_bytes"] += self.step_fn.last_h2d_bytes
         self.counters["d2h_bytes"] += 4 * len(tokens) + 16
-        for req, entry, s in zip(plan.requests, plan.entries, plan.samples):
-            done_before = req.num_computed
-            n_prompt = len(req.prompt_token_ids)
-            self.counters["prompt_tokens"] += max(0, min(n_prompt, done_before + len(entry.tokens)) - min(n_prompt, done_before))
         self.counters["generated_tokens"] += len(tokens)
         for out in self.scheduler.step_done(plan, tokens):
             outs.append(out)
@@ -148,20 +214,27 @@ class Engine:
                 self._requests.pop(out.request_id, None)
         return outs
 
-    def _read_back(self, sampled: torch.Tensor) -> list[int]:
+    def _read_back(self, sampled: torch.Tensor, ready=None) -> list[int]:
         """Sampled ids and the kernels' status word in one wait: two small copies into pinned
-        memory, one synchronisation."""
+        memory on a side stream that waits only for the step that made them (a later step may
+        already be running on the main stream), one synchronisation."""
         n = sampled.numel()
         if self.rt.device.type != "cuda":
             self.step_fn.check_status()
             return sampled.tolist()
         if self._host_out is None or self._host_out.numel() < n + 4:
             self._host_out = torch.empty(max(n + 4, 260), dtype=torch.int32).pin_memory()
-        self._host_out[:n].copy_(sampled, non_blocking=True)
-        self._host_out[n:n + 4].copy_(self.step_fn.status, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.rt.device)
+        with torch.cuda.stream(self._side):
+            if ready is not None:
+                self._side.wait_event(ready)
+            self._host_out[:n].copy_(sampled, non_blocking=True)
+            self._host_out[n:n + 4].copy_(self.step_fn.status, non_blocking=True)
+        self._side.synchronize()
         vals = self._host_out[:n + 4].tolist()
         if vals[n]:
+            torch.cuda.current_stream().synchronize()
             self.step_fn.check_status()          # raises with the code's meaning and clears the word
         return vals[:n]
 

@@ -45,6 +45,7 @@ class Plan:
     samples: list[bool] = field(default_factory=list)          # does this entry yield a token?
     preempted: list[Request] = field(default_factory=list)
     finished: list[Request] = field(default_factory=list)      # ended while planning (errors, aborts)
+    launched: bool = False                                     # its tokens are committed to the cache
 
     @property
     def num_tokens(self) -> int:
@@ -216,7 +217,8 @@ class Scheduler:
         if req.cache is not None:
             if req.cache.reserved:
                 self.manager.rollback(req.cache)
-            self.manager.free(req.request_id)
+            if req.request_id in self.manager.requests:
+                self.manager.free(req.request_id)
             req.cache = None
         req.status = status
         if req in self.running:
@@ -241,22 +243,36 @@ class Scheduler:
         (scheduler/scheduler.go:139-145,294-307); the pages they took go back."""
         outs = []
         for req in plan.requests:
+            if req.status.finished:
+                continue
             req.error = message
             self._finish(req, RequestStatus.FINISHED_ERROR)
             outs.append(self._output(req, []))
         return outs
 
+    def step_launched(self, plan: Plan) -> None:
+        """The step is on its way: its tokens count as in the cache (the pages are committed).
+        What the tokens *are* is not needed for this, so an engine that runs one step ahead
+        calls it before the sampled ids have come back."""
+        for entry, req in zip(plan.entries, plan.requests):
+            self.manager.commit(req.cache)
+            req.num_computed += len(entry.tokens)
+        plan.launched = True
+
     def step_done(self, plan: Plan, tokens: list[int]) -> list[RequestOutput]:
-        """Commit the step: `tokens` holds one sampled id per entry with samples=True, in
-        order.  -> the increments to report."""
+        """The step ran: `tokens` holds one sampled id per entry with samples=True, in order.
+        -> the increments to report.  A request that ended while this step was already in
+        flight (one step ahead) is skipped: its token is dropped."""
+        if not plan.launched:
+            self.step_launched(plan)
         outs = []
         it = iter(tokens)
         for entry, req, sample in zip(plan.entries, plan.requests, plan.samples):
-            self.manager.commit(req.cache)
-            req.num_computed += len(entry.tokens)
             if not sample:
                 continue
             tok = int(next(it))
+            if req.status.finished:
+                continue
             req.output_token_ids.append(tok)
             req.status = RequestStatus.RUNNING
             sp = req.sampling
@@ -268,6 +284,36 @@ class Scheduler:
                 self._finish(req, RequestStatus.FINISHED_LENGTH)
             outs.append(self._output(req, [tok]))
         return outs
+
+    def plan_ahead(self, prev: Plan) -> Plan | None:
+        """The step after `prev`, planned before prev's sampled ids are known: possible when
+        prev gave every running request one token, nothing waits, nothing is to be aborted and
+        no request can end by length at prev.  Every request gets a place-holder token (the
+        engine copies the sampled id in on the device).  None when it cannot be done."""
+        if self.waiting or self._aborts or not prev.entries or len(prev.requests) != len(self.running):
+            return None
+        for entry, req, sample in zip(prev.entries, prev.requests, prev.samples):
+            if len(entry.tokens) != 1 or not sample or req.status.finished or req.cache is None:
+                return None
+            if len(req.output_token_ids) + 2 > req.sampling.max_tokens or req.sampling.penalties_on:
+                return None
+            if self.max_positions and req.num_tokens + 2 >= self.max_positions:
+                return None
+        plan = Plan()
+        taken = []
+        try:
+            for req in prev.requests:
+                self.manager.reserve(req.cache, 1)
+                taken.append(req)
+        except OutOfPages:
+            for req in taken:
+                self.manager.rollback(req.cache)
+            return None
+        for req in prev.requests:
+            plan.entries.append(StepEntry(req.cache, [0], [0]))
+            plan.requests.append(req)
+            plan.samples.append(True)
+        return plan
 
     def _output(self, req: Request, new) -> RequestOutput:
         return RequestOutput(req.request_id, list(new), list(req.output_token_ids), req.status.finished,

@@ -69,8 +69,12 @@ class _DecodeGraph:
         ctx.max_q_len = 1
         return ctx
 
-    def run(self, fn, entries) -> tuple[torch.Tensor, StepContext]:
+    def run(self, fn, entries, tokens_from=None) -> tuple[torch.Tensor, StepContext]:
         ctx = self._context(fn, entries)
+        if tokens_from is not None:
+            # the ids sampled by the step before, still on the device: the token ids are the
+            # first array of the packed buffer
+            self.static.dev[:tokens_from.numel()].copy_(tokens_from)
         self.graph.replay()
         return self.logits, ctx
 
@@ -106,12 +110,15 @@ class StepFunction:
             if hasattr(k, "skinny_workspace"):
                 k.skinny_workspace(rt.device)
 
-    def run(self, entries: list[StepEntry], reserved: bool = False, check: bool = True) -> torch.Tensor:
+    def run(self, entries: list[StepEntry], reserved: bool = False, check: bool = True,
+            tokens_from: torch.Tensor | None = None) -> torch.Tensor:
         """-> float32 logits [sum(len(e.want)), vocab] on the device, in the order of the
         entries and of their `want`.  `reserved`: the caller (the scheduler) has taken the
         pages already and commits or rolls back itself.  `check=False` leaves the read of
         the kernels' status word to the caller, who reads results from the device anyway.
-        The tensor may be a view of a graph's output: use it before the next step."""
+        The tensor may be a view of a graph's output: use it before the next step.
+        `tokens_from` (one token per entry): take the ids from this device tensor instead of
+        from the entries, whose tokens are then place-holders."""
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -130,7 +137,7 @@ class StepFunction:
                 for e in entries:
                     self.manager.reserve(e.request, len(e.tokens))
                     taken.append(e.request)
-            logits, ctx = self._forward(entries)
+            logits, ctx = self._forward(entries, tokens_from)
             if check:
                 self.check_status()
         except BaseException:
@@ -145,7 +152,12 @@ class StepFunction:
         self.last_ctx = ctx
         return logits
 
-    def _forward(self, entries):
+    def graphable(self, entries) -> bool:
+        return self.cuda_graphs and len(entries) <= self.max_graph_rows and all(len(e.tokens) == 1 for e in entries)
+
+    def _forward(self, entries, tokens_from=None):
+        if tokens_from is not None and not self.graphable(entries):
+            raise StepError("ids can be fed from the device only into a captured decode step")
         if self.cuda_graphs and len(entries) <= self.max_graph_rows and all(len(e.tokens) == 1 for e in entries):
             ps = self.manager.page_size
             rows = _pow2_at_least(len(entries))
@@ -155,7 +167,7 @@ class StepFunction:
             g = self.graphs.get(key)
             if g is None:
                 g = self.graphs[key] = _DecodeGraph(self, rows, width, entries)
-            logits, ctx = g.run(self, entries)
+            logits, ctx = g.run(self, entries, tokens_from)
             self.graph_replays += 1
             self.graph_kernel_launches += g.kernel_launches
             # one wanted place per row in the graph; give back what was asked for

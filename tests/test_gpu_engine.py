@@ -198,3 +198,43 @@ def test_real_layer_sizes_bfloat16_against_32_bit(tmp_path):
             got = outs["bfloat16"][rid][pos]
             worst = max(worst, float(np.abs(got - ref).max() / np.abs(ref).max()))
     assert worst < 3e-2, worst
+
+
+def test_running_one_step_ahead_changes_no_token(dirs):
+    """The engine launches a decode step before it has read the ids of the one before (they
+    are fed on the device).  Tokens, finish reasons and counts must be those of the engine
+    that waits every step: with temperature sampling, with a request that stops on a token in
+    mid-flight (its look-ahead step is thrown away), with one that ends by length, and with
+    requests that arrive while others decode."""
+    from fastmlx_b200 import Engine, SamplingParams
+    cfg = tiny.TINY_B
+    prompts = [tiny.rand_tokens(n, cfg["vocab_size"], 300 + n) for n in (5, 33, 70, 12)]
+
+    def run(lookahead, stop_on=None):
+        eng = Engine(dirs["B"], dtype="float32", block_size=16, max_cache_tokens=2048, max_concurrent_requests=4,
+                     lookahead=lookahead)
+        sps = [SamplingParams(max_tokens=30, temperature=0.8, seed=7),
+               SamplingParams(max_tokens=40, temperature=0.0, stop_token_ids=[stop_on] if stop_on is not None else []),
+               SamplingParams(max_tokens=9, temperature=1.0, top_p=0.9, seed=9),
+               SamplingParams(max_tokens=25, temperature=0.0)]
+        ids = [eng.submit(p, sp) for p, sp in zip(prompts[:3], sps[:3])]
+        final, steps = {}, 0
+        while eng.has_unfinished():
+            steps += 1
+            if steps == 6:
+                ids.append(eng.submit(prompts[3], sps[3]))          # arrives while the others decode
+            for o in eng.step():
+                if o.finished:
+                    final[o.request_id] = o
+        assert eng.stats()["pages_used"] == 0
+        eng.manager.check()
+        return [(final[i].output_token_ids, final[i].finish_reason) for i in ids], eng.stats()
+
+    base, st0 = run(False)
+    stop_token = base[1][0][10]                                     # greedy request: stop it in mid-flight
+    want, _ = run(False, stop_token)
+    got, st1 = run(True, stop_token)
+    assert got == want
+    assert want[1][1] == "stop" and want[0][1] == "length" and want[2][1] == "length"
+    assert st1["graph_replays"] > 0
+    assert run(True)[0] == base
