@@ -63,6 +63,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the special-function unit (about two units in the last place; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -206,12 +212,12 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
     mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 2));
     const float m_new = fmaxf(m[x], mx[x]);
     const float m_use = m_new == -INFINITY ? 0.f : m_new;
-    alpha[x] = exp2f(m[x] - m_use);
+    alpha[x] = fast_exp2(m[x] - m_use);
     m[x] = m_new;
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
-      const float p0 = exp2f(s[j][2 * x] - m_use), p1 = exp2f(s[j][2 * x + 1] - m_use);
+      const float p0 = fast_exp2(s[j][2 * x] - m_use), p1 = fast_exp2(s[j][2 * x + 1] - m_use);
       s[j][2 * x] = p0;
       s[j][2 * x + 1] = p1;
       sum += p0 + p1;
@@ -228,7 +234,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
                     long long num_pages, float scale, int window, int* status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-  const int r = blockIdx.z, g = blockIdx.y, tile = blockIdx.x;
+  // the last query tiles of a row see the most keys: they start first
+  const int r = blockIdx.z, g = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
   const int rep = nh / nkv;
   const int t0 = row_start[r], q_len = row_start[r + 1] - t0, ctx = row_ctx[r];
   const int n_packed = q_len * rep;

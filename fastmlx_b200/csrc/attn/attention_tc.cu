@@ -1,0 +1,495 @@
+// Paged causal attention for prompt portions on the fifth-generation tensor cores
+// (head sizes 64 and 128; compile with -DFMX_HD=<head size>).
+//
+// A CTA owns 128 packed query rows of one request and one kv head (row i = token i / rep,
+// query head g*rep + i % rep) and walks over the keys in tiles of 128.
+//   warp 0, one lane : producer.  One 3-D TMA load brings the query tile; per key tile, one
+//                      2-D TMA load per page brings K and one brings V (a page of a kv head is
+//                      a contiguous [page_size, hd] block of the cache), all with the 128-byte
+//                      swizzle the MMA expects.  Pages beyond the last visible key are replaced
+//                      by an out-of-bounds box, which TMA fills with zeros.
+//   warp 1, one lane : MMA issuer.  S_j = Q K_j^T (tcgen05.mma, both operands K-major) into one
+//                      of two score buffers in tensor memory, then, one tile behind, O_j = P_j V_j
+//                      (P from shared memory, V as an MN-major operand) into one of two output
+//                      buffers: the tensor core computes S_{j+1} while the softmax of tile j runs.
+//   warps 2-5        : softmax and epilogue, one thread per query row.  Scores come from tensor
+//                      memory (tcgen05.ld), running maximum and sum are 32-bit, probabilities go
+//                      to shared memory in bfloat16, the per-tile outputs are rescaled and summed
+//                      in registers.
+// Every barrier wait is bounded by time; a wait that runs out leaves FMX_WAIT_EXPIRED in the
+// status word and the CTA frees its tensor memory and returns.  No cluster, no multicast.
+#include <cuda.h>
+#include <math.h>
+#include "common.cuh"
+
+#ifndef FMX_HD
+#error "compile with -DFMX_HD=<head size>"
+#endif
+
+#if FMX_HD == 64 || FMX_HD == 128
+namespace {
+constexpr int HD = FMX_HD;
+constexpr int KB = HD / 64;                    // 64-wide blocks of the head dimension
+constexpr int BM = 128, BN = 128;
+constexpr int TILE_BYTES = 128 * 128;          // a [128 x 64] bfloat16 block, 128-byte rows
+constexpr int KV_STAGES = HD == 64 ? 3 : 2;
+constexpr int P_BUFS = HD == 64 ? 2 : 1;
+constexpr int Q_BYTES = KB * TILE_BYTES, K_BYTES = KB * TILE_BYTES, V_BYTES = KB * TILE_BYTES;
+constexpr int P_BYTES = 2 * TILE_BYTES;        // 128 rows x 128 keys
+constexpr int THREADS = 320;                  // producer, MMA issuer, eight softmax warps
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int TMEM_COLS = 512;
+constexpr int S_COL = 0, O_COL = 256;          // S0, S1 at 0, 128; O0, O1 at 256, 256 + HD
+constexpr long long WAIT_CYCLES = 2000000000LL;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + (size_t)KV_STAGES * (K_BYTES + V_BYTES) + (size_t)P_BUFS * P_BYTES +
+                              1024 + 512 + 2 * 2 * 128 * 4;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if (clock64() - t0 > WAIT_CYCLES) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+// K-major operand, rows of 128 bytes, 128-byte swizzle (see tc/gemm_tcgen05.cu).
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// MN-major operand (V: keys down, head dimension across and contiguous): 64 elements of the
+// head dimension are one 128-byte row, eight key rows one swizzle atom; the leading byte offset
+// steps to the next 64 elements of the head dimension, the stride byte offset to the next
+// eight keys.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo_bytes) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint32_t idesc_f16(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 2^x by the special-function unit (about two units in the last place; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct Bars {
+  uint64_t q_full;
+  uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
+  uint64_t s_full[2], s_empty[2];
+  uint64_t p_full[P_BUFS], p_empty[P_BUFS];
+  uint64_t o_full[2], o_empty[2];
+  uint64_t x_bar[2];                           // the two column halves meet here (256 arrivals)
+  uint32_t tmem_slot;
+  float xmax[2][2][128];                       // [tile parity][column half][row]: the halves' maxima
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                       const int* block_tables, int bt_stride, const int* row_start, const int* row_ctx, bf16* out,
+                       int nh, int nkv, int page_size, long long num_pages, long long kv_rows, float scale,
+                       int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sq = smem;
+  unsigned char* skv = sq + Q_BYTES;                                   // [stage][K | V]
+  unsigned char* sp = skv + (size_t)KV_STAGES * (K_BYTES + V_BYTES);   // [P_BUFS]
+  Bars* bars = reinterpret_cast<Bars*>(sp + (size_t)P_BUFS * P_BYTES);
+
+  // the last query tiles of a row see the most keys: they start first
+  const int r = blockIdx.z, g = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+  const int rep = nh / nkv;
+  const int tok_per_tile = BM / rep;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bars->q_full), 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(smem_u32(&bars->kv_full[s]), 1);
+      mbar_init(smem_u32(&bars->kv_empty[s]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars->s_full[i]), 1);
+      mbar_init(smem_u32(&bars->s_empty[i]), SOFTMAX_THREADS);
+      mbar_init(smem_u32(&bars->o_full[i]), 1);
+      mbar_init(smem_u32(&bars->o_empty[i]), SOFTMAX_THREADS);
+    }
+    for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&bars->x_bar[i]), SOFTMAX_THREADS);
+    for (int i = 0; i < P_BUFS; ++i) {
+      mbar_init(smem_u32(&bars->p_full[i]), SOFTMAX_THREADS);
+      mbar_init(smem_u32(&bars->p_empty[i]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_slot;
+  pdl_trigger();
+  pdl_wait();
+
+  const int t0 = row_start[r], q_len = row_start[r + 1] - t0, ctx = row_ctx[r];
+  const int tok0 = tile * tok_per_tile;                   // first token of this tile within the row
+  const bool active = tok0 < q_len && ctx >= 0;
+  const int n_tok = active ? min(tok_per_tile, q_len - tok0) : 0;
+  const int kend = ctx + tok0 + n_tok;                    // one past the last key any row of the tile sees
+  const int n_tiles = active ? (kend + BN - 1) / BN : 0;
+  const int pages_per_tile = BN / page_size;
+
+  if (warp == 0 && lane == 0 && active) {
+    // ------------------------------------------------------------------ producer
+    const int* bt = block_tables + (long long)r * bt_stride;
+    mbar_expect_tx(smem_u32(&bars->q_full), Q_BYTES);
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb)
+      tma_load_3d(smem_u32(sq + kb * TILE_BYTES), &map_q, kb * 64, g * rep, t0 + tok0, smem_u32(&bars->q_full));
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1)) { ok = false; break; }
+      const uint32_t fb = smem_u32(&bars->kv_full[stage]);
+      unsigned char* sk = skv + (size_t)stage * (K_BYTES + V_BYTES);
+      unsigned char* sv = sk + K_BYTES;
+      mbar_expect_tx(fb, K_BYTES + V_BYTES);
+      for (int pi = 0; pi < pages_per_tile; ++pi) {
+        const int key0 = j * BN + pi * page_size;
+        long long krow = kv_rows, vrow = kv_rows;           // out of bounds: the box reads as zeros
+        if (key0 < kend) {
+          const int blk = key0 / page_size;
+          const int page = blk < bt_stride ? bt[blk] : -1;
+          if (page < 0 || page >= num_pages) {
+            fmx_set_status(status, FMX_BAD_PAGE, page, r);
+          } else {
+            krow = (((long long)page * 2 + 0) * nkv + g) * page_size;
+            vrow = (((long long)page * 2 + 1) * nkv + g) * page_size;
+          }
+        }
+        const int off = pi * page_size * 128;               // rows of 128 bytes
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_2d(smem_u32(sk + kb * TILE_BYTES + off), &map_kv, kb * 64, (int)krow, fb);
+          tma_load_2d(smem_u32(sv + kb * TILE_BYTES + off), &map_kv, kb * 64, (int)vrow, fb);
+        }
+      }
+      if (++stage == KV_STAGES) { stage = 0; phase ^= 1; }
+    }
+    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 11, blockIdx.x);
+  } else if (warp == 1 && lane == 0 && active) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc_qk = idesc_f16(BM, BN, 0), idesc_pv = idesc_f16(BM, HD, 1);
+    bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
+    tc_fence_after();
+    auto issue_pv = [&](int j) -> bool {
+      const int st = j % KV_STAGES, pb = j % P_BUFS, ob = j & 1;
+      if (!mbar_wait(smem_u32(&bars->p_full[pb]), (uint32_t)((j / P_BUFS) & 1))) return false;
+      if (!mbar_wait(smem_u32(&bars->o_empty[ob]), (uint32_t)(((j >> 1) & 1) ^ 1))) return false;
+      tc_fence_after();
+      const uint32_t pa = smem_u32(sp + (size_t)pb * P_BYTES);
+      const uint32_t va = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES) + K_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb)          // 64 keys each
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)        // 16 keys each
+          umma(tmem + O_COL + ob * HD, desc_kmajor(pa + kb * TILE_BYTES) + 2 * k4,
+               desc_mnmajor(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (kb | k4) ? 1u : 0u);
+      umma_commit(smem_u32(&bars->o_full[ob]));
+      umma_commit(smem_u32(&bars->p_empty[pb]));
+      umma_commit(smem_u32(&bars->kv_empty[st]));
+      return true;
+    };
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j % KV_STAGES, sb = j & 1;
+      if (!mbar_wait(smem_u32(&bars->kv_full[st]), (uint32_t)((j / KV_STAGES) & 1))) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&bars->s_empty[sb]), (uint32_t)(((j >> 1) & 1) ^ 1))) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t qa = smem_u32(sq), ka = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES));
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+          umma(tmem + S_COL + sb * BN, desc_kmajor(qa + kb * TILE_BYTES) + 2 * k4,
+               desc_kmajor(ka + kb * TILE_BYTES) + 2 * k4, idesc_qk, (kb | k4) ? 1u : 0u);
+      umma_commit(smem_u32(&bars->s_full[sb]));
+      if (j > 0) ok = issue_pv(j - 1);
+    }
+    if (ok && n_tiles > 0) ok = issue_pv(n_tiles - 1);
+    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 12, blockIdx.x);
+  } else if (warp >= 2 && active) {
+    // ------------------------------------------------------------------ softmax and epilogue
+    // Two threads per query row: warps 2-5 take the first 64 keys of every tile and the first
+    // half of the head dimension of the output, warps 6-9 the second halves.
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;                 // this thread's packed row and tensor-memory lane
+    const int tok = row / rep, head = g * rep + row - tok * rep;
+    const bool rvalid = tok < n_tok;
+    const int lim = rvalid ? ctx + tok0 + tok : -1;      // last key this row sees
+    const float sl2 = scale * LOG2E;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    constexpr int OH = HD / 2;                           // output columns of this thread
+    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    float o[OH];
+#pragma unroll
+    for (int d = 0; d < OH; ++d) o[d] = 0.f;
+    bool ok = true;
+
+    auto take_output = [&](int j, float alpha) -> bool {   // o = o * alpha + (P_j V_j)[row, this half]
+      const int ob = j & 1;
+      if (!mbar_wait(smem_u32(&bars->o_full[ob]), (uint32_t)((j >> 1) & 1))) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < OH; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + O_COL + ob * HD + half * OH + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, __uint_as_float(v[i]));
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars->o_empty[ob]));
+      return true;
+    };
+
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int sb = j & 1, pb = j % P_BUFS, st = j % KV_STAGES;
+      if (!mbar_wait(smem_u32(&bars->s_full[sb]), (uint32_t)((j >> 1) & 1))) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = j * BN + half * 64;               // first key of this thread's 64 columns
+      const bool need_mask = j * BN + BN - 1 > ctx + tok0;  // some row of the tile does not see the whole tile
+      uint32_t v0[32], v1[32];
+      tmem_ld32(lane_addr + S_COL + sb * BN + half * 64, v0);
+      tmem_ld32(lane_addr + S_COL + sb * BN + half * 64 + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars->s_empty[sb]));         // the scores are in registers now
+      float sc[64];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        sc[i] = (!need_mask || key0 + i <= lim) ? __uint_as_float(v0[i]) * sl2 : -INFINITY;
+        sc[32 + i] = (!need_mask || key0 + 32 + i <= lim) ? __uint_as_float(v1[i]) * sl2 : -INFINITY;
+        mx = fmaxf(mx, fmaxf(sc[i], sc[32 + i]));
+      }
+      // the row's maximum over the whole tile: exchange with the thread that has the other half
+      bars->xmax[j & 1][half][row] = mx;
+      mbar_arrive(smem_u32(&bars->x_bar[j & 1]));
+      if (!mbar_wait(smem_u32(&bars->x_bar[j & 1]), (uint32_t)((j >> 1) & 1))) { ok = false; break; }
+      mx = fmaxf(mx, bars->xmax[j & 1][half ^ 1][row]);
+      const float m_new = fmaxf(m, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = fast_exp2(m - m_use);
+      m = m_new;
+      if (!mbar_wait(smem_u32(&bars->p_empty[pb]), (uint32_t)(((j / P_BUFS) & 1) ^ 1))) { ok = false; break; }
+      // probabilities to shared memory (K-major, 128-byte rows, swizzled by row): this thread's
+      // 64 keys are the k block `half` of the tile
+      unsigned char* prow = sp + (size_t)pb * P_BYTES + half * TILE_BYTES + row * 128;
+      float sum = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        float pr[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          pr[i] = fast_exp2(sc[8 * ch + i] - m_use);
+          sum += pr[i];
+        }
+        uint4 w;
+        w.x = pack2(pr[0], pr[1]);
+        w.y = pack2(pr[2], pr[3]);
+        w.z = pack2(pr[4], pr[5]);
+        w.w = pack2(pr[6], pr[7]);
+        *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = w;
+      }
+      l = l * alpha + sum;
+      if (j * BN + BN > kend && half == 0) {
+        // keys past the last visible one share pages with stale rows: their values must be
+        // zeros, since 0 * NaN would poison the product
+        if (!mbar_wait(smem_u32(&bars->kv_full[st]), (uint32_t)((j / KV_STAGES) & 1))) { ok = false; break; }
+        unsigned char* sv = skv + (size_t)st * (K_BYTES + V_BYTES) + K_BYTES;
+        if (j * BN + row >= kend) {
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              *reinterpret_cast<uint4*>(sv + kb * TILE_BYTES + row * 128 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(smem_u32(&bars->p_full[pb]));
+      // one tile behind: add the previous tile's output
+      if (j > 0) ok = take_output(j - 1, alpha_prev);
+      alpha_prev = alpha;
+    }
+    if (ok && n_tiles > 0) ok = take_output(n_tiles - 1, alpha_prev);
+    // the row's sum: both halves saw the same maxima, so their sums just add
+    if (ok) {
+      // tile n_tiles uses the exchange buffers of that parity: nobody reads them any more
+      const int jx = n_tiles;
+      bars->xmax[jx & 1][half][row] = l;
+      mbar_arrive(smem_u32(&bars->x_bar[jx & 1]));
+      ok = mbar_wait(smem_u32(&bars->x_bar[jx & 1]), (uint32_t)((jx >> 1) & 1));
+      l += bars->xmax[jx & 1][half ^ 1][row];
+    }
+    if (!ok) {
+      if (lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 13, blockIdx.x);
+    } else if (rvalid) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      bf16* op = out + ((long long)(t0 + tok0 + tok) * nh + head) * HD + half * OH;
+#pragma unroll
+      for (int c = 0; c < OH; c += 8) {
+        uint4 w;
+        w.x = pack2(o[c] * inv, o[c + 1] * inv);
+        w.y = pack2(o[c + 2] * inv, o[c + 3] * inv);
+        w.z = pack2(o[c + 4] * inv, o[c + 5] * inv);
+        w.w = pack2(o[c + 6] * inv, o[c + 7] * inv);
+        *reinterpret_cast<uint4*>(op + c) = w;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+}  // namespace
+
+// 1 when this head size has the tensor-memory kernel.
+FMX_EXPORT int fmx_attn_prefill_tc_available() { return 1; }
+
+// As fmx_attn_prefill, without a window, for nh / nkv in {1, 2, 4, 8, 16} and a page size
+// that divides 128 and is at least 8.  q rows (tokens) are T; the out-of-range part of the
+// last query tile reads as zeros.
+FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, const void* kv, const int* block_tables,
+                                   int bt_stride, const int* row_start, const int* row_ctx, void* out, int rows,
+                                   int max_q_len, int nh, int nkv, int page_size, long long num_pages, float scale,
+                                   int* status, cudaStream_t stream) {
+  if (rows == 0 || max_q_len == 0) return 0;
+  if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv) return fmx_fail("fmx_attn_prefill_tc: bad sizes rows=%d nh=%d nkv=%d", rows, nh, nkv);
+  const int rep = nh / nkv;
+  if (rep > 16 || (rep & (rep - 1))) return fmx_fail("fmx_attn_prefill_tc: %d query heads per kv head is no power of two up to 16", rep);
+  if (page_size < 8 || BN % page_size) return fmx_fail("fmx_attn_prefill_tc: a page of %d tokens does not tile 128 keys", page_size);
+  if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_prefill_tc: too many rows or kv heads for one launch");
+  if (q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)kv & 15)) return fmx_fail("fmx_attn_prefill_tc: q and the cache must be 16-byte aligned");
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return fmx_fail("fmx_attn_prefill_tc: cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap map_q, map_kv;
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nh, (cuuint64_t)T};
+    const cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_stride * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)rep, (cuuint32_t)(BM / rep)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult rc = enc(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fmx_fail("fmx_attn_prefill_tc: encoding the query map failed with code %d", (int)rc);
+  }
+  const long long kv_rows = num_pages * 2 * nkv * page_size;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)kv_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult rc = enc(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(kv), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fmx_fail("fmx_attn_prefill_tc: encoding the cache map failed with code %d", (int)rc);
+  }
+  if (kv_rows >= 2147483647LL) return fmx_fail("fmx_attn_prefill_tc: the cache has too many rows for a 32-bit coordinate");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: %zu bytes of shared memory refused: %s", SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tok_per_tile = BM / rep;
+  dim3 grid((max_q_len + tok_per_tile - 1) / tok_per_tile, nkv, rows);
+  cudaError_t e = fmx_launch(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, map_q, map_kv, block_tables,
+                             bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size, num_pages, kv_rows, scale, status);
+  if (e != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+#else
+#include "common.cuh"
+FMX_EXPORT int fmx_attn_prefill_tc_available() { return 0; }
+FMX_EXPORT int fmx_attn_prefill_tc(const void*, long long, int, const void*, const int*, int, const int*, const int*, void*,
+                                   int, int, int, int, int, long long, float, int*, cudaStream_t) {
+  return fmx_fail("fmx_attn_prefill_tc: this head size has no tensor-memory attention kernel");
+}
+#endif

@@ -355,6 +355,37 @@ def paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> 
     return out
 
 
+# Which kernel attends for prompt portions: "auto" takes the tensor-memory kernel where it is
+# at least as fast as the mma.sync one (head size 128: 196 TFLOP/s both; at head size 64 the
+# softmax warps cannot keep up yet: 150 against 180), "tcgen05" and "mma" force one.
+_ATTN_CHOICE = _os.environ.get("FASTMLX_ATTN", "auto")
+TC_ATTN_MIN_TOKENS = 64
+
+
+def _use_tc_attention(hd: int) -> bool:
+    return _ATTN_CHOICE == "tcgen05" or (_ATTN_CHOICE == "auto" and hd == 128)
+
+
+def tc_attention_ok(nh: int, nkv: int, hd: int, page_size: int, window: int) -> bool:
+    """Sizes the tensor-memory attention kernel takes: head size 64 or 128, a power of two (at
+    most 16) of query heads per kv head, a page size that divides 128 (at least 8), no window."""
+    rep = nh // nkv
+    return (hd in (64, 128) and window <= 0 and rep <= 16 and rep & (rep - 1) == 0
+            and page_size >= 8 and 128 % page_size == 0)
+
+
+def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale) -> torch.Tensor:
+    """Causal attention of prompt portions on the tcgen05 tensor cores (TMA-fed, scores and
+    outputs in tensor memory)."""
+    T = qkv.shape[0]
+    out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    bt = group.block_tables
+    call(f"attn_hd{hd}", "fmx_attn_prefill_tc", qkv.data_ptr(), qkv.stride(0), T, kv.data_ptr(), bt.data_ptr(),
+         bt.stride(0), ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), out.data_ptr(), ctx.R, int(ctx.max_q_len), nh,
+         nkv, kv.shape[3], kv.shape[0], float(scale), _ptr(ctx.status), _stream())
+    return out
+
+
 def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Tensor:
     """Attention of every token of the step over the pages of its own request.
     qkv[T, >= nh*hd] holds the (rotated) queries first; -> [T, nh*hd].  bfloat16 with a head
@@ -365,6 +396,9 @@ def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Te
     if qkv.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0:
         if ctx.all_decode and nh // nkv <= 16:
             return paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
+        if _use_tc_attention(hd) and ctx.max_q_len >= TC_ATTN_MIN_TOKENS and tc_attention_ok(nh, nkv, hd, kv.shape[3], window) \
+                and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
+            return paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale)
         return paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
     return paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
 

@@ -82,11 +82,15 @@ def main(argv=None) -> int:
     elif a.kernel == "attn_prefill":
         a.ctx = a.ctx if a.ctx != 8192 else 0
         qkv, kv, ctx, grp = _attention_inputs(a, a.qlen)
-        us = _time_graph(lambda: k.paged_attention_prefill(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, 0),
-                         a.launches, a.replays)
         flops = 4 * a.nh * a.hd * a.batch * (a.qlen * a.ctx + a.qlen * (a.qlen + 1) / 2)
-        print(f"attn_prefill B={a.batch} ctx={a.ctx} qlen={a.qlen} nh={a.nh} nkv={a.nkv} hd={a.hd}: {us:.1f} us, "
-              f"{flops / us / 1e6:.0f} TFLOP/s")
+        impls = [("mma.sync", lambda: k.paged_attention_prefill(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, 0))]
+        if k.tc_attention_ok(a.nh, a.nkv, a.hd, a.page, 0):
+            impls.append(("tcgen05", lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5)))
+        for name, f in impls:
+            us = _time_graph(f, a.launches, a.replays)
+            print(f"attn_prefill {name} B={a.batch} ctx={a.ctx} qlen={a.qlen} nh={a.nh} nkv={a.nkv} hd={a.hd}: {us:.1f} us, "
+                  f"{flops / us / 1e6:.0f} TFLOP/s")
+        print("status", ctx.status.tolist())
     elif a.kernel == "gemm":
         w = torch.randn(a.N, a.K, device=DEV, dtype=torch.bfloat16) * 0.02
         x = torch.randn(a.M, a.K, device=DEV, dtype=torch.bfloat16)
