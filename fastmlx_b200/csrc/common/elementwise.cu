@@ -28,6 +28,30 @@ __global__ void gather_rows_kernel(const T* table, const int* ids, T* out,
   }
 }
 
+// A table stored in 32-bit feeding bfloat16 activations: gather and round.
+__global__ void gather_rows_f32_to_bf16_kernel(const float* table, const int* ids, bf16* out, int d, long long nrows,
+                                               int* status, int code) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const long long id = ids[t];
+  bf16* dst = out + (long long)t * d;
+  const bool bad = id < 0 || id >= nrows;
+  if (bad && threadIdx.x == 0) fmx_set_status(status, code, id, t);
+  const float* src = table + (bad ? 0 : id) * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = __float2bfloat16_rn(bad ? 0.f : src[i]);
+}
+
+FMX_EXPORT int fmx_gather_rows_f32_to_bf16(const float* table, const int* ids, void* out, int n, int d,
+                                           long long nrows, int* status, int code, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (n < 0 || d <= 0) return fmx_fail("fmx_gather_rows_f32_to_bf16: bad sizes n=%d d=%d", n, d);
+  fmx_launch(gather_rows_f32_to_bf16_kernel, dim3(n), dim3(d >= 2048 ? 256 : 128), 0, stream, table, ids, (bf16*)out, d,
+             nrows, status, code);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+
 FMX_EXPORT int fmx_gather_rows(const void* table, const int* ids, void* out, int n, int d, long long nrows,
                                int dtype, int* status, int code, cudaStream_t stream) {
   if (n == 0) return 0;

@@ -56,7 +56,16 @@ def gather_rows(table: torch.Tensor, ids: torch.Tensor, status, code: int = BAD_
     return out
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, status) -> torch.Tensor:
+def embedding(ids: torch.Tensor, table: torch.Tensor, status, out_dtype=None) -> torch.Tensor:
+    """Rows of the table; a table stored in 32-bit can feed bfloat16 activations (rounded here)."""
+    if out_dtype == torch.bfloat16 and table.dtype == torch.float32:
+        _need_cuda(table, ids)
+        assert ids.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+        n, d = ids.numel(), table.shape[1]
+        out = torch.empty((n, d), dtype=torch.bfloat16, device=table.device)
+        call("common", "fmx_gather_rows_f32_to_bf16", table.data_ptr(), ids.data_ptr(), out.data_ptr(), n, d,
+             table.shape[0], _ptr(status), BAD_TOKEN, _stream())
+        return out
     return gather_rows(table, ids, status, BAD_TOKEN)
 
 

@@ -23,6 +23,8 @@ class Embedding(Part):
         return 0          # a step reads T rows, not the table
 
     def forward(self, ids, ctx):
+        if self.weight.dtype != self.rt.dtype:          # a table stored in 32-bit under bfloat16 activations
+            return self.rt.k.embedding(ids, self.weight, ctx.status, self.rt.dtype)
         return self.rt.k.embedding(ids, self.weight, ctx.status)
 
 

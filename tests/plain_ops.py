@@ -16,11 +16,12 @@ def gather_rows(table, ids, status, code=4):
     return table[ids.long()].clone()
 
 
-def embedding(ids, table, status):
+def embedding(ids, table, status, out_dtype=None):
     if ((ids < 0) | (ids >= table.shape[0])).any():
         status[0] = 1
         ids = ids.clamp(0, table.shape[0] - 1)
-    return table[ids.long()].clone()
+    out = table[ids.long()].clone()
+    return out.to(out_dtype) if out_dtype is not None else out
 
 
 def add_rmsnorm(x, residual, weight, eps):

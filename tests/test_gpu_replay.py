@@ -156,3 +156,20 @@ def test_first_tokens(models, name, dtype):
     steps = traces.tail_decoded(prompts, tail=2)
     outs, _ = _run(d, dtype, steps, 256, 16)
     _compare(steps, outs, prompts, ref, TOL[dtype])
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_weights_stored_in_32_bit_under_bfloat16(tmp_path, name):
+    """A folder whose tensors are all float32, run with bfloat16 activations: the tensors stay
+    32-bit (products take 32-bit weights), activations and cache are bfloat16."""
+    cfg = tiny.CONFIGS[name]
+    d = tiny.make_model_dir(tmp_path, cfg, seed=17, dtype=torch.float32)
+    W = tiny.load_plain_weights(d)
+    assert all(t.dtype == torch.float32 for t in W.values())
+    prompts = {"p": tiny.rand_tokens(70, cfg["vocab_size"], 3), "q": tiny.rand_tokens(9, cfg["vocab_size"], 4)}
+    ref = {r: plain_llama.forward(cfg, W, t, round_to=torch.bfloat16) for r, t in prompts.items()}
+    for cut in (traces.whole, traces.mixed):
+        steps = cut(prompts)
+        outs, rp = _run(d, "bfloat16", steps, 256, 16)
+        assert rp.model.layers[0].mixer.qkv.weight.dtype == torch.float32
+        _compare(steps, outs, prompts, ref, TOL["bfloat16"])
