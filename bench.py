@@ -40,6 +40,12 @@ LLAMA_1B = {
                      "original_max_position_embeddings": 8192},
     "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
 }
+LLAMA_3B = dict(LLAMA_1B, num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, head_dim=128)
+LLAMA_8B = dict(LLAMA_1B, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, head_dim=128,
+                intermediate_size=14336, tie_word_embeddings=False,
+                rope_scaling=dict(LLAMA_1B["rope_scaling"], factor=8.0))
+SHAPES = {"1b": ("llama-3.2-1b-shape", LLAMA_1B), "3b": ("llama-3.2-3b-shape", LLAMA_3B),
+          "8b": ("llama-3.1-8b-shape", LLAMA_8B)}
 FULL_LAYERS = 16
 CONTEXT = 8192
 BATCH = 8
@@ -262,7 +268,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration's 16")
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes: Llama-3.2-1B (the default run), 3B, or 3.1-8B")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and batch 64 points")
@@ -286,7 +293,10 @@ def main() -> int:
     import torch
     from fastmlx_b200 import Engine
 
-    cfg = dict(LLAMA_1B, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
+    args.layers = args.layers or full_layers
+    cfg = dict(shape, num_hidden_layers=args.layers)
     vocab = cfg["vocab_size"]
     big = 64 if not args.no_points else args.batch
     pool_tokens = max(big, args.batch) * (args.context + 64) + PREFILL_TOKENS + 64
@@ -330,17 +340,17 @@ def main() -> int:
     step_bytes = nums["weight_bytes"] + args.batch * main_pt["ctx"] * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms / 1e3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape, context 8192)",
+        "metric": f"decode tok/s at batch {args.batch} ({shape_name}, context {args.context})",
         "value": round(args.batch / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random N(0, 0.02) weights",
-        "config": {"model": "llama-3.2-1b-shape", "layers": args.layers, "layers_of_full_config": FULL_LAYERS,
+        "config": {"model": shape_name, "layers": args.layers, "layers_of_full_config": full_layers,
                    "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
                    "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate_size": cfg["intermediate_size"], "vocab_size": vocab, "tie_word_embeddings": True,
-                   "rope": "theta 500000, llama3 x32", "global_batch": args.batch, "seq_len": args.context,
+                   "intermediate_size": cfg["intermediate_size"], "vocab_size": vocab, "tie_word_embeddings": cfg["tie_word_embeddings"],
+                   "rope": f"theta 500000, llama3 x{cfg['rope_scaling']['factor']:g}", "global_batch": args.batch, "seq_len": args.context,
                    "context_at_timing": main_pt["ctx"], "page_size": args.block_size, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (2.5 GB of weights per step)", "cuda_graphs": not args.no_cuda_graphs, "timing": "fastest of 3 regions of K steps",
+                   "l2": f"inputs larger than L2 ({nums['weight_bytes'] / 1e9:.1f} GB of weights per step)", "cuda_graphs": not args.no_cuda_graphs, "timing": "fastest of 3 regions of K steps",
                    "peaks": pk["source"]},
         "clocks": clock.summary(),
         "e2e": {"value": round(args.batch / (main_pt["e2e_ms"] / 1e3), 1), "unit": "tokens/s",
