@@ -210,30 +210,6 @@ def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn
     return out
 
 
-def skinny_stream(x, w, out_dtype=torch.bfloat16, bias=None, residual=None, block: int = 0, out=None, splits=None,
-                  blocks: int = 0):
-    """x[M <= 16, K] @ w[N, K]^T, one warp per 16-row tile of w, persistent blocks.  Epilogues as
-    `skinny_fused` (bias, residual, SiLU-mul over block-interleaved gate/up rows)."""
-    M, K = x.shape
-    N = w.shape[0]
-    n_out = N // 2 if block else N
-    if out is None:
-        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-    tiles = N // 32 if block else -(-N // 16)
-    if splits is None:
-        # every warp of two blocks per SM should have a tile, and a warp at least 512 of K
-        splits = max(1, min((2 * NUM_SMS * 8) // tiles, K // 512))
-    per = (2 if block else 1) * (1 if M <= 8 else 2) * 128
-    while splits > 1 and (tiles * splits * per > SKINNY_WS_FLOATS or tiles > SKINNY_TICKETS):
-        splits -= 1
-    ws, tickets = skinny_workspace(x.device) if splits > 1 else (None, None)
-    call("bf16", "fmx_skinny_stream", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-         M, N, K, _dt(out), _ptr(bias), _ptr(residual), residual.stride(0) if residual is not None else 0, int(block),
-         splits, _ptr(ws), ws.numel() if ws is not None else 0, _ptr(tickets),
-         tickets.numel() if tickets is not None else 0, int(blocks), _stream())
-    return out
-
-
 def can_fuse_skinny(x, w, bias=None) -> bool:
     """May this product run on the fused skinny kernel (norm prologue, residual / SiLU-mul epilogue)?"""
     return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and bias is None
@@ -273,13 +249,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_MAX_ROWS \
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32):
-        # Measured on B200 at 1 and 8 rows: up to ~8k output features the warp-per-tile kernel
-        # wins (its K splits fill the GPU), the block-per-tile kernel wins above that, and from
-        # ~64k features on (the vocabulary) the library's product streams best.
-        N = w.shape[0]
-        if N <= 8192:
-            return skinny_stream(x, w, out_dtype, bias)
-        if N < 65536 or bias is not None:
+        # From ~64k output features on (the vocabulary) the library's product streams best
+        # (77 us against 89 us for 128256 x 2048); below that this kernel, whose launch overlaps
+        # its predecessor's tail.
+        if w.shape[0] < 65536 or bias is not None:
             return skinny_gemm(x, w, bias, out_dtype)
         return torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else torch.mm(x, w.t(), out_dtype=out_dtype)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] >= TC_MIN_ROWS and bias is None \

@@ -33,7 +33,6 @@ _SIGNATURES = {
         "fmx_logit_bias": [_P, _L, _I, _P, _P, _P, _I, _P],
     },
     "bf16": {
-        "fmx_skinny_stream": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _L, _I, _I, _P, _L, _P, _L, _I, _P],
         "fmx_skinny_fused": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _F, _P, _L, _I, _I, _P, _L, _P, _L, _P],
         "fmx_skinny_gemm": [_P, _L, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _L, _P],
     },

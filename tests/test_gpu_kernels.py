@@ -184,50 +184,6 @@ def test_skinny_gemm(M, N, K, out_dtype):
     assert int(k().skinny_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(16, 32), (131, 80), (3072, 2048), (2048, 8192), (17, 1000), (50, 8), (4096, 14336)])
-def test_skinny_stream(M, N, K):
-    """The warp-per-tile product: every row count, widths off the tile and k-block grids, with a
-    bias, with K split over warps (twice over the same workspace), with the residual epilogue."""
-    x, w = rnd(M, K, dtype=torch.bfloat16, seed=61), rnd(N, K, dtype=torch.bfloat16, seed=62, scale=0.05)
-    b = rnd(N, seed=63) if N % 2 else None
-    ref = plain_ops.linear(x, w, b, torch.float64)
-    bd = b.to(DEV) if b is not None else None
-    # 32-bit sums of K products: a few roundings of the running sum, growing like sqrt(K)
-    bound = (x.abs().double() @ w.abs().double().t()) * 2.0 ** -24 * 4 * (K ** 0.5 + 2) + 1e-30
-    for out_dtype in (torch.bfloat16, torch.float32):
-        for splits in (None, 1, 3):
-            for _ in range(2):
-                got = k().skinny_stream(x.to(DEV), w.to(DEV), out_dtype, bd, splits=splits)
-                if out_dtype == torch.float32:
-                    assert ((got.cpu().double() - ref).abs() <= bound).all(), f"stream product, splits {splits}"
-                else:
-                    close(got, ref, out_dtype, f"stream product, splits {splits}")
-    alone = k().skinny_stream(x[M - 1:].contiguous().to(DEV), w.to(DEV), torch.float32, bd, splits=1)
-    batch = k().skinny_stream(x.to(DEV), w.to(DEV), torch.float32, bd, splits=1)
-    assert torch.equal(alone[0], batch[M - 1])           # a row's result does not depend on the batch
-    res = rnd(M, N, dtype=torch.bfloat16, seed=64)
-    stream = res.clone().to(DEV)
-    k().skinny_stream(x.to(DEV), w.to(DEV), residual=stream, out=stream)
-    want = plain_ops.linear(x, w, None, torch.bfloat16).double() + res.double()
-    close(stream, want, torch.bfloat16, "residual epilogue", extra=2.0 ** -8 * want.abs().max().item())
-    assert int(k().skinny_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
-
-
-@pytest.mark.parametrize("M", [1, 8])
-@pytest.mark.parametrize("I,K,blk", [(128, 64, 128), (8192, 2048, 128), (384, 200, 128), (64, 72, 32)])
-def test_skinny_stream_gate_up(M, I, K, blk):
-    x = rnd(M, K, dtype=torch.bfloat16, seed=71, scale=2.0)
-    wg, wu = rnd(I, K, dtype=torch.bfloat16, seed=72, scale=0.1), rnd(I, K, dtype=torch.bfloat16, seed=73, scale=0.1)
-    w = torch.stack([wg.view(-1, blk, K), wu.view(-1, blk, K)], dim=1).reshape(2 * I, K).contiguous()
-    g = plain_ops.linear(x, wg, None, torch.bfloat16)
-    u = plain_ops.linear(x, wu, None, torch.bfloat16)
-    ref = plain_ops.silu_mul(torch.cat([g, u], dim=1))
-    for splits in (None, 1, 2):
-        got = k().skinny_stream(x.to(DEV), w.to(DEV), block=blk, splits=splits)
-        close(got, ref, torch.bfloat16, "gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
-
-
 @pytest.mark.parametrize("M", [1, 3, 8])
 @pytest.mark.parametrize("N,K", [(64, 64), (3072, 2048), (2048, 8192), (144, 200), (256, 72)])
 def test_skinny_fused_norm_and_residual(M, N, K):
