@@ -109,6 +109,8 @@ class StepFunction:
                 k.attention_tickets(rt.device)
             if hasattr(k, "skinny_workspace"):
                 k.skinny_workspace(rt.device)
+            if getattr(k, "stream_enabled", lambda: False)():
+                k.stream_workspace(rt.device)
 
     def run(self, entries: list[StepEntry], reserved: bool = False, check: bool = True,
             tokens_from: torch.Tensor | None = None) -> torch.Tensor:

@@ -210,6 +210,75 @@ def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn
     return out
 
 
+STREAM_MAX_ROWS = 128
+STREAM_RING_BYTES = 110 * 1024    # a CTA's ring of stages: small enough for two CTAs on one SM
+_stream_ws: dict = {}
+
+
+def stream_plan(M: int, N: int, K: int, dual: bool, ctas: int | None = None, ring_bytes: int | None = None):
+    """-> (CTAs, stages, workspace floats, tickets) of the streaming product for these sizes."""
+    halves = 2 if dual else 1
+    nb = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+    tiles = N // 256 if dual else -(-N // 128)
+    total = tiles * (-(-K // 64) if dual else -(-K // 128))       # a unit: 32 KB of W
+    stage_bytes = 32768 + (1 if dual else 2) * nb * 128
+    stages = max(2, min(12, (ring_bytes or STREAM_RING_BYTES) // stage_bytes))
+    ctas = max(1, min(ctas or NUM_SMS, total))
+    return ctas, stages, ctas * 2 * halves * M * 128, tiles
+
+
+def stream_workspace(device):
+    """Partial sums and tickets of the streaming product, one pair per device, made once at the
+    largest size a call can need (one CTA per SM, 128 rows, a gate/up pair: 39 MB) since a
+    CUDA graph holds their addresses.  The tickets start at zero and every launch leaves them
+    at zero.  Launches sharing them run on one stream."""
+    ws = _stream_ws.get(device)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the streaming product's workspace must exist before a CUDA graph is captured")
+        ws = (torch.empty(NUM_SMS * 2 * 2 * STREAM_MAX_ROWS * 128, dtype=torch.float32, device=device),
+              torch.zeros(1 << 14, dtype=torch.int32, device=device))
+        _stream_ws[device] = ws
+    return ws
+
+
+_DECODE_GEMM = _os.environ.get("FASTMLX_DECODE_GEMM", "skinny")     # "stream": the tcgen05 streaming product
+
+
+def stream_enabled() -> bool:
+    return _DECODE_GEMM == "stream"
+
+
+def can_stream(x, w, bias=None, block: int = 0) -> bool:
+    """May this product run on the streaming tcgen05 kernel?"""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and 0 < x.shape[0] <= STREAM_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and w.shape[0] <= 128 << 14
+            and (block == 0 or (block == 128 and w.shape[0] % 256 == 0 and bias is None)))
+
+
+def gemm_stream(x, w, bias=None, out_dtype=torch.bfloat16, block: int = 0, ctas=None, ring_bytes=None, status=None):
+    """x[M <= 128, K] @ w[N, K]^T with W streamed once through shared memory by TMA and
+    multiplied on the tcgen05 tensor cores (W's rows on the lanes of tensor memory, tokens on
+    its columns).  block = 128: w's rows alternate in blocks of 128 gate rows and their up
+    rows, and the result is silu(gate) * up, [M, N/2]."""
+    M, K = x.shape
+    N = w.shape[0]
+    dual = block > 0
+    if dual and block != 128:
+        raise KernelError(f"the streaming product takes gate/up blocks of 128 rows, not {block}")
+    n_ctas, stages, floats, n_tickets = stream_plan(M, N, K, dual, ctas, ring_bytes)
+    ws, tickets = stream_workspace(x.device)
+    if floats > ws.numel() or n_tickets > tickets.numel():
+        raise KernelError(f"the streaming product's workspace does not hold {floats} floats and {n_tickets} tickets")
+    out = torch.empty((M, N // 2 if dual else N), dtype=out_dtype, device=x.device)
+    call("tc", "fmx_gemm_stream", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), out.data_ptr(),
+         out.stride(0), M, N, K, _dt(out), 1 if dual else 0, n_ctas, stages, ws.data_ptr(), ws.numel(),
+         tickets.data_ptr(), tickets.numel(), _ptr(status if status is not None else _status_word(x.device)), _stream())
+    return out
+
+
 def can_fuse_skinny(x, w, bias=None) -> bool:
     """May this product run on the fused skinny kernel (norm prologue, residual / SiLU-mul epilogue)?"""
     return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and bias is None
@@ -246,6 +315,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
     _need_cuda(x, w, bias)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
     assert x.stride(1) == 1 and w.stride(1) == 1
+    if _DECODE_GEMM == "stream" and x.shape[0] < TC_MIN_ROWS and w.shape[0] < 65536 and can_stream(x, w, bias) \
+            and out_dtype in (torch.bfloat16, torch.float32):
+        return gemm_stream(x, w, bias, out_dtype)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_MAX_ROWS \
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32):

@@ -68,6 +68,10 @@ def main(argv=None) -> int:
     ap.add_argument("--M", type=int, default=8)
     ap.add_argument("--N", type=int, default=2048)
     ap.add_argument("--K", type=int, default=8192)
+    ap.add_argument("--ctas", type=int, default=0, help="CTAs of the streaming product (0: one per SM)")
+    ap.add_argument("--ring", type=int, default=0, help="KB of shared-memory ring of the streaming product (0: default)")
+    ap.add_argument("--resident", action="store_true", help="one weight matrix, reused (it may stay in L2)")
+    ap.add_argument("--only", default="", help="time only the implementations whose name starts so")
     ap.add_argument("--launches", type=int, default=10, help="kernel launches per graph")
     ap.add_argument("--replays", type=int, default=5)
     a = ap.parse_args(argv)
@@ -103,17 +107,32 @@ def main(argv=None) -> int:
             print(f"gemm M={a.M} N={a.N} K={a.K} {name}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
         print("status", st.tolist())
     else:
-        copies = max(1, int(300e6 // (a.N * a.K * 2)) + 1)        # more weight than L2 holds
+        copies = 1 if a.resident else max(1, int(300e6 // (a.N * a.K * 2)) + 1)        # more weight than L2 holds
         ws = [torch.randn(a.N, a.K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
         x = torch.randn(a.M, a.K, device=DEV, dtype=torch.bfloat16)
+        st = torch.zeros(4, dtype=torch.int32, device=DEV)
+        k.set_status_word(x.device, st)
         at = [0]
 
-        def f():
-            at[0] = (at[0] + 1) % copies
-            return k.skinny_gemm(x, ws[at[0]], None, torch.bfloat16, splits=a.splits or None)
-        us = _time_graph(f, a.launches, a.replays)
-        print(f"skinny_gemm M={a.M} N={a.N} K={a.K} splits={a.splits or k.skinny_splits(a.M, a.N, a.K)}: {us:.1f} us, "
-              f"{a.N * a.K * 2 / us / 1e3:.0f} GB/s of weights")
+        def rotating(fn):
+            def f():
+                at[0] = (at[0] + 1) % copies
+                return fn(ws[at[0]])
+            return f
+        impls = [("cublas", lambda w: torch.mm(x, w.t()))]
+        if a.M <= 16:
+            impls.append((f"skinny splits={a.splits or k.skinny_splits(a.M, a.N, a.K)}",
+                          lambda w: k.skinny_gemm(x, w, None, torch.bfloat16, splits=a.splits or None)))
+        if k.can_stream(x, ws[0]):
+            ctas, stages, _, _ = k.stream_plan(a.M, a.N, a.K, False, a.ctas or None, a.ring * 1024 or None)
+            impls.append((f"stream ctas={ctas} stages={stages}",
+                          lambda w: k.gemm_stream(x, w, ctas=a.ctas or None, ring_bytes=a.ring * 1024 or None)))
+        for name, fn in impls:
+            if not name.startswith(a.only):
+                continue
+            us = _time_graph(rotating(fn), a.launches, a.replays)
+            print(f"skinny_gemm M={a.M} N={a.N} K={a.K} {name}: {us:.1f} us, {a.N * a.K * 2 / us / 1e3:.0f} GB/s of weights")
+        print("status", st.tolist())
     return 0
 
 

@@ -225,6 +225,55 @@ def test_skinny_fused_gate_up(M, I, K, blk):
         close(got, ref, torch.bfloat16, "gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
 
 
+@pytest.mark.parametrize("M", [1, 7, 8, 16, 17, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(16, 32), (128, 64), (131, 80), (3072, 2048), (2048, 8192), (50, 8), (320, 192), (1000, 1000)])
+def test_gemm_stream(M, N, K):
+    """The streaming tcgen05 product: every column count, widths that are no multiple of the
+    64-wide k block or of the 128-row tile, with and without a bias, both output types; cut
+    over many, few and one CTA (whole tiles, tiles shared by two and by many CTAs), twice in a
+    row over the same workspace and tickets."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=11), rnd(N, K, dtype=torch.bfloat16, seed=12, scale=0.05)
+    b = rnd(N, seed=13) if N % 2 else None
+    ref = plain_ops.linear(x, w, b, torch.float64)
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None
+    first = None
+    for out_dtype in (torch.bfloat16, torch.float32):
+        scale = ref.abs().max().item() * 8 if out_dtype == torch.float32 else None
+        for ctas in (None, 1, 2, 3, 37):
+            for ring in (None, 40 * 1024):
+                for _ in range(2):
+                    got = k().gemm_stream(xd, wd, bd, out_dtype, ctas=ctas, ring_bytes=ring, status=st)
+                    close(got, ref, out_dtype, f"stream gemm, {ctas} CTAs", scale=scale)
+        if first is None:
+            first = got
+    # a row's result does not depend on how many rows share the step
+    alone = k().gemm_stream(xd[M - 1:].contiguous(), wd, bd, torch.float32, ctas=37, status=st)
+    assert torch.equal(alone[0], got[M - 1])
+    assert st.tolist()[0] == 0
+    assert int(k().stream_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("M", [1, 8, 40])
+@pytest.mark.parametrize("I,K", [(128, 64), (8192, 2048), (384, 200), (1280, 72)])
+def test_gemm_stream_gate_up(M, I, K):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=51, scale=2.0)
+    wg, wu = rnd(I, K, dtype=torch.bfloat16, seed=52, scale=0.1), rnd(I, K, dtype=torch.bfloat16, seed=53, scale=0.1)
+    w = torch.stack([wg.view(-1, 128, K), wu.view(-1, 128, K)], dim=1).reshape(2 * I, K).contiguous()
+    g = plain_ops.linear(x, wg, None, torch.bfloat16)
+    u = plain_ops.linear(x, wu, None, torch.bfloat16)
+    ref = plain_ops.silu_mul(torch.cat([g, u], dim=1))
+    st = torch.zeros(4, dtype=torch.int32, device=DEV)
+    for ctas in (None, 1, 5):
+        for _ in range(2):
+            got = k().gemm_stream(x.to(DEV), w.to(DEV), block=128, ctas=ctas, status=st)
+            assert got.shape == (M, I)
+            close(got, ref, torch.bfloat16, "streamed gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
+    assert st.tolist()[0] == 0
+    with pytest.raises(k().KernelError):
+        k().gemm_stream(x.to(DEV), w.to(DEV), block=64)
+
+
 @pytest.mark.parametrize("ta,tw,tc", [(torch.bfloat16, torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32, torch.float32),
                                       (torch.bfloat16, torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16)])
 def test_gemm_simple_mixed_types(ta, tw, tc):
