@@ -13,6 +13,11 @@
 // (gridDim.y): each block leaves its partial tile in a workspace and takes a ticket; the
 // block that draws the last ticket of a tile adds the partials in split order and writes
 // the result.  Nobody waits for anybody, and the sum's order is fixed.
+//
+// Up to eight splits can instead form a thread-block cluster (gridDim.y = the cluster's size):
+// every block leaves its partial tile in its own shared memory, and after one cluster barrier
+// the block of rank 0 reads its peers' tiles through distributed shared memory, in rank order.
+// That replaces a store, a fence, an atomic and a load through L2 by one hardware barrier.
 #include "common.cuh"
 
 namespace {
@@ -29,7 +34,18 @@ template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-template <int MT, int U, typename TO>
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer(const float* mine, unsigned rank) {
+  unsigned a = (unsigned)__cvta_generic_to_shared(mine), ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+template <int MT, int U, typename TO, bool CLUSTER>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long ldw,
                    const float* __restrict__ bias, TO* __restrict__ out, long long ldo, int M, int N, int K,
@@ -103,6 +119,30 @@ skinny_gemm_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, lon
   __syncthreads();
   constexpr int TILE_ELEMS = 16 * 8 * MT;
   const int splits = gridDim.y;
+  if (CLUSTER) {
+    __shared__ float part[TILE_ELEMS];
+    for (int idx = threadIdx.x; idx < TILE_ELEMS; idx += WARPS * 32) {
+      const int tok = idx / 16, row = idx - tok * 16;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) v += red[w][row][tok];
+      part[idx] = v;
+    }
+    cluster_sync();                                      // every block's tile is in its shared memory
+    if (blockIdx.y == 0) {
+      for (int idx = threadIdx.x; idx < TILE_ELEMS; idx += WARPS * 32) {
+        const int tok = idx / 16, row = idx - tok * 16;
+        const int n = n0 + row;
+        if (tok >= M || n >= N) continue;
+        float v = 0.f;
+        for (int sp = 0; sp < splits; ++sp) v += ld_peer(part + idx, (unsigned)sp);
+        if (bias) v += bias[n];
+        store_out<TO>(out + (long long)tok * ldo + n, v);
+      }
+    }
+    cluster_sync();                                      // nobody leaves while its tile may still be read
+    return;
+  }
   if (splits == 1) {
     for (int idx = threadIdx.x; idx < TILE_ELEMS; idx += WARPS * 32) {
       const int tok = idx / 16, row = idx - tok * 16;    // consecutive threads write consecutive features
@@ -145,9 +185,14 @@ skinny_gemm_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, lon
 
 template <int MT, int U, typename TO>
 void launch(const void* x, long long ldx, const void* W, long long ldw, const float* bias, void* out, long long ldo,
-            int M, int N, int K, int splits, float* ws, int* tickets, cudaStream_t stream) {
-  fmx_launch(skinny_gemm_kernel<MT, U, TO>, dim3((N + 15) / 16, splits), dim3(WARPS * 32), 0, stream, (const bf16*)x,
-             ldx, (const bf16*)W, ldw, bias, (TO*)out, ldo, M, N, K, ws, tickets);
+            int M, int N, int K, int splits, float* ws, int* tickets, bool cluster, cudaStream_t stream) {
+  if (cluster)
+    fmx_launch_cluster(skinny_gemm_kernel<MT, U, TO, true>, dim3((N + 15) / 16, splits), dim3(WARPS * 32), 0, stream,
+                       dim3(1, splits, 1), (const bf16*)x, ldx, (const bf16*)W, ldw, bias, (TO*)out, ldo, M, N, K, ws,
+                       tickets);
+  else
+    fmx_launch(skinny_gemm_kernel<MT, U, TO, false>, dim3((N + 15) / 16, splits), dim3(WARPS * 32), 0, stream,
+               (const bf16*)x, ldx, (const bf16*)W, ldw, bias, (TO*)out, ldo, M, N, K, ws, tickets);
 }
 }  // namespace
 
@@ -160,7 +205,8 @@ FMX_EXPORT long long fmx_skinny_gemm_ws_floats(int M, int N, int splits) {
 FMX_EXPORT long long fmx_skinny_gemm_tickets(int N, int splits) { return splits <= 1 ? 0 : (N + 15) / 16; }
 
 // x, W bfloat16 with rows 16-byte aligned (K, ldx, ldw multiples of 8); out bfloat16
-// (out_dtype 1) or float (0); bias float or null.
+// (out_dtype 1) or float (0); bias float or null.  splits < 0: -splits blocks (2..8) form a
+// cluster and reduce through distributed shared memory; no workspace is used.
 FMX_EXPORT int fmx_skinny_gemm(const void* x, long long ldx, const void* W, long long ldw, const float* bias, void* out,
                                long long ldo, int M, int N, int K, int out_dtype, int splits, float* ws,
                                long long ws_floats, int* tickets, long long n_tickets, cudaStream_t stream) {
@@ -168,17 +214,20 @@ FMX_EXPORT int fmx_skinny_gemm(const void* x, long long ldx, const void* W, long
   if (M < 0 || M > 16 || N < 0 || K <= 0) return fmx_fail("fmx_skinny_gemm: takes 1..16 rows, got M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15))
     return fmx_fail("fmx_skinny_gemm: rows must be 16-byte aligned (K=%d ldx=%lld ldw=%lld)", K, ldx, ldw);
+  const bool cluster = splits < 0;
+  if (cluster) splits = -splits;
+  if (cluster && (splits < 2 || splits > 8)) return fmx_fail("fmx_skinny_gemm: a cluster holds 2..8 splits, not %d", splits);
   if (splits < 1 || splits > 65535) return fmx_fail("fmx_skinny_gemm: bad split count %d", splits);
-  if (splits > 1 && (ws == nullptr || tickets == nullptr || ws_floats < fmx_skinny_gemm_ws_floats(M, N, splits) ||
+  if (splits > 1 && !cluster && (ws == nullptr || tickets == nullptr || ws_floats < fmx_skinny_gemm_ws_floats(M, N, splits) ||
                      n_tickets < fmx_skinny_gemm_tickets(N, splits)))
     return fmx_fail("fmx_skinny_gemm: %d splits need %lld floats and %lld tickets of workspace", splits,
                     fmx_skinny_gemm_ws_floats(M, N, splits), fmx_skinny_gemm_tickets(N, splits));
   if (out_dtype == FMX_BF16) {
-    if (M <= 8) launch<1, 8, bf16>(x, ldx, W, ldw, bias, out, ldo, M, N, K, splits, ws, tickets, stream);
-    else launch<2, 4, bf16>(x, ldx, W, ldw, bias, out, ldo, M, N, K, splits, ws, tickets, stream);
+    if (M <= 8) launch<1, 8, bf16>(x, ldx, W, ldw, bias, out, ldo, M, N, K, splits, ws, tickets, cluster, stream);
+    else launch<2, 4, bf16>(x, ldx, W, ldw, bias, out, ldo, M, N, K, splits, ws, tickets, cluster, stream);
   } else if (out_dtype == FMX_F32) {
-    if (M <= 8) launch<1, 8, float>(x, ldx, W, ldw, bias, out, ldo, M, N, K, splits, ws, tickets, stream);
-    else launch<2, 4, float>(x, ldx, W, ldw, bias, out, ldo, M, N, K, splits, ws, tickets, stream);
+    if (M <= 8) launch<1, 8, float>(x, ldx, W, ldw, bias, out, ldo, M, N, K, splits, ws, tickets, cluster, stream);
+    else launch<2, 4, float>(x, ldx, W, ldw, bias, out, ldo, M, N, K, splits, ws, tickets, cluster, stream);
   } else {
     return fmx_fail("fmx_skinny_gemm: unknown output dtype %d", out_dtype);
   }

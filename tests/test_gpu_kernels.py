@@ -176,7 +176,7 @@ def test_skinny_gemm(M, N, K, out_dtype):
     assert torch.equal(alone[0], got[M - 1])
     # K split over blocks: the same values up to the order of the partial sums, twice in a row
     # over the same workspace and tickets
-    for splits in (2, 3, 7):
+    for splits in (2, 3, 7, -2, -5, -8):                # negative: that many blocks as one cluster
         for _ in range(2):
             sp = k().skinny_gemm(x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None, out_dtype, splits=splits)
             close(sp, ref, out_dtype, f"skinny gemm, {splits} splits",
