@@ -173,6 +173,42 @@ def skinny_gemm(x, w, bias, out_dtype, splits=None) -> torch.Tensor:
     return out
 
 
+GEMV_MAX_ROWS = 16
+
+
+def can_gemv(x, w) -> bool:
+    """May this product run on the whole-K kernel of decode steps?"""
+    return (_DECODE_GEMM == "gemv" and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and 0 < x.shape[0] <= GEMV_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
+            and w.stride(1) == 1 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemv_width(n_out: int, block: int = 0) -> int:
+    """Output features per block: 32 once that still fills every SM four times, else 16."""
+    wide = 32 if n_out >= 32 * 4 * NUM_SMS else 16
+    while block and block % wide:
+        wide //= 2
+    return wide
+
+
+def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 0, out=None, wide=None):
+    """x[M <= 16, K] @ w[N, K]^T, one block per `wide` (8, 16, 32) output features and the whole of K:
+    nothing is summed across blocks.  residual [M, n_out] is added to the product (out may be
+    the residual itself).  block > 0: w's rows alternate in blocks of `block` gate rows and
+    their up rows, and the result is silu(gate) * up, [M, N/2]."""
+    M, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if block else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+    if wide is None:
+        wide = gemv_width(n_out, block)
+    call("bf16", "fmx_gemv", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), _ptr(residual),
+         residual.stride(0) if residual is not None else 0, out.data_ptr(), out.stride(0), M, N, K, _dt(out), int(block),
+         int(wide), _stream())
+    return out
+
+
 EPI_PLAIN, EPI_SILU_MUL, EPI_RESIDUAL = 0, 1, 2
 
 
@@ -242,7 +278,9 @@ def stream_workspace(device):
     return ws
 
 
-_DECODE_GEMM = _os.environ.get("FASTMLX_DECODE_GEMM", "skinny")     # "stream": the tcgen05 streaming product
+# which kernel multiplies the few rows of a decode step: "gemv" (whole K per block), "skinny"
+# (16-row tiles, K split over blocks), "stream" (TMA ring + tcgen05)
+_DECODE_GEMM = _os.environ.get("FASTMLX_DECODE_GEMM", "gemv")
 
 
 def stream_enabled() -> bool:
@@ -315,6 +353,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
     _need_cuda(x, w, bias)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
     assert x.stride(1) == 1 and w.stride(1) == 1
+    if _DECODE_GEMM == "gemv" and w.shape[0] < 65536 and can_gemv(x, w) and out_dtype in (torch.bfloat16, torch.float32):
+        # From ~64k output features on (the vocabulary) the library's product streams best.
+        return gemv(x, w, bias, out_dtype)
     if _DECODE_GEMM == "stream" and x.shape[0] < TC_MIN_ROWS and w.shape[0] < 65536 and can_stream(x, w, bias) \
             and out_dtype in (torch.bfloat16, torch.float32):
         return gemm_stream(x, w, bias, out_dtype)

@@ -123,6 +123,9 @@ def main(argv=None) -> int:
         if a.M <= 16:
             impls.append((f"skinny splits={a.splits or k.skinny_splits(a.M, a.N, a.K)}",
                           lambda w: k.skinny_gemm(x, w, None, torch.bfloat16, splits=a.splits or None)))
+            impls.append(("gemv 8 features", lambda w: k.gemv(x, w, wide=8)))
+            impls.append(("gemv 16 features", lambda w: k.gemv(x, w, wide=16)))
+            impls.append(("gemv 32 features", lambda w: k.gemv(x, w, wide=32)))
         if k.can_stream(x, ws[0]):
             ctas, stages, _, _ = k.stream_plan(a.M, a.N, a.K, False, a.ctas or None, a.ring * 1024 or None)
             impls.append((f"stream ctas={ctas} stages={stages}",

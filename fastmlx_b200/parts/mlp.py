@@ -33,6 +33,9 @@ class SwiGLU(FeedForward):
         if self.block and self.gate_up.bias is None and x.dtype == w.dtype == torch.bfloat16 \
                 and x.shape[0] >= getattr(k, "TC_MIN_ROWS", 1 << 30) and getattr(k, "tc_enabled", lambda: False)():
             act = k.gemm_tcgen05(x, w, ctx.status if ctx is not None else None, epilogue=k.EPI_SILU_MUL)
+        elif self.block and self.block % 16 == 0 and self.gate_up.bias is None and hasattr(k, "can_gemv") and k.can_gemv(x, w):
+            # decode steps: a block owns some gate rows and their up rows, SiLU-mul in its epilogue
+            act = k.gemv(x, w, block=self.block)
         elif self.block and getattr(k, "stream_enabled", lambda: False)() and k.can_stream(x, w, self.gate_up.bias, self.block):
             # few rows: W streamed once through the tensor cores, SiLU-mul in the epilogue
             act = k.gemm_stream(x, w, block=self.block, status=ctx.status if ctx is not None else None)

@@ -225,6 +225,50 @@ def test_skinny_fused_gate_up(M, I, K, blk):
         close(got, ref, torch.bfloat16, "gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
 
 
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 32), (64, 64), (131, 80), (3072, 2048), (2048, 8192), (50, 8), (320, 192), (17, 1000)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemv(M, N, K, out_dtype):
+    """The product with the whole of K in one block: every row count up to 16, widths that are
+    no multiple of the 32-wide k block or of the 8-feature tile, bias, residual in place, both
+    tile widths."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=11), rnd(N, K, dtype=torch.bfloat16, seed=12, scale=0.05)
+    b = rnd(N, seed=13) if N % 2 else None
+    ref = plain_ops.linear(x, w, b, torch.float64)
+    scale = ref.abs().max().item() * 8 if out_dtype == torch.float32 else None
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None
+    for wide in (8, 16, 32):
+        got = k().gemv(xd, wd, bd, out_dtype, wide=wide)
+        close(got, ref, out_dtype, "gemv", scale=scale)
+        alone = k().gemv(xd[M - 1:].contiguous(), wd, bd, out_dtype, wide=wide)
+        if M <= 8:                                       # rows 8..15 sit in another accumulator half
+            assert torch.equal(alone[0], got[M - 1])     # a row's result does not depend on its companions
+    if out_dtype == torch.bfloat16:
+        res = rnd(M, N, dtype=torch.bfloat16, seed=44)
+        stream = res.clone().to(DEV)
+        out = k().gemv(xd, wd, residual=stream, out=stream)
+        assert out.data_ptr() == stream.data_ptr()
+        want = plain_ops.linear(x, w, None, torch.bfloat16).double() + res.double()
+        close(stream, want, torch.bfloat16, "gemv residual epilogue", extra=2.0 ** -8 * want.abs().max().item())
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("I,K,blk", [(128, 64, 128), (8192, 2048, 128), (384, 200, 128), (64, 72, 32), (48, 40, 16)])
+def test_gemv_gate_up(M, I, K, blk):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=51, scale=2.0)
+    wg, wu = rnd(I, K, dtype=torch.bfloat16, seed=52, scale=0.1), rnd(I, K, dtype=torch.bfloat16, seed=53, scale=0.1)
+    w = torch.stack([wg.view(-1, blk, K), wu.view(-1, blk, K)], dim=1).reshape(2 * I, K).contiguous()
+    g = plain_ops.linear(x, wg, None, torch.bfloat16)
+    u = plain_ops.linear(x, wu, None, torch.bfloat16)
+    ref = plain_ops.silu_mul(torch.cat([g, u], dim=1))
+    for wide in (8, 16, 32):
+        if blk % wide:
+            continue
+        got = k().gemv(x.to(DEV), w.to(DEV), block=blk, wide=wide)
+        assert got.shape == (M, I)
+        close(got, ref, torch.bfloat16, "gemv gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
+
+
 @pytest.mark.parametrize("M", [1, 7, 8, 16, 17, 33, 64, 100, 128])
 @pytest.mark.parametrize("N,K", [(16, 32), (128, 64), (131, 80), (3072, 2048), (2048, 8192), (50, 8), (320, 192), (1000, 1000)])
 def test_gemm_stream(M, N, K):
