@@ -351,7 +351,6 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   const int split = blockIdx.x, splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
   const int rep = nh / nkv;
-  pdl_trigger();
   pdl_wait();
   const int t = row_start[r];
   const int pos = positions[t];                      // -1 for a padding row: no keys at all
@@ -426,6 +425,7 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   }
   cp_async_wait<0>();
   __syncthreads();                                   // the tiles are done with; reuse the memory
+  pdl_trigger();                                     // the block's loads are done: room for the next kernel's
 
   // merge the four warps: each leaves (m, l, o) of its 16 rows
   float* mo = reinterpret_cast<float*>(smem_raw);    // [4][16][HD]
@@ -503,8 +503,8 @@ __global__ void attn_combine_kernel(const float* part_o, const float* part_ml, c
                                     int nh, int nkv, int splits) {
   const int h = blockIdx.x, r = blockIdx.y;
   const int rep = nh / nkv, g = h / rep, row = h - g * rep;
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = row_start[r];
   const long long base = (((long long)r * nkv + g) * splits) * 16 + row;
   float M = -INFINITY;

@@ -184,8 +184,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_slot;
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
 
   const int t0 = row_start[r], q_len = row_start[r + 1] - t0, ctx = row_ctx[r];
   const int tok0 = tile * tok_per_tile;                   // first token of this tile within the row

@@ -39,7 +39,6 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
   constexpr int TILES = DUAL ? 2 * NT : NT;
   constexpr int ROWS = HI ? 16 : 8;
   __shared__ float red[WARPS][TILES][ROWS][9];
-  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   // the first W row of each tile, and the first output column of the block
   int row0[TILES], out0;
@@ -103,6 +102,7 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
       }
     if (kb + WARPS * U < nkb) load_w(kb + WARPS * U);
   }
+  pdl_trigger();                                  // the block's loads are done: room for the next kernel's
 #pragma unroll
   for (int i = 0; i < TILES; ++i) {
     red[warp][i][g][2 * t] = acc[i][0];

@@ -39,7 +39,6 @@ skinny_fused_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, lo
   __shared__ float red[WARPS][NT][16][9];
   __shared__ float rstd_s[8];
   __shared__ int last_ticket;
-  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   int row0[NT], out0;
   if (NT == 2) {
@@ -89,6 +88,7 @@ skinny_fused_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, lo
   int kb = kb0 + warp;
   if (kb < nkb) load_w(kb);                       // W is never written: ahead of the wait
   pdl_wait();
+  pdl_trigger();
 
   float rstd = 1.f;
   if (norm_w != nullptr) {

@@ -52,7 +52,6 @@ skinny_gemm_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, lon
                    float* __restrict__ ws, int* __restrict__ tickets) {
   __shared__ float red[WARPS][16][8 * MT + 1];
   __shared__ int last_ticket;
-  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
   const bf16* w0 = W + (long long)min(n0 + g, N - 1) * ldw + 8 * t;
@@ -91,6 +90,7 @@ skinny_gemm_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, lon
     }
     if (!waited) {
       pdl_wait();
+      pdl_trigger();
       waited = true;
     }
 #pragma unroll
@@ -108,7 +108,10 @@ skinny_gemm_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, lon
         mma_bf16(acc[j], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b[u][j].z, b[u][j].w);
       }
   }
-  if (!waited) pdl_wait();                             // a warp without a k block still orders its writes
+  if (!waited) {
+    pdl_wait();
+    pdl_trigger();
+  }                             // a warp without a k block still orders its writes
 #pragma unroll
   for (int j = 0; j < MT; ++j) {
     red[warp][g][8 * j + 2 * t] = acc[j][0];

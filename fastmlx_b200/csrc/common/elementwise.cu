@@ -6,8 +6,8 @@
 template <typename T>
 __global__ void gather_rows_kernel(const T* table, const int* ids, T* out,
                                    int d, long long nrows, int* status, int code) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const long long id = ids[t];
   T* dst = out + (long long)t * d;
@@ -31,8 +31,8 @@ __global__ void gather_rows_kernel(const T* table, const int* ids, T* out,
 // A table stored in 32-bit feeding bfloat16 activations: gather and round.
 __global__ void gather_rows_f32_to_bf16_kernel(const float* table, const int* ids, bf16* out, int d, long long nrows,
                                                int* status, int code) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const long long id = ids[t];
   bf16* dst = out + (long long)t * d;
@@ -100,8 +100,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
 template <int BLOCK, int CH>
 __global__ void __launch_bounds__(BLOCK)
 add_rmsnorm_bf16_vec_kernel(const bf16* x, bf16* residual, const float* __restrict__ w, bf16* out, int d, float eps) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const long long row = blockIdx.x;
   const int nvec = d / 8;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
@@ -206,8 +206,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
 
 // bfloat16 with I a multiple of 8: eight elements per thread, 16-byte loads and stores.
 __global__ void silu_mul_bf16_vec_kernel(const bf16* gu, bf16* out, int I, int blk) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const long long t = blockIdx.y;
   const int nvec = I / 8, bvec = blk / 8;
   const uint4* gp = reinterpret_cast<const uint4*>(gu + t * 2 * I);

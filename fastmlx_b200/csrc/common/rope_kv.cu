@@ -60,8 +60,8 @@ rope_kv_write_bf16_vec_kernel(bf16* qkv, const int* positions, const float* __re
                               const long long* slot_mapping, bf16* kv, int nh, int nkv, int hd, int rot,
                               int page_size, long long num_pages, long long row_stride, int* status) {
   extern __shared__ float sc[];                 // [half] sines, [half] cosines
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   bf16* row = qkv + (long long)t * row_stride;
   const int half = rot / 2;

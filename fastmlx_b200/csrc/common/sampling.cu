@@ -84,8 +84,8 @@ __device__ float block_scan(float v, float* total) {
 __global__ void __launch_bounds__(SBLOCK)
 sample_kernel(const float* logits, long long ld, int V, const float* temperature, const float* uniform,
               const unsigned char* keep, long long keep_ld, int* out) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const float* row = logits + (long long)r * ld;
   const unsigned char* kp = keep ? keep + (long long)r * keep_ld : nullptr;

@@ -96,7 +96,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_trigger();
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------------ producer
@@ -119,6 +118,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       if (++k == kb) { k = 0; ++tile; }
     }
     pdl_wait();                                    // x is the output of the kernel ahead
+    pdl_trigger();
     for (int st = 0, kx = k0; st < ahead; ++st) {
 #pragma unroll
       for (int j = 0; j < KSUB; ++j)

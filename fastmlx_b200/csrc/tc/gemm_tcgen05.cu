@@ -157,8 +157,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_trigger();
   pdl_wait();                                      // A is the output of the kernel before this one
+  pdl_trigger();
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------------ producer

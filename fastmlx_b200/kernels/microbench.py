@@ -78,8 +78,15 @@ def main(argv=None) -> int:
     if a.kernel == "attn_decode":
         qkv, kv, ctx, grp = _attention_inputs(a, 1)
         splits = a.splits or k.decode_splits(a.batch, a.nkv, a.ctx + 1, a.hd)
-        us = _time_graph(lambda: k.paged_attention_decode(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, 0,
-                                                          splits=splits), a.launches, a.replays)
+        # as in a model, where every layer has a cache of its own: more K and V than L2 holds
+        copies = 1 if a.resident else max(1, int(400e6 // kv.numel() // 2) + 1)
+        kvs = [kv] + [torch.randn_like(kv) for _ in range(copies - 1)]
+        at = [0]
+
+        def f():
+            at[0] = (at[0] + 1) % copies
+            return k.paged_attention_decode(qkv, kvs[at[0]], ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, 0, splits=splits)
+        us = _time_graph(f, a.launches, a.replays)
         nbytes = a.batch * (a.ctx + 1) * a.nkv * a.hd * 2 * 2
         print(f"attn_decode B={a.batch} ctx={a.ctx} nh={a.nh} nkv={a.nkv} hd={a.hd} page={a.page} splits={splits}: "
               f"{us:.1f} us, {nbytes / us / 1e3:.0f} GB/s of K and V")
