@@ -351,7 +351,7 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   const int split = blockIdx.x, splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
   const int rep = nh / nkv;
-  pdl_wait();
+  // Row starts, positions and block tables are in place before the step's first kernel runs.
   const int t = row_start[r];
   const int pos = positions[t];                      // -1 for a padding row: no keys at all
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
@@ -366,6 +366,20 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   const int kend = min(pos + 1, kbeg + per);
   const int kstart = kbeg & ~3;
   const int n_tiles = kend > kbeg ? (kend - kstart + BN - 1) / BN : 0;
+
+  auto stage_k = [&](int s) { return smem + (size_t)s * 2 * TILE; };
+  auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
+  // Keys before this row's new one were written by earlier steps: tiles that end before it are
+  // fetched while the kernel ahead (which writes the new key and the queries) is still running.
+  int fetched = 0;
+#pragma unroll
+  for (int s = 0; s < DECODE_STAGES - 1; ++s) {
+    if (fetched == s && s < n_tiles && min(kend, kstart + (s + 1) * BN) <= pos) {
+      load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
+      fetched = s + 1;
+    }
+  }
+  pdl_wait();
 
   unsigned qf[KSTEPS][4];
 #pragma unroll
@@ -388,11 +402,10 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
 
-  auto stage_k = [&](int s) { return smem + (size_t)s * 2 * TILE; };
-  auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
+  // the groups of the pipeline: tile s is in group s, whether it went out before the wait or not
 #pragma unroll
   for (int s = 0; s < DECODE_STAGES - 1; ++s) {
-    if (s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
+    if (s >= fetched && s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
     cp_async_commit();
   }
   for (int it = 0; it < n_tiles; ++it) {

@@ -6,7 +6,7 @@
 // operand.  As in skinny_gemm.cu nothing is staged in shared memory: the sum over k does not
 // care in which order k is visited, so each thread loads 16 contiguous bytes of a W row and
 // of an x row straight into registers and hands them to two MMAs under a permutation of k
-// that is the same for both operands.  The eight warps of a block take interleaved 32-wide
+// that is the same for both operands.  The 8 or 16 warps of a block take interleaved 32-wide
 // slices of K and add their partial tiles through shared memory in warp order.
 //
 // With 8 features per block a 2048-wide output still makes 256 blocks, enough to keep every
@@ -17,7 +17,6 @@
 #include "common.cuh"
 
 namespace {
-constexpr int WARPS = 8;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                          unsigned b1) {
@@ -32,7 +31,7 @@ template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { 
 
 // NT tiles of 8 features per block; HI: rows 8..15 of x exist; DUAL: the NT tiles are gate
 // tiles and each has an up tile `blk` rows further on.
-template <int NT, bool HI, bool DUAL, int U, typename TO>
+template <int NT, bool HI, bool DUAL, int U, int WARPS, typename TO>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long ldw, const float* __restrict__ bias,
             const bf16* residual, long long ldr, TO* out, long long ldo, int M, int N, int K, int blk) {
@@ -133,11 +132,11 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
   }
 }
 
-template <int NT, bool HI, bool DUAL, int U, typename TO>
+template <int NT, bool HI, bool DUAL, int U, int WARPS, typename TO>
 void launch(const void* x, long long ldx, const void* W, long long ldw, const float* bias, const void* residual,
             long long ldr, void* out, long long ldo, int M, int N, int K, int blk, cudaStream_t stream) {
   const int n_out = DUAL ? N / 2 : N;
-  fmx_launch(gemv_kernel<NT, HI, DUAL, U, TO>, dim3((n_out + 8 * NT - 1) / (8 * NT)), dim3(WARPS * 32), 0, stream,
+  fmx_launch(gemv_kernel<NT, HI, DUAL, U, WARPS, TO>, dim3((n_out + 8 * NT - 1) / (8 * NT)), dim3(WARPS * 32), 0, stream,
              (const bf16*)x, ldx, (const bf16*)W, ldw, bias, (const bf16*)residual, ldr, (TO*)out, ldo, M, N, K, blk);
 }
 }  // namespace
@@ -145,10 +144,11 @@ void launch(const void* x, long long ldx, const void* W, long long ldw, const fl
 // x [M <= 16, K] and W [N, K] bfloat16, rows 16-byte aligned; out [M, N] bfloat16 (out_dtype 1)
 // or float (0); bias float[N] or null; residual bfloat16 [M, n_out] or null (may be `out`).
 // blk > 0: W's rows alternate in blocks of blk gate rows and blk up rows, out is [M, N/2] =
-// silu(gate) * up in bfloat16.  wide: 8, 16 or 32 output features per block.
+// silu(gate) * up in bfloat16.  wide: 8, 16 or 32 output features per block; warps: 8 or 16
+// per block (16 when few blocks must keep many bytes in flight over a long K).
 FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long ldw, const float* bias, const void* residual,
                         long long ldr, void* out, long long ldo, int M, int N, int K, int out_dtype, int blk, int wide,
-                        cudaStream_t stream) {
+                        int warps, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (M < 0 || M > 16 || N < 0 || K <= 0) return fmx_fail("fmx_gemv: takes 1..16 rows, got M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15))
@@ -157,15 +157,22 @@ FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long l
     return fmx_fail("fmx_gemv: gate/up blocks of %d do not tile %d rows", blk, N);
   if (blk > 0 && out_dtype != FMX_BF16) return fmx_fail("fmx_gemv: the SiLU-mul epilogue writes bfloat16");
   const bool hi = M > 8;
+  if (warps != 8 && warps != 16) return fmx_fail("fmx_gemv: 8 or 16 warps per block, not %d", warps);
+  if (warps == 16 && wide == 32) return fmx_fail("fmx_gemv: 32 features per block go with 8 warps");
   if (wide != 8 && wide != 16 && wide != 32) return fmx_fail("fmx_gemv: 8, 16 or 32 features per block, not %d", wide);
   if (blk > 0 && blk % wide) return fmx_fail("fmx_gemv: %d features per block do not tile gate/up blocks of %d", wide, blk);
-#define FMX_GV(NT_, HI_, DUAL_, U_, TO_) \
-  launch<NT_, HI_, DUAL_, U_, TO_>(x, ldx, W, ldw, bias, residual, ldr, out, ldo, M, N, K, blk, stream)
+#define FMX_GV1(NT_, HI_, DUAL_, U_, W_, TO_) \
+  launch<NT_, HI_, DUAL_, U_, W_, TO_>(x, ldx, W, ldw, bias, residual, ldr, out, ldo, M, N, K, blk, stream)
+#define FMX_GV(NT_, HI_, DUAL_, U_, TO_)                 \
+  do {                                                   \
+    if (warps == 16) FMX_GV1(NT_, HI_, DUAL_, U_, 16, TO_); \
+    else FMX_GV1(NT_, HI_, DUAL_, U_, 8, TO_);           \
+  } while (0)
 #define FMX_GV_WIDTHS(HI_, DUAL_, TO_, U8, U16, U32)      \
   do {                                                    \
     if (wide == 8) FMX_GV(1, HI_, DUAL_, U8, TO_);        \
     else if (wide == 16) FMX_GV(2, HI_, DUAL_, U16, TO_); \
-    else FMX_GV(4, HI_, DUAL_, U32, TO_);                 \
+    else FMX_GV1(4, HI_, DUAL_, U32, 8, TO_);             \
   } while (0)
   if (blk > 0) {
     if (hi) FMX_GV_WIDTHS(true, true, bf16, 4, 2, 1);
@@ -180,6 +187,7 @@ FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long l
     return fmx_fail("fmx_gemv: unknown output dtype %d", out_dtype);
   }
 #undef FMX_GV_WIDTHS
+#undef FMX_GV1
 #undef FMX_GV
   FMX_LAUNCH_CHECK();
   return 0;

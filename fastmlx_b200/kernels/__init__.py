@@ -174,6 +174,8 @@ def skinny_gemm(x, w, bias, out_dtype, splits=None) -> torch.Tensor:
 
 
 GEMV_MAX_ROWS = 16
+# from this many output features on (the vocabulary) a decode step's product goes to the library
+LIBRARY_MIN_FEATURES = int(_os.environ.get("FASTMLX_LIBRARY_MIN_FEATURES", "65536"))
 
 
 def can_gemv(x, w) -> bool:
@@ -184,14 +186,16 @@ def can_gemv(x, w) -> bool:
 
 
 def gemv_width(n_out: int, block: int = 0) -> int:
-    """Output features per block: 32 once that still fills every SM four times, else 16."""
-    wide = 32 if n_out >= 32 * 4 * NUM_SMS else 16
+    """Output features per block: 32 once that still gives every SM a block, else 16 (measured:
+    wider blocks re-read x less and keep more of W in flight per block, but too few of them
+    leave SMs idle)."""
+    wide = 32 if n_out // 32 >= NUM_SMS else 16
     while block and block % wide:
         wide //= 2
     return wide
 
 
-def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 0, out=None, wide=None):
+def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 0, out=None, wide=None, warps=None):
     """x[M <= 16, K] @ w[N, K]^T, one block per `wide` (8, 16, 32) output features and the whole of K:
     nothing is summed across blocks.  residual [M, n_out] is added to the product (out may be
     the residual itself).  block > 0: w's rows alternate in blocks of `block` gate rows and
@@ -203,9 +207,12 @@ def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     if wide is None:
         wide = gemv_width(n_out, block)
+    if warps is None:
+        # fewer blocks than SMs over a long K: twice the warps keep enough bytes in flight
+        warps = 16 if wide < 32 and -(-n_out // wide) < NUM_SMS and K >= 4096 else 8
     call("bf16", "fmx_gemv", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), _ptr(residual),
          residual.stride(0) if residual is not None else 0, out.data_ptr(), out.stride(0), M, N, K, _dt(out), int(block),
-         int(wide), _stream())
+         int(wide), int(warps), _stream())
     return out
 
 
@@ -353,10 +360,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
     _need_cuda(x, w, bias)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
     assert x.stride(1) == 1 and w.stride(1) == 1
-    if _DECODE_GEMM == "gemv" and w.shape[0] < 65536 and can_gemv(x, w) and out_dtype in (torch.bfloat16, torch.float32):
+    if _DECODE_GEMM == "gemv" and w.shape[0] < LIBRARY_MIN_FEATURES and can_gemv(x, w) and out_dtype in (torch.bfloat16, torch.float32):
         # From ~64k output features on (the vocabulary) the library's product streams best.
         return gemv(x, w, bias, out_dtype)
-    if _DECODE_GEMM == "stream" and x.shape[0] < TC_MIN_ROWS and w.shape[0] < 65536 and can_stream(x, w, bias) \
+    if _DECODE_GEMM == "stream" and x.shape[0] < TC_MIN_ROWS and w.shape[0] < LIBRARY_MIN_FEATURES and can_stream(x, w, bias) \
             and out_dtype in (torch.bfloat16, torch.float32):
         return gemm_stream(x, w, bias, out_dtype)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_MAX_ROWS \
@@ -365,7 +372,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
         # From ~64k output features on (the vocabulary) the library's product streams best
         # (77 us against 89 us for 128256 x 2048); below that this kernel, whose launch overlaps
         # its predecessor's tail.
-        if w.shape[0] < 65536 or bias is not None:
+        if w.shape[0] < LIBRARY_MIN_FEATURES or bias is not None:
             return skinny_gemm(x, w, bias, out_dtype)
         return torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else torch.mm(x, w.t(), out_dtype=out_dtype)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] >= TC_MIN_ROWS and bias is None \

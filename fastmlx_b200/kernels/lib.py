@@ -34,7 +34,7 @@ _SIGNATURES = {
     },
     "bf16": {
         "fmx_skinny_fused": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _F, _P, _L, _I, _I, _P, _L, _P, _L, _P],
-        "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+        "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],
         "fmx_skinny_gemm": [_P, _L, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _L, _P],
     },
     "tc": {

@@ -70,6 +70,7 @@ def main(argv=None) -> int:
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--ctas", type=int, default=0, help="CTAs of the streaming product (0: one per SM)")
     ap.add_argument("--ring", type=int, default=0, help="KB of shared-memory ring of the streaming product (0: default)")
+    ap.add_argument("--dual", action="store_true", help="skinny_gemm: the gate/up product with SiLU-mul")
     ap.add_argument("--resident", action="store_true", help="one weight matrix, reused (it may stay in L2)")
     ap.add_argument("--only", default="", help="time only the implementations whose name starts so")
     ap.add_argument("--launches", type=int, default=10, help="kernel launches per graph")
@@ -130,13 +131,19 @@ def main(argv=None) -> int:
         if a.M <= 16:
             impls.append((f"skinny splits={a.splits or k.skinny_splits(a.M, a.N, a.K)}",
                           lambda w: k.skinny_gemm(x, w, None, torch.bfloat16, splits=a.splits or None)))
-            impls.append(("gemv 8 features", lambda w: k.gemv(x, w, wide=8)))
-            impls.append(("gemv 16 features", lambda w: k.gemv(x, w, wide=16)))
-            impls.append(("gemv 32 features", lambda w: k.gemv(x, w, wide=32)))
+            impls.append(("gemv 8 features", lambda w: k.gemv(x, w, wide=8, warps=8)))
+            impls.append(("gemv 16 features", lambda w: k.gemv(x, w, wide=16, warps=8)))
+            impls.append(("gemv 32 features", lambda w: k.gemv(x, w, wide=32, warps=8)))
+            impls.append(("gemv 8 features, 16 warps", lambda w: k.gemv(x, w, wide=8, warps=16)))
+            impls.append(("gemv 16 features, 16 warps", lambda w: k.gemv(x, w, wide=16, warps=16)))
         if k.can_stream(x, ws[0]):
             ctas, stages, _, _ = k.stream_plan(a.M, a.N, a.K, False, a.ctas or None, a.ring * 1024 or None)
             impls.append((f"stream ctas={ctas} stages={stages}",
                           lambda w: k.gemm_stream(x, w, ctas=a.ctas or None, ring_bytes=a.ring * 1024 or None)))
+        if a.dual:                      # N rows of gate and up in blocks of 128, SiLU-mul in the epilogue
+            impls = [(f"gemv gate/up {wd} features", (lambda wd: lambda w: k.gemv(x, w, block=128, wide=wd))(wd)) for wd in (8, 16, 32)]
+            if a.M <= 8:
+                impls.append(("skinny_fused gate/up", lambda w: k.skinny_fused(x, w, block=128)))
         for name, fn in impls:
             if not name.startswith(a.only):
                 continue

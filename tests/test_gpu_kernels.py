@@ -237,10 +237,10 @@ def test_gemv(M, N, K, out_dtype):
     ref = plain_ops.linear(x, w, b, torch.float64)
     scale = ref.abs().max().item() * 8 if out_dtype == torch.float32 else None
     xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None
-    for wide in (8, 16, 32):
-        got = k().gemv(xd, wd, bd, out_dtype, wide=wide)
+    for wide, warps in ((8, 8), (16, 8), (32, 8), (8, 16), (16, 16)):
+        got = k().gemv(xd, wd, bd, out_dtype, wide=wide, warps=warps)
         close(got, ref, out_dtype, "gemv", scale=scale)
-        alone = k().gemv(xd[M - 1:].contiguous(), wd, bd, out_dtype, wide=wide)
+        alone = k().gemv(xd[M - 1:].contiguous(), wd, bd, out_dtype, wide=wide, warps=warps)
         if M <= 8:                                       # rows 8..15 sit in another accumulator half
             assert torch.equal(alone[0], got[M - 1])     # a row's result does not depend on its companions
     if out_dtype == torch.bfloat16:
