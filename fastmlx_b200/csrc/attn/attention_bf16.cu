@@ -346,7 +346,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int* block_tables, int bt_stride,
                    const int* row_start, const int* positions, bf16* out, float* part_o, float* part_ml, int nh, int nkv,
-                   int page_size, long long num_pages, float scale, int window, int* status, int* tickets) {
+                   int page_size, long long num_pages, float scale, int window, int* status, int* tickets,
+                   const float* __restrict__ inv_freq, int rot, int interleaved, int rope_mode) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   const int split = blockIdx.x, splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
@@ -381,6 +382,71 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   }
   pdl_wait();
 
+  const bf16* qbase = q + (long long)t * q_stride + (long long)g * rep * HD;
+  long long qhead_stride = HD;
+  if (rope_mode > 0) {
+    // q, k and v arrive as the projection left them: rotate the queries into shared memory, and
+    // let the block whose keys include the row's new one rotate that key and store it and
+    // its value in the cache, as the separate kernel would have.  The last stage of the ring
+    // is free until the first pass of the loop below: it holds the rotated queries meanwhile.
+    bf16* q_rot = stage_k(DECODE_STAGES - 1);          // [16][HD]
+    float* rope_sin = reinterpret_cast<float*>(q_rot + 16 * HD);
+    float* rope_cos = rope_sin + HD / 2;
+    static_assert(16 * HD * 2 + HD * 4 <= TILE * 2, "the rotated queries must fit one K tile");
+    const int half = rot / 2;
+    const float fpos = (float)pos;
+    for (int j = threadIdx.x; j < half; j += THREADS) sincosf(fpos * inv_freq[j], &rope_sin[j], &rope_cos[j]);
+    __syncthreads();
+    const bf16* row = q + (long long)t * q_stride;
+    for (int it = threadIdx.x; it < rep * (HD / 2); it += THREADS) {
+      const int h = it / (HD / 2), j = it - h * (HD / 2);
+      const bf16* src = qbase + (long long)h * HD;
+      bf16* dst = q_rot + h * HD;
+      if (j < half) {
+        const int i0 = interleaved ? 2 * j : j, i1 = interleaved ? 2 * j + 1 : j + half;
+        float x, y;
+        rope_pair(__bfloat162float(src[i0]), __bfloat162float(src[i1]), rope_sin[j], rope_cos[j], x, y);
+        dst[i0] = __float2bfloat16_rn(x);
+        dst[i1] = __float2bfloat16_rn(y);
+      } else {                                       // beyond the rotated part: two elements per item
+        const int e = rot + 2 * (j - half);
+        dst[e] = src[e];
+        dst[e + 1] = src[e + 1];
+      }
+    }
+    if (rope_mode == 1 && pos >= 0 && kbeg <= pos && pos < kend) {
+      const int blk = c.page_shift >= 0 ? pos >> c.page_shift : pos / page_size;
+      const int page = blk < bt_stride ? c.bt[blk] : -1;
+      if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) fmx_set_status(status, FMX_BAD_PAGE, page, r);
+      } else {
+        const int off = pos - blk * page_size;
+        const bf16* ksrc = row + (long long)(nh + g) * HD;
+        const bf16* vsrc = row + (long long)(nh + nkv + g) * HD;
+        bf16* kdst = const_cast<bf16*>(kv) + ((((long long)page * 2 + 0) * nkv + g) * page_size + off) * HD;
+        bf16* vdst = const_cast<bf16*>(kv) + ((((long long)page * 2 + 1) * nkv + g) * page_size + off) * HD;
+        for (int j = threadIdx.x; j < HD / 2; j += THREADS) {
+          if (j < half) {
+            const int i0 = interleaved ? 2 * j : j, i1 = interleaved ? 2 * j + 1 : j + half;
+            float x, y;
+            rope_pair(__bfloat162float(ksrc[i0]), __bfloat162float(ksrc[i1]), rope_sin[j], rope_cos[j], x, y);
+            kdst[i0] = __float2bfloat16_rn(x);
+            kdst[i1] = __float2bfloat16_rn(y);
+          } else {
+            const int e = rot + 2 * (j - half);
+            kdst[e] = ksrc[e];
+            kdst[e + 1] = ksrc[e + 1];
+          }
+          vdst[2 * j] = vsrc[2 * j];
+          vdst[2 * j + 1] = vsrc[2 * j + 1];
+        }
+        __threadfence();                             // the tile loads below read the new key through L2
+      }
+    }
+    __syncthreads();
+    qbase = q_rot;
+  }
+
   unsigned qf[KSTEPS][4];
 #pragma unroll
   for (int k = 0; k < KSTEPS; ++k)
@@ -388,7 +454,7 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
     for (int x = 0; x < 2; ++x) {
       const int hrow = gq + 8 * x;
       const bool ok = hrow < rep;
-      const bf16* qp = q + (long long)t * q_stride + (long long)(g * rep + (ok ? hrow : 0)) * HD + 16 * k + 2 * tq;
+      const bf16* qp = qbase + (long long)(ok ? hrow : 0) * qhead_stride + 16 * k + 2 * tq;
       qf[k][x] = ok ? *reinterpret_cast<const unsigned*>(qp) : 0u;
       qf[k][x + 2] = ok ? *reinterpret_cast<const unsigned*>(qp + 8) : 0u;
     }
@@ -587,8 +653,10 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
                                int bt_stride, const int* row_start, const int* positions, void* out, float* scratch,
                                long long scratch_floats, int* tickets, int rows, int splits, int nh, int nkv,
                                int page_size, long long num_pages, float scale, int window, int* status,
-                               cudaStream_t stream) {
+                               const float* inv_freq, int rot, int interleaved, int rope_mode, cudaStream_t stream) {
   if (rows == 0) return 0;
+  if (rope_mode < 0 || rope_mode > 2 || (rope_mode > 0 && (rot < 0 || rot > HD || (rot & 1) || (rot > 0 && inv_freq == nullptr))))
+    return fmx_fail("fmx_attn_decode: bad rotary arguments mode=%d rot=%d", rope_mode, rot);
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || splits <= 0)
     return fmx_fail("fmx_attn_decode: bad sizes rows=%d nh=%d nkv=%d page=%d splits=%d", rows, nh, nkv, page_size, splits);
   if (nh / nkv > 16) return fmx_fail("fmx_attn_decode: %d query heads per kv head is above 16", nh / nkv);
@@ -609,7 +677,7 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
   dim3 grid(splits, nkv, rows);
   fmx_launch(attn_decode_kernel, grid, dim3(THREADS), decode_smem(), stream,
       (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
-      part_ml, nh, nkv, page_size, num_pages, scale, window, status, tickets);
+      part_ml, nh, nkv, page_size, num_pages, scale, window, status, tickets, inv_freq, rot, interleaved, rope_mode);
   FMX_LAUNCH_CHECK();
   if (splits > 1 && tickets == nullptr) {
     fmx_launch(attn_combine_kernel, dim3(nh, rows), dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)part_o,
@@ -681,7 +749,7 @@ FMX_EXPORT int fmx_attn_decode_noalloc(const void* q, long long q_stride, const 
   dim3 grid(splits, nkv, rows);
   attn_decode_kernel<<<grid, THREADS, decode_smem(), stream>>>(
       (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
-      part_ml, nh, nkv, page_size, num_pages, scale, window, status, (int*)nullptr);
+      part_ml, nh, nkv, page_size, num_pages, scale, window, status, (int*)nullptr, (const float*)nullptr, 0, 0, 0);
   FMX_LAUNCH_CHECK();
   if (splits > 1) {
     attn_combine_kernel<<<dim3(nh, rows), HD < 128 ? 64 : 128, 0, stream>>>(part_o, part_ml, row_start, (bf16*)out, nh,

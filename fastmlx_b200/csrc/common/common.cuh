@@ -57,6 +57,13 @@ template <int BLOCK> __device__ __forceinline__ float block_sum(float v) {
   return r;
 }
 
+// One rotary pair, with the arithmetic pinned (no contraction left to the compiler) so that
+// every kernel that rotates gets the same bits: (a, b) -> (a c - b s, b c + a s).
+__device__ __forceinline__ void rope_pair(float a, float b, float s, float c, float& x, float& y) {
+  x = __fmaf_rn(a, c, -__fmul_rn(b, s));
+  y = __fmaf_rn(b, c, __fmul_rn(a, s));
+}
+
 // Programmatic dependent launch.  A kernel launched through fmx_launch may be scheduled
 // while the kernel before it in the stream is still running: it does what needs no input
 // from its predecessor (index arithmetic, reading weights), calls pdl_wait() before it reads

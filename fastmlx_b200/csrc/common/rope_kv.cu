@@ -26,8 +26,10 @@ __global__ void rope_kv_write_kernel(T* qkv, const int* __restrict__ positions, 
       const float a = to_f(p[i0]), b = to_f(p[i1]);
       float s, c;
       sincosf(pos * inv_freq[j], &s, &c);
-      p[i0] = from_f<T>(a * c - b * s);
-      p[i1] = from_f<T>(b * c + a * s);
+      float x, y;
+      rope_pair(a, b, s, c, x, y);
+      p[i0] = from_f<T>(x);
+      p[i1] = from_f<T>(y);
     }
   }
   if (kv == nullptr || slot_mapping == nullptr || nkv == 0) return;
@@ -94,8 +96,11 @@ rope_kv_write_bf16_vec_kernel(bf16* qkv, const int* positions, const float* __re
           const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
           const int j = 8 * c + 2 * e;
           const float s0 = sc[j], c0 = sc[half + j], s1 = sc[j + 1], c1 = sc[half + j + 1];
-          a2[e] = __floats2bfloat162_rn(fa.x * c0 - fb.x * s0, fa.y * c1 - fb.y * s1);
-          b2[e] = __floats2bfloat162_rn(fb.x * c0 + fa.x * s0, fb.y * c1 + fa.y * s1);
+          float x0, y0, x1, y1;
+          rope_pair(fa.x, fb.x, s0, c0, x0, y0);
+          rope_pair(fa.y, fb.y, s1, c1, x1, y1);
+          a2[e] = __floats2bfloat162_rn(x0, x1);
+          b2[e] = __floats2bfloat162_rn(y0, y1);
         }
         *reinterpret_cast<uint4*>(p + 8 * c) = a;
         *reinterpret_cast<uint4*>(p + half + 8 * c) = b;

@@ -285,6 +285,8 @@ def stream_workspace(device):
     return ws
 
 
+_FUSE_ROPE = _os.environ.get("FASTMLX_FUSE_ROPE", "1") != "0"     # decode attention rotates and stores by itself
+
 # which kernel multiplies the few rows of a decode step: "gemv" (whole K per block), "skinny"
 # (16-row tiles, K split over blocks), "stream" (TMA ring + tcgen05)
 _DECODE_GEMM = _os.environ.get("FASTMLX_DECODE_GEMM", "gemv")
@@ -460,8 +462,11 @@ def attn_decode_scratch_floats(rows: int, nkv: int, splits: int, hd: int) -> int
     return 0 if splits <= 1 else rows * nkv * splits * 16 * (hd + 2)
 
 
-def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, splits=None) -> torch.Tensor:
-    """Every row brings one token: split over the keys, all query heads of a kv head together."""
+def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, splits=None, rope=None) -> torch.Tensor:
+    """Every row brings one token: split over the keys, all query heads of a kv head together.
+    rope = (inv_freq or None, rotary_dim, traditional, store): qkv is as the projection left it;
+    the kernel rotates the queries itself and, if `store`, rotates each row's new key and puts
+    it and its value into the cache (what rope_kv_write does in a kernel of its own)."""
     T = qkv.shape[0]
     R = ctx.R
     out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
@@ -471,10 +476,14 @@ def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, spli
     scratch = attention_scratch(qkv.device, need) if need else None
     tickets = attention_tickets(qkv.device) if need and R * nkv <= ATTN_TICKETS else None
     bt = group.block_tables
+    inv_freq, rot, trad, mode = None, 0, False, 0
+    if rope is not None:
+        inv_freq, rot, trad, store = rope
+        mode = 1 if store else 2
     call(f"attn_hd{hd}", "fmx_attn_decode", qkv.data_ptr(), qkv.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
          ctx.row_start.data_ptr(), ctx.positions.data_ptr(), out.data_ptr(), _ptr(scratch),
          scratch.numel() if scratch is not None else 0, _ptr(tickets), R, splits, nh, nkv, kv.shape[3], kv.shape[0],
-         float(scale), int(window), _ptr(ctx.status), _stream())
+         float(scale), int(window), _ptr(ctx.status), _ptr(inv_freq), int(rot), 1 if trad else 0, mode, _stream())
     return out
 
 
@@ -520,7 +529,14 @@ def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale) -> torch
     return out
 
 
-def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Tensor:
+def decode_attention_fuses_rope(qkv, kv, ctx, nh, nkv, hd) -> bool:
+    """Will `paged_attention` take this step on the split decode kernel, which can rotate q and
+    k and store k and v itself?"""
+    return (_FUSE_ROPE and qkv.is_cuda and qkv.dtype == torch.bfloat16 and kv is not None and kv.dtype == qkv.dtype
+            and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0 and ctx.all_decode and nh // nkv <= 16)
+
+
+def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window, rope=None) -> torch.Tensor:
     """Attention of every token of the step over the pages of its own request.
     qkv[T, >= nh*hd] holds the (rotated) queries first; -> [T, nh*hd].  bfloat16 with a head
     size in steps of 16 (at most 256) runs on the tensor cores; everything else, and all
@@ -529,7 +545,10 @@ def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Te
     assert kv.is_contiguous() and kv.dtype == qkv.dtype and qkv.stride(1) == 1
     if qkv.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0:
         if ctx.all_decode and nh // nkv <= 16:
-            return paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
+            return paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, rope=rope)
+    if rope is not None:
+        raise KernelError("only the split decode kernel rotates by itself: ask decode_attention_fuses_rope first")
+    if qkv.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0:
         if _use_tc_attention(hd) and ctx.max_q_len >= TC_ATTN_MIN_TOKENS and tc_attention_ok(nh, nkv, hd, kv.shape[3], window) \
                 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
             return paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale)

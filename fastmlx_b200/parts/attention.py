@@ -48,6 +48,17 @@ class GQAAttention(Mixer):
         return self.o.forward(self._attend(self.qkv.forward(x), ctx, cache))
 
     def _attend(self, qkv, ctx, cache):
+        k = self.rt.k
+        fuses = getattr(k, "decode_attention_fuses_rope", None)
+        rope = None
+        if fuses is not None and fuses(qkv, cache.kv, ctx, self.nh, self.nkv, self.hd):
+            rope = self.pos.fused_args(cache)
+        if rope is not None:
+            # decode steps: the attention kernel rotates q and the new k and stores k and v itself
+            if self.share_kv:
+                rope = rope[:3] + (False,)
+            return k.paged_attention(qkv, cache.kv, ctx, ctx.groups[cache.group], self.nh, self.nkv, self.hd,
+                                     self.scale, self.window, rope=rope)
         self.pos.apply_and_store(qkv, ctx, cache, self.nh, 0 if self.share_kv else self.nkv, self.hd)
         return self.rt.k.paged_attention(qkv, cache.kv, ctx, ctx.groups[cache.group],
                                          self.nh, self.nkv, self.hd, self.scale, self.window)

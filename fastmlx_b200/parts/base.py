@@ -157,6 +157,11 @@ class PositionEncoding(Part):
     def apply_and_store(self, qkv, ctx, cache, nh: int, nkv: int, hd: int) -> None:  # pragma: no cover
         raise NotImplementedError
 
+    def fused_args(self, cache):
+        """If a mixer's kernel may do this part's work itself: (frequencies or None, rotated
+        width, traditional pairing, whether to store k and v); else None."""
+        return None
+
 
 @dataclass(frozen=True)
 class Run:

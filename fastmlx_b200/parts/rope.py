@@ -57,6 +57,12 @@ class RotaryEmbedding(PositionEncoding):
             nh, nkv, hd, ctx.status)
 
 
+    def fused_args(self, cache):
+        """What a mixer kernel needs to rotate and store by itself: (frequencies, rotated
+        width, pairing, whether to store k and v)."""
+        return (self.inv_freq, self.rotary_dim, self.traditional, bool(cache.kv is not None and cache.writable))
+
+
 class NoPositionEncoding(PositionEncoding):
     """Stores k and v unrotated (a mixer whose positions come from elsewhere)."""
 
@@ -67,3 +73,6 @@ class NoPositionEncoding(PositionEncoding):
             g.slot_mapping if (g is not None and cache.writable) else None,
             cache.kv if cache.writable else None,
             nh, nkv, hd, ctx.status)
+
+    def fused_args(self, cache):
+        return (None, 0, False, bool(cache.kv is not None and cache.writable))

@@ -529,6 +529,40 @@ def test_split_decode_attention(nh, nkv, hd, page_size, window, splits):
     close(got, ref, torch.bfloat16, "split decode attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES)
+@pytest.mark.parametrize("rot_frac,traditional", [(1.0, False), (0.5, False), (1.0, True), (0.0, False)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_decode_attention_rotates_and_stores_by_itself(nh, nkv, hd, page_size, rot_frac, traditional, splits):
+    """The decode kernel given q, k, v as the projection left them: the same bits, in its
+    output and in the cache, as the rotary kernel followed by the decode kernel."""
+    rows = [(0, 1), (1, 1), (63, 1), (64, 1), (65, 1), (300, 1), (1000, 1), (127, 1)]
+    _, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, 0)
+    rot = int(hd * rot_frac) // 2 * 2
+    inv = (10000.0 ** (-torch.arange(0, rot, 2, dtype=torch.float64) / max(rot, 1))).float().to(DEV) if rot else None
+    qkv = rnd(len(rows), (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=77).to(DEV)
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    bt = grp.block_tables
+    slots = torch.tensor([int(bt[r, c // page_size]) * page_size + c % page_size for r, (c, _) in enumerate(rows)],
+                         dtype=torch.int64, device=DEV)
+    # the two kernels
+    qkv_a, kv_a = qkv.clone(), kv.to(DEV).clone()
+    k().rope_kv_write(qkv_a, dctx.positions, inv, rot, traditional, slots, kv_a, nh, nkv, hd, dctx.status)
+    want = k().paged_attention_decode(qkv_a, kv_a, dctx, dgrp, nh, nkv, hd, hd ** -0.5, 0, splits=splits)
+    # the one
+    qkv_b, kv_b = qkv.clone(), kv.to(DEV).clone()
+    got = k().paged_attention_decode(qkv_b, kv_b, dctx, dgrp, nh, nkv, hd, hd ** -0.5, 0, splits=splits,
+                                     rope=(inv, rot, traditional, True))
+    assert dctx.status.tolist()[0] == 0
+    assert torch.equal(kv_a, kv_b), "the cache holds other bits"
+    assert torch.equal(got, want)
+    assert torch.equal(qkv_b, qkv), "the fused kernel must leave qkv alone"
+    # queries only (a layer that reads another layer's cache): the cache stays as it is
+    kv_c = kv_a.clone()
+    got_q = k().paged_attention_decode(qkv.clone(), kv_c, dctx, dgrp, nh, nkv, hd, hd ** -0.5, 0, splits=splits,
+                                       rope=(inv, rot, traditional, False))
+    assert torch.equal(kv_c, kv_a) and torch.equal(got_q, want)
+
+
 TC_SHAPES = [(4, 1, 64, 16), (8, 2, 64, 16), (32, 8, 64, 16), (8, 8, 64, 32), (16, 1, 64, 128), (8, 2, 128, 16),
              (24, 24, 128, 64), (16, 2, 128, 8)]
 
