@@ -20,6 +20,7 @@
 // status word and the CTA frees its tensor memory and returns.  No cluster, no multicast.
 #include <cuda.h>
 #include <math.h>
+#include <type_traits>
 #include "common.cuh"
 
 #ifndef FMX_HD
@@ -414,6 +415,330 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 }
 
+#if FMX_HD == 64
+// ------------------------------------------------------------------------------------
+// Two query tiles per CTA (head size 64).  The CTA owns 256 packed query rows: tile A (rows
+// 0-127) and tile B (rows 128-255) share every K/V tile that TMA brings, and each has a
+// softmax group of four warps with one thread per query row, so no row statistic ever
+// crosses a thread.  While one group works on its scores the tensor core computes the other
+// tile's, and K and V are read from shared memory once for 256 rows.
+//   tensor memory: S_A 0..127, S_B 128..255, O_A[2] at 256 and 320, O_B[2] at 384 and 448.
+//   shared memory: Q_A, Q_B (16 KB each), three K/V stages (32 KB each), P_A, P_B (32 KB each).
+// A softmax thread reads its row of scores twice from tensor memory, 32 columns at a time
+// (once for the maximum, once for the exponentials), which keeps it at 64 output and 32
+// score registers.
+namespace two {
+constexpr int KV_ST = 3;
+constexpr int THREADS2 = 320;                   // producer, MMA issuer, 4 + 4 softmax warps
+constexpr int GROUP_THREADS = 128;
+constexpr size_t SMEM2 = 2 * (size_t)Q_BYTES + (size_t)KV_ST * (K_BYTES + V_BYTES) + 2 * (size_t)P_BYTES + 1024 + 512;
+constexpr int S2_COL = 0, O2_COL = 256;
+
+struct Bars2 {
+  uint64_t q_full;
+  uint64_t kv_full[KV_ST], kv_empty[KV_ST];
+  uint64_t s_full[2], s_empty[2];               // per query tile
+  uint64_t p_full[2], p_empty[2];
+  uint64_t o_full[2][2], o_empty[2][2];         // [query tile][buffer]
+  uint32_t tmem_slot;
+};
+
+__global__ void __launch_bounds__(THREADS2, 1)
+attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                        const int* block_tables, int bt_stride, const int* row_start, const int* row_ctx, bf16* out,
+                        int nh, int nkv, int page_size, long long num_pages, long long kv_rows, float scale,
+                        int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sq = smem;                                             // [2] query tiles
+  unsigned char* skv = sq + 2 * Q_BYTES;                                // [stage][K | V]
+  unsigned char* sp = skv + (size_t)KV_ST * (K_BYTES + V_BYTES);        // [2] probabilities
+  Bars2* bars = reinterpret_cast<Bars2*>(sp + 2 * (size_t)P_BYTES);
+
+  // the last query tiles of a row see the most keys: they start first
+  const int r = blockIdx.z, g = blockIdx.y, pair = gridDim.x - 1 - blockIdx.x;
+  const int rep = nh / nkv;
+  const int tok_per_tile = BM / rep;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bars->q_full), 1);
+    for (int s = 0; s < KV_ST; ++s) {
+      mbar_init(smem_u32(&bars->kv_full[s]), 1);
+      mbar_init(smem_u32(&bars->kv_empty[s]), 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(smem_u32(&bars->s_full[x]), 1);
+      mbar_init(smem_u32(&bars->s_empty[x]), GROUP_THREADS);
+      mbar_init(smem_u32(&bars->p_full[x]), GROUP_THREADS);
+      mbar_init(smem_u32(&bars->p_empty[x]), 1);
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(smem_u32(&bars->o_full[x][i]), 1);
+        mbar_init(smem_u32(&bars->o_empty[x][i]), GROUP_THREADS);
+      }
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_slot;
+  pdl_wait();
+  pdl_trigger();
+
+  const int t0 = row_start[r], q_len = row_start[r + 1] - t0, ctx = row_ctx[r];
+  // per query tile: first token, tokens, one past the last key any of its rows sees, key tiles
+  const int tok0_a = 2 * pair * tok_per_tile, tok0_b = tok0_a + tok_per_tile;
+  const bool act_a = tok0_a < q_len && ctx >= 0, act_b = tok0_b < q_len && ctx >= 0;
+  const int n_tok_a = act_a ? min(tok_per_tile, q_len - tok0_a) : 0, n_tok_b = act_b ? min(tok_per_tile, q_len - tok0_b) : 0;
+  const int kend_a = ctx + tok0_a + n_tok_a, kend_b = ctx + tok0_b + n_tok_b;
+  const int n_tiles_a = act_a ? (kend_a + BN - 1) / BN : 0, n_tiles_b = act_b ? (kend_b + BN - 1) / BN : 0;
+  const int n_all = max(n_tiles_a, n_tiles_b);         // tile B sees at least what A sees
+  const int kend_all = max(act_a ? kend_a : 0, act_b ? kend_b : 0);
+  const int pages_per_tile = BN / page_size;
+
+  if (warp == 0 && lane == 0 && n_all > 0) {
+    // ------------------------------------------------------------------ producer
+    const int* bt = block_tables + (long long)r * bt_stride;
+    mbar_expect_tx(smem_u32(&bars->q_full), 2 * Q_BYTES);
+#pragma unroll
+    for (int x = 0; x < 2; ++x)             // a tile past the row's end reads as zeros
+      tma_load_3d(smem_u32(sq + x * Q_BYTES), &map_q, 0, g * rep, t0 + (x ? tok0_b : tok0_a), smem_u32(&bars->q_full));
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int j = 0; j < n_all && ok; ++j) {
+      if (!mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1)) { ok = false; break; }
+      const uint32_t fb = smem_u32(&bars->kv_full[stage]);
+      unsigned char* sk = skv + (size_t)stage * (K_BYTES + V_BYTES);
+      unsigned char* sv = sk + K_BYTES;
+      mbar_expect_tx(fb, K_BYTES + V_BYTES);
+      for (int pi = 0; pi < pages_per_tile; ++pi) {
+        const int key0 = j * BN + pi * page_size;
+        long long krow = kv_rows, vrow = kv_rows;           // out of bounds: the box reads as zeros
+        if (key0 < kend_all) {
+          const int blk = key0 / page_size;
+          const int page = blk < bt_stride ? bt[blk] : -1;
+          if (page < 0 || page >= num_pages) {
+            fmx_set_status(status, FMX_BAD_PAGE, page, r);
+          } else {
+            krow = (((long long)page * 2 + 0) * nkv + g) * page_size;
+            vrow = (((long long)page * 2 + 1) * nkv + g) * page_size;
+          }
+        }
+        const int off = pi * page_size * 128;               // rows of 128 bytes
+        tma_load_2d(smem_u32(sk + off), &map_kv, 0, (int)krow, fb);
+        tma_load_2d(smem_u32(sv + off), &map_kv, 0, (int)vrow, fb);
+      }
+      if (++stage == KV_ST) { stage = 0; phase ^= 1; }
+    }
+    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 21, blockIdx.x);
+  } else if (warp == 1 && lane == 0 && n_all > 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc_qk = idesc_f16(BM, BN, 0), idesc_pv = idesc_f16(BM, HD, 1);
+    bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
+    tc_fence_after();
+    auto issue_qk = [&](int x, int j) -> bool {
+      const int st = j % KV_ST;
+      if (!mbar_wait(smem_u32(&bars->s_empty[x]), (uint32_t)((j & 1) ^ 1))) return false;
+      tc_fence_after();
+      const uint32_t qa = smem_u32(sq + x * Q_BYTES), ka = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES));
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4)
+        umma(tmem + S2_COL + x * BN, desc_kmajor(qa) + 2 * k4, desc_kmajor(ka) + 2 * k4, idesc_qk, k4 ? 1u : 0u);
+      umma_commit(smem_u32(&bars->s_full[x]));
+      return true;
+    };
+    auto issue_pv = [&](int x, int j) -> bool {
+      const int st = j % KV_ST, ob = j & 1;
+      if (!mbar_wait(smem_u32(&bars->p_full[x]), (uint32_t)(j & 1))) return false;
+      if (!mbar_wait(smem_u32(&bars->o_empty[x][ob]), (uint32_t)(((j >> 1) & 1) ^ 1))) return false;
+      tc_fence_after();
+      const uint32_t pa = smem_u32(sp + (size_t)x * P_BYTES);
+      const uint32_t va = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES) + K_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb)          // 64 keys each
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)        // 16 keys each
+          umma(tmem + O2_COL + (x * 2 + ob) * HD, desc_kmajor(pa + kb * TILE_BYTES) + 2 * k4,
+               desc_mnmajor(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (kb | k4) ? 1u : 0u);
+      umma_commit(smem_u32(&bars->o_full[x][ob]));
+      umma_commit(smem_u32(&bars->p_empty[x]));
+      return true;
+    };
+    for (int j = 0; j < n_all && ok; ++j) {
+      const int st = j % KV_ST;
+      if (!mbar_wait(smem_u32(&bars->kv_full[st]), (uint32_t)((j / KV_ST) & 1))) { ok = false; break; }
+      tc_fence_after();
+      if (j < n_tiles_a) ok = issue_qk(0, j);
+      if (ok && j < n_tiles_b) ok = issue_qk(1, j);
+      if (j > 0 && ok) {
+        if (j - 1 < n_tiles_a) ok = issue_pv(0, j - 1);
+        if (ok && j - 1 < n_tiles_b) ok = issue_pv(1, j - 1);
+        if (ok) umma_commit(smem_u32(&bars->kv_empty[(j - 1) % KV_ST]));
+      }
+    }
+    if (ok) {
+      if (n_all - 1 < n_tiles_a) ok = issue_pv(0, n_all - 1);
+      if (ok && n_all - 1 < n_tiles_b) ok = issue_pv(1, n_all - 1);
+      if (ok) umma_commit(smem_u32(&bars->kv_empty[(n_all - 1) % KV_ST]));
+    }
+    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 22, blockIdx.x);
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ softmax and epilogue
+    const int x = (warp - 2) >> 2;                       // query tile of this group
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                 // this thread's packed row and tensor-memory lane
+    const int tok = row / rep, head = g * rep + row - tok * rep;
+    const int tok0 = x ? tok0_b : tok0_a, n_tok = x ? n_tok_b : n_tok_a;
+    const bool rvalid = tok < n_tok;
+    const int lim = rvalid ? ctx + tok0 + tok : -1;      // last key this row sees
+    const float sl2 = scale * LOG2E;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_addr = lane_addr + S2_COL + x * BN;
+    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    bool ok = true;
+    const int nt = x ? n_tiles_b : n_tiles_a;
+
+    auto take_output = [&](int j, float alpha) -> bool {   // o = o * alpha + (P_j V_j)[row]
+      const int ob = j & 1;
+      if (!mbar_wait(smem_u32(&bars->o_full[x][ob]), (uint32_t)((j >> 1) & 1))) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + O2_COL + (x * 2 + ob) * HD + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, __uint_as_float(v[i]));
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars->o_empty[x][ob]));
+      return true;
+    };
+
+    for (int j = 0; j < nt && ok; ++j) {
+      const int st = j % KV_ST;
+      if (!mbar_wait(smem_u32(&bars->s_full[x]), (uint32_t)(j & 1))) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = j * BN;
+      const bool need_mask = key0 + BN - 1 > ctx + tok0;     // some row of the tile does not see the whole tile
+      // first pass: the row's maximum (tiles left of the diagonal need no mask)
+      float mx = -INFINITY;
+      if (!need_mask) {
+#pragma unroll
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(s_addr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(s_addr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, key0 + c + i <= lim ? __uint_as_float(v[i]) : -INFINITY);
+        }
+      }
+      mx *= sl2;                                         // scale > 0: the maximum commutes with it
+      const float m_new = fmaxf(m, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = fast_exp2(m - m_use);
+      m = m_new;
+      if (!mbar_wait(smem_u32(&bars->p_empty[x]), (uint32_t)((j & 1) ^ 1))) { ok = false; break; }
+      // second pass: probabilities to shared memory (K-major, 128-byte rows, swizzled by row)
+      float sum = 0.f;
+      auto second_pass = [&](auto masked) {
+        constexpr bool MASKED = decltype(masked)::value;
+#pragma unroll
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(s_addr + c, v);
+          tmem_ld_wait();
+          unsigned char* prow = sp + (size_t)x * P_BYTES + (c >> 6) * TILE_BYTES + row * 128;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            float pr[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int col = c + 8 * ch + i;
+              float sc = fmaf(__uint_as_float(v[8 * ch + i]), sl2, -m_use);
+              if (MASKED && key0 + col > lim) sc = -INFINITY;
+              pr[i] = fast_exp2(sc);
+              sum += pr[i];
+            }
+            uint4 w;
+            w.x = pack2(pr[0], pr[1]);
+            w.y = pack2(pr[2], pr[3]);
+            w.z = pack2(pr[4], pr[5]);
+            w.w = pack2(pr[6], pr[7]);
+            const int chunk = ((c & 63) >> 3) + ch;     // 16-byte chunk within the 128-byte row
+            *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+          }
+        }
+      };
+      if (need_mask) second_pass(std::true_type{});
+      else second_pass(std::false_type{});
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars->s_empty[x]));          // the scores have been read twice: free for tile j + 1
+      l = l * alpha + sum;
+      if (key0 + BN > kend_all) {
+        // keys past the last visible one share pages with stale rows: their values must be
+        // zeros, since 0 * NaN would poison the product (both groups write the same zeros)
+        if (!mbar_wait(smem_u32(&bars->kv_full[st]), (uint32_t)((j / KV_ST) & 1))) { ok = false; break; }
+        unsigned char* sv = skv + (size_t)st * (K_BYTES + V_BYTES) + K_BYTES;
+        if (key0 + row >= kend_all) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(sv + row * 128 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(smem_u32(&bars->p_full[x]));
+      // one tile behind: add the previous tile's output
+      if (j > 0) ok = take_output(j - 1, alpha_prev);
+      alpha_prev = alpha;
+    }
+    if (ok && nt > 0) ok = take_output(nt - 1, alpha_prev);
+    if (!ok) {
+      if (lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 23, blockIdx.x);
+    } else if (rvalid) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      bf16* op = out + ((long long)(t0 + tok0 + tok) * nh + head) * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 8) {
+        uint4 w;
+        w.x = pack2(o[c] * inv, o[c + 1] * inv);
+        w.y = pack2(o[c + 2] * inv, o[c + 3] * inv);
+        w.z = pack2(o[c + 4] * inv, o[c + 5] * inv);
+        w.w = pack2(o[c + 6] * inv, o[c + 7] * inv);
+        *reinterpret_cast<uint4*>(op + c) = w;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+}  // namespace two
+#endif
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -435,11 +760,12 @@ FMX_EXPORT int fmx_attn_prefill_tc_available() { return 1; }
 
 // As fmx_attn_prefill, without a window, for nh / nkv in {1, 2, 4, 8, 16} and a page size
 // that divides 128 and is at least 8.  q rows (tokens) are T; the out-of-range part of the
-// last query tile reads as zeros.
+// last query tile reads as zeros.  variant 1: one query tile per CTA; otherwise two where the
+// head size has that kernel (64).
 FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, const void* kv, const int* block_tables,
                                    int bt_stride, const int* row_start, const int* row_ctx, void* out, int rows,
                                    int max_q_len, int nh, int nkv, int page_size, long long num_pages, float scale,
-                                   int* status, cudaStream_t stream) {
+                                   int variant, int* status, cudaStream_t stream) {
   if (rows == 0 || max_q_len == 0) return 0;
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv) return fmx_fail("fmx_attn_prefill_tc: bad sizes rows=%d nh=%d nkv=%d", rows, nh, nkv);
   const int rep = nh / nkv;
@@ -479,6 +805,24 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
     configured = true;
   }
   const int tok_per_tile = BM / rep;
+#if FMX_HD == 64
+  if (variant != 1) {                         // two query tiles per CTA
+    static bool configured2 = false;
+    if (!configured2) {
+      cudaError_t e2 = cudaFuncSetAttribute(two::attn_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)two::SMEM2);
+      if (e2 != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: %zu bytes of shared memory refused: %s", two::SMEM2,
+                                             cudaGetErrorString(e2));
+      configured2 = true;
+    }
+    dim3 grid2((max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile), nkv, rows);
+    cudaError_t e2 = fmx_launch(two::attn_prefill_tc2_kernel, grid2, dim3(two::THREADS2), two::SMEM2, stream, map_q, map_kv,
+                                block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size, num_pages,
+                                kv_rows, scale, status);
+    if (e2 != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launch failed: %s", cudaGetErrorString(e2));
+    return 0;
+  }
+#endif
   dim3 grid((max_q_len + tok_per_tile - 1) / tok_per_tile, nkv, rows);
   cudaError_t e = fmx_launch(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, map_q, map_kv, block_tables,
                              bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size, num_pages, kv_rows, scale, status);
@@ -489,7 +833,7 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
 #include "common.cuh"
 FMX_EXPORT int fmx_attn_prefill_tc_available() { return 0; }
 FMX_EXPORT int fmx_attn_prefill_tc(const void*, long long, int, const void*, const int*, int, const int*, const int*, void*,
-                                   int, int, int, int, int, long long, float, int*, cudaStream_t) {
+                                   int, int, int, int, int, long long, float, int, int*, cudaStream_t) {
   return fmx_fail("fmx_attn_prefill_tc: this head size has no tensor-memory attention kernel");
 }
 #endif

@@ -517,7 +517,7 @@ def tc_attention_ok(nh: int, nkv: int, hd: int, page_size: int, window: int) -> 
             and page_size >= 8 and 128 % page_size == 0)
 
 
-def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale) -> torch.Tensor:
+def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale, variant: int = 0) -> torch.Tensor:
     """Causal attention of prompt portions on the tcgen05 tensor cores (TMA-fed, scores and
     outputs in tensor memory)."""
     T = qkv.shape[0]
@@ -525,7 +525,7 @@ def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale) -> torch
     bt = group.block_tables
     call(f"attn_hd{hd}", "fmx_attn_prefill_tc", qkv.data_ptr(), qkv.stride(0), T, kv.data_ptr(), bt.data_ptr(),
          bt.stride(0), ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), out.data_ptr(), ctx.R, int(ctx.max_q_len), nh,
-         nkv, kv.shape[3], kv.shape[0], float(scale), _ptr(ctx.status), _stream())
+         nkv, kv.shape[3], kv.shape[0], float(scale), int(variant), _ptr(ctx.status), _stream())
     return out
 
 

@@ -42,7 +42,7 @@ _SIGNATURES = {
         "fmx_gemm_stream": [_P, _L, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P, _L, _P, _P],
     },
     "attn": {
-        "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _P, _P],
+        "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
         "fmx_attn_prefill": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
         "fmx_attn_decode": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I, _I, _P],
     },

@@ -97,7 +97,11 @@ def main(argv=None) -> int:
         flops = 4 * a.nh * a.hd * a.batch * (a.qlen * a.ctx + a.qlen * (a.qlen + 1) / 2)
         impls = [("mma.sync", lambda: k.paged_attention_prefill(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, 0))]
         if k.tc_attention_ok(a.nh, a.nkv, a.hd, a.page, 0):
-            impls.append(("tcgen05", lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5)))
+            impls.append(("tcgen05, one query tile per CTA",
+                          lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, variant=1)))
+            if a.hd == 64:
+                impls.append(("tcgen05, two query tiles per CTA",
+                              lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, variant=0)))
         for name, f in impls:
             us = _time_graph(f, a.launches, a.replays)
             print(f"attn_prefill {name} B={a.batch} ctx={a.ctx} qlen={a.qlen} nh={a.nh} nkv={a.nkv} hd={a.hd}: {us:.1f} us, "

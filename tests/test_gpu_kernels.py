@@ -567,8 +567,9 @@ TC_SHAPES = [(4, 1, 64, 16), (8, 2, 64, 16), (32, 8, 64, 16), (8, 8, 64, 32), (1
              (24, 24, 128, 64), (16, 2, 128, 8)]
 
 
+@pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("nh,nkv,hd,page_size", TC_SHAPES)
-def test_tensor_memory_prefill_attention(nh, nkv, hd, page_size):
+def test_tensor_memory_prefill_attention(nh, nkv, hd, page_size, variant):
     """The tcgen05 attention kernel on portions with and without earlier context, single
     tokens, rows that end inside a 128-row tile and inside a 128-key tile."""
     rows = [(0, 37), (90, 1), (31, 2), (0, 1), (15, 17), (64, 1), (200, 130), (0, 128), (127, 129), (0, 300)]
@@ -576,13 +577,15 @@ def test_tensor_memory_prefill_attention(nh, nkv, hd, page_size):
     ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, 0)
     dctx, dgrp = _full_ctx(rows, ctx, grp)
     assert k().tc_attention_ok(nh, nkv, hd, page_size, 0)
-    got = k().paged_attention_prefill_tc(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5)
+    # variant 0: two query tiles per CTA where the head size has that kernel; 1: always one
+    got = k().paged_attention_prefill_tc(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, variant=variant)
     assert dctx.status.tolist()[0] == 0
     close(got, ref, torch.bfloat16, "tensor-memory attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
 
 
+@pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("key_pos", [0, 15, 16, 127, 128, 129, 255, 256, 511, 700])
-def test_tensor_memory_attention_far_key_and_unseen_keys(key_pos):
+def test_tensor_memory_attention_far_key_and_unseen_keys(key_pos, variant):
     """One key among 701 dominates for one head (a tile edge or a page edge that loses it shows
     at once); pages hold NaN wherever a key is out of sight."""
     nh, nkv, hd, page_size = 8, 2, 64, 16
@@ -596,7 +599,7 @@ def test_tensor_memory_attention_far_key_and_unseen_keys(key_pos):
             p = int(grp.block_tables[r, j // page_size])
             poisoned[p, :, :, j % page_size] = kv[p, :, :, j % page_size]
     dctx, dgrp = _full_ctx(rows, ctx, grp)
-    got = k().paged_attention_prefill_tc(q.to(DEV), poisoned.to(DEV), dctx, dgrp, nh, nkv, hd, 1.0)
+    got = k().paged_attention_prefill_tc(q.to(DEV), poisoned.to(DEV), dctx, dgrp, nh, nkv, hd, 1.0, variant=variant)
     assert torch.isfinite(got).all()
     close(got, ref, torch.bfloat16, "dominant key", scale=7.0)
 
