@@ -116,6 +116,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+// 64 columns: two 32-column loads in flight under one wait.
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+  uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+  uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+  tmem_ld32(taddr, lo);
+  tmem_ld32(taddr + 32, hi);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // 2^x by the special-function unit (about two units in the last place; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -422,11 +440,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // softmax group of four warps with one thread per query row, so no row statistic ever
 // crosses a thread.  While one group works on its scores the tensor core computes the other
 // tile's, and K and V are read from shared memory once for 256 rows.
-//   tensor memory: S_A 0..127, S_B 128..255, O_A[2] at 256 and 320, O_B[2] at 384 and 448.
+//   tensor memory: S_A 0..127, S_B 128..255, O_A 256..319, O_B 320..383.
 //   shared memory: Q_A, Q_B (16 KB each), three K/V stages (32 KB each), P_A, P_B (32 KB each).
-// A softmax thread reads its row of scores twice from tensor memory, 32 columns at a time
-// (once for the maximum, once for the exponentials), which keeps it at 64 output and 32
-// score registers.
+// The outputs stay in tensor memory: every P V product accumulates onto them, and a row's
+// output is rescaled there only when its running maximum has grown by more than 2^8 since the
+// scale in use was fixed (probabilities then stay below 2^8, far inside bfloat16 and 32-bit
+// range; the final division by the row sum, kept at the same scale, undoes it exactly).  A
+// softmax thread reads its row of scores twice from tensor memory, 64 columns at a time (once
+// for the maximum, once for the exponentials), and holds no output in registers.
 namespace two {
 constexpr int KV_ST = 3;
 constexpr int THREADS2 = 320;                   // producer, MMA issuer, 4 + 4 softmax warps
@@ -439,7 +460,7 @@ struct Bars2 {
   uint64_t kv_full[KV_ST], kv_empty[KV_ST];
   uint64_t s_full[2], s_empty[2];               // per query tile
   uint64_t p_full[2], p_empty[2];
-  uint64_t o_full[2][2], o_empty[2][2];         // [query tile][buffer]
+  uint64_t o_full[2];                           // per query tile: a P V product has landed
   uint32_t tmem_slot;
 };
 
@@ -472,10 +493,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(smem_u32(&bars->s_empty[x]), GROUP_THREADS);
       mbar_init(smem_u32(&bars->p_full[x]), GROUP_THREADS);
       mbar_init(smem_u32(&bars->p_empty[x]), 1);
-      for (int i = 0; i < 2; ++i) {
-        mbar_init(smem_u32(&bars->o_full[x][i]), 1);
-        mbar_init(smem_u32(&bars->o_empty[x][i]), GROUP_THREADS);
-      }
+      mbar_init(smem_u32(&bars->o_full[x]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -555,19 +573,18 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       return true;
     };
     auto issue_pv = [&](int x, int j) -> bool {
-      const int st = j % KV_ST, ob = j & 1;
+      const int st = j % KV_ST;
       if (!mbar_wait(smem_u32(&bars->p_full[x]), (uint32_t)(j & 1))) return false;
-      if (!mbar_wait(smem_u32(&bars->o_empty[x][ob]), (uint32_t)(((j >> 1) & 1) ^ 1))) return false;
       tc_fence_after();
       const uint32_t pa = smem_u32(sp + (size_t)x * P_BYTES);
       const uint32_t va = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES) + K_BYTES);
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb)          // 64 keys each
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)        // 16 keys each
-          umma(tmem + O2_COL + (x * 2 + ob) * HD, desc_kmajor(pa + kb * TILE_BYTES) + 2 * k4,
-               desc_mnmajor(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (kb | k4) ? 1u : 0u);
-      umma_commit(smem_u32(&bars->o_full[x][ob]));
+        for (int k4 = 0; k4 < 4; ++k4)        // 16 keys each; the first tile's first MMA starts the sum
+          umma(tmem + O2_COL + x * HD, desc_kmajor(pa + kb * TILE_BYTES) + 2 * k4,
+               desc_mnmajor(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (j > 0 || (kb | k4)) ? 1u : 0u);
+      umma_commit(smem_u32(&bars->o_full[x]));
       umma_commit(smem_u32(&bars->p_empty[x]));
       return true;
     };
@@ -601,29 +618,11 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const float sl2 = scale * LOG2E;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_addr = lane_addr + S2_COL + x * BN;
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    const uint32_t o_addr = lane_addr + O2_COL + x * HD;
+    // m: the scale in use (log2 domain), fixed until the running maximum outgrows it by 2^8
+    float m = -INFINITY, l = 0.f;
     bool ok = true;
     const int nt = x ? n_tiles_b : n_tiles_a;
-
-    auto take_output = [&](int j, float alpha) -> bool {   // o = o * alpha + (P_j V_j)[row]
-      const int ob = j & 1;
-      if (!mbar_wait(smem_u32(&bars->o_full[x][ob]), (uint32_t)((j >> 1) & 1))) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < HD; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(lane_addr + O2_COL + (x * 2 + ob) * HD + c, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, __uint_as_float(v[i]));
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bars->o_empty[x][ob]));
-      return true;
-    };
 
     for (int j = 0; j < nt && ok; ++j) {
       const int st = j % KV_ST;
@@ -635,41 +634,61 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       float mx = -INFINITY;
       if (!need_mask) {
 #pragma unroll
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + c, v);
+        for (int c = 0; c < BN; c += 64) {
+          uint32_t v[64];
+          tmem_ld64(s_addr + c, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+          for (int i = 0; i < 64; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + c, v);
+        for (int c = 0; c < BN; c += 64) {
+          uint32_t v[64];
+          tmem_ld64(s_addr + c, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, key0 + c + i <= lim ? __uint_as_float(v[i]) : -INFINITY);
+          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, key0 + c + i <= lim ? __uint_as_float(v[i]) : -INFINITY);
         }
       }
       mx *= sl2;                                         // scale > 0: the maximum commutes with it
-      const float m_new = fmaxf(m, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = fast_exp2(m - m_use);
-      m = m_new;
+      const bool grow = mx > m + 8.0f || (m == -INFINITY && mx > -INFINITY);
+      float alpha = 1.0f;
+      if (grow) {
+        alpha = fast_exp2(m - mx);                       // 0 while nothing has been summed
+        m = mx;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // the output so far is at the old scale: bring this warp's rows to the new one
+        if (!mbar_wait(smem_u32(&bars->o_full[x]), (uint32_t)((j - 1) & 1))) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(o_addr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st32(o_addr + c, v);
+        }
+        tmem_st_wait();
+        l *= alpha;
+      }
+      const float m_use = m == -INFINITY ? 0.f : m;
       if (!mbar_wait(smem_u32(&bars->p_empty[x]), (uint32_t)((j & 1) ^ 1))) { ok = false; break; }
-      // second pass: probabilities to shared memory (K-major, 128-byte rows, swizzled by row)
+      // second pass: probabilities to shared memory (K-major, 128-byte rows, swizzled by row);
+      // 64 columns are one 128-byte row of one k block
       float sum = 0.f;
       auto second_pass = [&](auto masked) {
         constexpr bool MASKED = decltype(masked)::value;
 #pragma unroll
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + c, v);
+        for (int c = 0; c < BN; c += 64) {
+          uint32_t v[64];
+          tmem_ld64(s_addr + c, v);
           tmem_ld_wait();
           unsigned char* prow = sp + (size_t)x * P_BYTES + (c >> 6) * TILE_BYTES + row * 128;
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
+          for (int ch = 0; ch < 8; ++ch) {
             float pr[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -684,8 +703,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             w.y = pack2(pr[2], pr[3]);
             w.z = pack2(pr[4], pr[5]);
             w.w = pack2(pr[6], pr[7]);
-            const int chunk = ((c & 63) >> 3) + ch;     // 16-byte chunk within the 128-byte row
-            *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+            *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = w;
           }
         }
       };
@@ -693,7 +711,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       else second_pass(std::false_type{});
       tc_fence_before();
       mbar_arrive(smem_u32(&bars->s_empty[x]));          // the scores have been read twice: free for tile j + 1
-      l = l * alpha + sum;
+      l += sum;
       if (key0 + BN > kend_all) {
         // keys past the last visible one share pages with stale rows: their values must be
         // zeros, since 0 * NaN would poison the product (both groups write the same zeros)
@@ -706,25 +724,32 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
       mbar_arrive(smem_u32(&bars->p_full[x]));
-      // one tile behind: add the previous tile's output
-      if (j > 0) ok = take_output(j - 1, alpha_prev);
-      alpha_prev = alpha;
     }
-    if (ok && nt > 0) ok = take_output(nt - 1, alpha_prev);
+    if (ok && nt > 0) ok = mbar_wait(smem_u32(&bars->o_full[x]), (uint32_t)((nt - 1) & 1));
     if (!ok) {
       if (lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 23, blockIdx.x);
-    } else if (rvalid) {
+    } else if (nt > 0) {
+      tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       bf16* op = out + ((long long)(t0 + tok0 + tok) * nh + head) * HD;
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
-        uint4 w;
-        w.x = pack2(o[c] * inv, o[c + 1] * inv);
-        w.y = pack2(o[c + 2] * inv, o[c + 3] * inv);
-        w.z = pack2(o[c + 4] * inv, o[c + 5] * inv);
-        w.w = pack2(o[c + 6] * inv, o[c + 7] * inv);
-        *reinterpret_cast<uint4*>(op + c) = w;
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(o_addr + c, v);                        // the whole warp loads; valid rows store
+        tmem_ld_wait();
+        if (rvalid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack2(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            w.y = pack2(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            w.z = pack2(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            w.w = pack2(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(op + c + i) = w;
+          }
+        }
       }
     }
   }
