@@ -3,8 +3,8 @@
 //
 // A CTA owns 128 packed query rows of one request and one kv head (row i = token i / rep,
 // query head g*rep + i % rep) and walks over the keys in tiles of 128.
-//   warp 0, one lane : producer.  One 3-D TMA load brings the query tile; per key tile, one
-//                      2-D TMA load per page brings K and one brings V (a page of a kv head is
+//   warp 0           : producer.  One 3-D TMA load brings the query tile; per key tile, one
+//                      2-D TMA load per page (one lane per page) brings K and one brings V (a page of a kv head is
 //                      a contiguous [page_size, hd] block of the cache), all with the 128-byte
 //                      swizzle the MMA expects.  Pages beyond the last visible key are replaced
 //                      by an out-of-bounds box, which TMA fills with zeros.
@@ -116,6 +116,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+#if FMX_HD == 64
 // 64 columns: two 32-column loads in flight under one wait.
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
   uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
@@ -134,6 +135,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+#endif
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // 2^x by the special-function unit (about two units in the last place; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -214,23 +216,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_tiles = active ? (kend + BN - 1) / BN : 0;
   const int pages_per_tile = BN / page_size;
 
-  if (warp == 0 && lane == 0 && active) {
+  if (warp == 0 && active) {
     // ------------------------------------------------------------------ producer
+    // The whole warp: lane 0 owns the barriers; lane p looks up page p of the tile and issues
+    // its copies, so that the block-table reads of a tile overlap instead of queueing.
     const int* bt = block_tables + (long long)r * bt_stride;
-    mbar_expect_tx(smem_u32(&bars->q_full), Q_BYTES);
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&bars->q_full), Q_BYTES);
 #pragma unroll
-    for (int kb = 0; kb < KB; ++kb)
-      tma_load_3d(smem_u32(sq + kb * TILE_BYTES), &map_q, kb * 64, g * rep, t0 + tok0, smem_u32(&bars->q_full));
+      for (int kb = 0; kb < KB; ++kb)
+        tma_load_3d(smem_u32(sq + kb * TILE_BYTES), &map_q, kb * 64, g * rep, t0 + tok0, smem_u32(&bars->q_full));
+    }
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1)) { ok = false; break; }
+    for (int j = 0; j < n_tiles; ++j) {
       const uint32_t fb = smem_u32(&bars->kv_full[stage]);
-      unsigned char* sk = skv + (size_t)stage * (K_BYTES + V_BYTES);
-      unsigned char* sv = sk + K_BYTES;
-      mbar_expect_tx(fb, K_BYTES + V_BYTES);
-      for (int pi = 0; pi < pages_per_tile; ++pi) {
+      if (lane == 0) {
+        ok = mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1);
+        if (ok) mbar_expect_tx(fb, K_BYTES + V_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        const int pi = lane;
+        unsigned char* sk = skv + (size_t)stage * (K_BYTES + V_BYTES);
+        unsigned char* sv = sk + K_BYTES;
         const int key0 = j * BN + pi * page_size;
         long long krow = kv_rows, vrow = kv_rows;           // out of bounds: the box reads as zeros
         if (key0 < kend) {
@@ -252,7 +263,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       if (++stage == KV_STAGES) { stage = 0; phase ^= 1; }
     }
-    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 11, blockIdx.x);
+    if (!ok && lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 11, blockIdx.x);
   } else if (warp == 1 && lane == 0 && active) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t idesc_qk = idesc_f16(BM, BN, 0), idesc_pv = idesc_f16(BM, HD, 1);
@@ -520,23 +531,32 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int kend_all = max(act_a ? kend_a : 0, act_b ? kend_b : 0);
   const int pages_per_tile = BN / page_size;
 
-  if (warp == 0 && lane == 0 && n_all > 0) {
+  if (warp == 0 && n_all > 0) {
     // ------------------------------------------------------------------ producer
+    // The whole warp: lane 0 owns the barriers; lane p looks up page p of the tile and issues
+    // its two copies, so that the block-table reads of a tile overlap instead of queueing.
     const int* bt = block_tables + (long long)r * bt_stride;
-    mbar_expect_tx(smem_u32(&bars->q_full), 2 * Q_BYTES);
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&bars->q_full), 2 * Q_BYTES);
 #pragma unroll
-    for (int x = 0; x < 2; ++x)             // a tile past the row's end reads as zeros
-      tma_load_3d(smem_u32(sq + x * Q_BYTES), &map_q, 0, g * rep, t0 + (x ? tok0_b : tok0_a), smem_u32(&bars->q_full));
+      for (int x = 0; x < 2; ++x)             // a tile past the row's end reads as zeros
+        tma_load_3d(smem_u32(sq + x * Q_BYTES), &map_q, 0, g * rep, t0 + (x ? tok0_b : tok0_a), smem_u32(&bars->q_full));
+    }
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int j = 0; j < n_all && ok; ++j) {
-      if (!mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1)) { ok = false; break; }
+    for (int j = 0; j < n_all; ++j) {
       const uint32_t fb = smem_u32(&bars->kv_full[stage]);
-      unsigned char* sk = skv + (size_t)stage * (K_BYTES + V_BYTES);
-      unsigned char* sv = sk + K_BYTES;
-      mbar_expect_tx(fb, K_BYTES + V_BYTES);
-      for (int pi = 0; pi < pages_per_tile; ++pi) {
+      if (lane == 0) {
+        ok = mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1);
+        if (ok) mbar_expect_tx(fb, K_BYTES + V_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        const int pi = lane;
+        unsigned char* sk = skv + (size_t)stage * (K_BYTES + V_BYTES);
+        unsigned char* sv = sk + K_BYTES;
         const int key0 = j * BN + pi * page_size;
         long long krow = kv_rows, vrow = kv_rows;           // out of bounds: the box reads as zeros
         if (key0 < kend_all) {
@@ -555,7 +575,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       if (++stage == KV_ST) { stage = 0; phase ^= 1; }
     }
-    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 21, blockIdx.x);
+    if (!ok && lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 21, blockIdx.x);
   } else if (warp == 1 && lane == 0 && n_all > 0) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t idesc_qk = idesc_f16(BM, BN, 0), idesc_pv = idesc_f16(BM, HD, 1);
