@@ -506,7 +506,7 @@ TC_ATTN_MIN_TOKENS = 64
 
 
 def _use_tc_attention(hd: int) -> bool:
-    return _ATTN_CHOICE == "tcgen05" or (_ATTN_CHOICE == "auto" and hd == 128)
+    return _ATTN_CHOICE == "tcgen05" or (_ATTN_CHOICE == "auto" and hd in (64, 128))
 
 
 def tc_attention_ok(nh: int, nkv: int, hd: int, page_size: int, window: int) -> bool:
