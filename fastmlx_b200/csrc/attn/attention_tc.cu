@@ -69,6 +69,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (clock64() - t0 > WAIT_CYCLES) return false;
   }
 }
+// One probe, no waiting: has the phase of this parity completed?
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
@@ -581,21 +591,19 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t idesc_qk = idesc_f16(BM, BN, 0), idesc_pv = idesc_f16(BM, HD, 1);
     bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
     tc_fence_after();
-    auto issue_qk = [&](int x, int j) -> bool {
+    // The two query tiles advance independently: whichever product has its inputs goes next
+    // (scores of tile j need its K tile and the score buffer read out; P V of tile j needs its
+    // probabilities), so one tile's softmax never waits for the other's.
+    auto issue_qk = [&](int x, int j) {
       const int st = j % KV_ST;
-      if (!mbar_wait(smem_u32(&bars->s_empty[x]), (uint32_t)((j & 1) ^ 1))) return false;
-      tc_fence_after();
       const uint32_t qa = smem_u32(sq + x * Q_BYTES), ka = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES));
 #pragma unroll
       for (int k4 = 0; k4 < 4; ++k4)
         umma(tmem + S2_COL + x * BN, desc_kmajor(qa) + 2 * k4, desc_kmajor(ka) + 2 * k4, idesc_qk, k4 ? 1u : 0u);
       umma_commit(smem_u32(&bars->s_full[x]));
-      return true;
     };
-    auto issue_pv = [&](int x, int j) -> bool {
+    auto issue_pv = [&](int x, int j) {
       const int st = j % KV_ST;
-      if (!mbar_wait(smem_u32(&bars->p_full[x]), (uint32_t)(j & 1))) return false;
-      tc_fence_after();
       const uint32_t pa = smem_u32(sp + (size_t)x * P_BYTES);
       const uint32_t va = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES) + K_BYTES);
 #pragma unroll
@@ -606,24 +614,37 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                desc_mnmajor(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (j > 0 || (kb | k4)) ? 1u : 0u);
       umma_commit(smem_u32(&bars->o_full[x]));
       umma_commit(smem_u32(&bars->p_empty[x]));
-      return true;
     };
-    for (int j = 0; j < n_all && ok; ++j) {
-      const int st = j % KV_ST;
-      if (!mbar_wait(smem_u32(&bars->kv_full[st]), (uint32_t)((j / KV_ST) & 1))) { ok = false; break; }
-      tc_fence_after();
-      if (j < n_tiles_a) ok = issue_qk(0, j);
-      if (ok && j < n_tiles_b) ok = issue_qk(1, j);
-      if (j > 0 && ok) {
-        if (j - 1 < n_tiles_a) ok = issue_pv(0, j - 1);
-        if (ok && j - 1 < n_tiles_b) ok = issue_pv(1, j - 1);
-        if (ok) umma_commit(smem_u32(&bars->kv_empty[(j - 1) % KV_ST]));
+    int qk_a = 0, qk_b = 0, pv_a = 0, pv_b = 0, released = 0;
+    long long t_last = clock64();
+    while (ok && (pv_a < n_tiles_a || pv_b < n_tiles_b)) {
+      bool progress = false;
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        int& qk = x ? qk_b : qk_a;
+        int& pv = x ? pv_b : pv_a;
+        const int n = x ? n_tiles_b : n_tiles_a;
+        if (qk < n && mbar_test(smem_u32(&bars->kv_full[qk % KV_ST]), (uint32_t)((qk / KV_ST) & 1)) &&
+            mbar_test(smem_u32(&bars->s_empty[x]), (uint32_t)((qk & 1) ^ 1))) {
+          tc_fence_after();
+          issue_qk(x, qk);
+          ++qk;
+          progress = true;
+        }
+        if (pv < qk && mbar_test(smem_u32(&bars->p_full[x]), (uint32_t)(pv & 1))) {
+          tc_fence_after();
+          issue_pv(x, pv);
+          ++pv;
+          progress = true;
+        }
       }
-    }
-    if (ok) {
-      if (n_all - 1 < n_tiles_a) ok = issue_pv(0, n_all - 1);
-      if (ok && n_all - 1 < n_tiles_b) ok = issue_pv(1, n_all - 1);
-      if (ok) umma_commit(smem_u32(&bars->kv_empty[(n_all - 1) % KV_ST]));
+      // a K/V stage goes back once both tiles' products over it have been issued
+      while (released < n_all && (released >= n_tiles_a || pv_a > released) && (released >= n_tiles_b || pv_b > released)) {
+        umma_commit(smem_u32(&bars->kv_empty[released % KV_ST]));
+        ++released;
+      }
+      if (progress) t_last = clock64();
+      else if (clock64() - t_last > WAIT_CYCLES) ok = false;
     }
     if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 22, blockIdx.x);
   } else if (warp >= 2) {
