@@ -22,6 +22,7 @@
 #include <math.h>
 #include <type_traits>
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 #ifndef FMX_HD
 #error "compile with -DFMX_HD=<head size>"
@@ -29,6 +30,7 @@
 
 #if FMX_HD == 64 || FMX_HD == 128
 namespace {
+using namespace fmx_tc;
 constexpr int HD = FMX_HD;
 constexpr int KB = HD / 64;                    // 64-wide blocks of the head dimension
 constexpr int BM = 128, BN = 128;
@@ -41,112 +43,10 @@ constexpr int THREADS = 320;                  // producer, MMA issuer, eight sof
 constexpr int SOFTMAX_THREADS = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int S_COL = 0, O_COL = 256;          // S0, S1 at 0, 128; O0, O1 at 256, 256 + HD
-constexpr long long WAIT_CYCLES = 2000000000LL;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + (size_t)KV_STAGES * (K_BYTES + V_BYTES) + (size_t)P_BUFS * P_BYTES +
                               1024 + 512 + 2 * 2 * 128 * 4;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  const long long t0 = clock64();
-  for (;;) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-    if (clock64() - t0 > WAIT_CYCLES) return false;
-  }
-}
-// One probe, no waiting: has the phase of this parity completed?
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
-}
-// K-major operand, rows of 128 bytes, 128-byte swizzle (see tc/gemm_tcgen05.cu).
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-         ((uint64_t)2 << 61);
-}
-// MN-major operand (V: keys down, head dimension across and contiguous): 64 elements of the
-// head dimension are one 128-byte row, eight key rows one swizzle atom; the leading byte offset
-// steps to the next 64 elements of the head dimension, the stride byte offset to the next
-// eight keys.
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo_bytes) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ uint32_t idesc_f16(int m, int n, int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-#if FMX_HD == 64
-// 64 columns: two 32-column loads in flight under one wait.
-__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
-  uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
-  uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
-  tmem_ld32(taddr, lo);
-  tmem_ld32(taddr + 32, hi);
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-#endif
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // 2^x by the special-function unit (about two units in the last place; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -276,7 +176,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (!ok && lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 11, blockIdx.x);
   } else if (warp == 1 && lane == 0 && active) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc_qk = idesc_f16(BM, BN, 0), idesc_pv = idesc_f16(BM, HD, 1);
+    const uint32_t idesc_qk = make_idesc(BM, BN, 0), idesc_pv = make_idesc(BM, HD, 1);
     bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
     tc_fence_after();
     auto issue_pv = [&](int j) -> bool {
@@ -290,8 +190,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int kb = 0; kb < 2; ++kb)          // 64 keys each
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4)        // 16 keys each
-          umma(tmem + O_COL + ob * HD, desc_kmajor(pa + kb * TILE_BYTES) + 2 * k4,
-               desc_mnmajor(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (kb | k4) ? 1u : 0u);
+          umma_f16(tmem + O_COL + ob * HD, make_desc_k128(pa + kb * TILE_BYTES) + 2 * k4,
+               make_desc_mn128(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (kb | k4) ? 1u : 0u);
       umma_commit(smem_u32(&bars->o_full[ob]));
       umma_commit(smem_u32(&bars->p_empty[pb]));
       umma_commit(smem_u32(&bars->kv_empty[st]));
@@ -307,8 +207,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4)
-          umma(tmem + S_COL + sb * BN, desc_kmajor(qa + kb * TILE_BYTES) + 2 * k4,
-               desc_kmajor(ka + kb * TILE_BYTES) + 2 * k4, idesc_qk, (kb | k4) ? 1u : 0u);
+          umma_f16(tmem + S_COL + sb * BN, make_desc_k128(qa + kb * TILE_BYTES) + 2 * k4,
+               make_desc_k128(ka + kb * TILE_BYTES) + 2 * k4, idesc_qk, (kb | k4) ? 1u : 0u);
       umma_commit(smem_u32(&bars->s_full[sb]));
       if (j > 0) ok = issue_pv(j - 1);
     }
@@ -588,7 +488,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (!ok && lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 21, blockIdx.x);
   } else if (warp == 1 && lane == 0 && n_all > 0) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc_qk = idesc_f16(BM, BN, 0), idesc_pv = idesc_f16(BM, HD, 1);
+    const uint32_t idesc_qk = make_idesc(BM, BN, 0), idesc_pv = make_idesc(BM, HD, 1);
     bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
     tc_fence_after();
     // The two query tiles advance independently: whichever product has its inputs goes next
@@ -599,7 +499,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const uint32_t qa = smem_u32(sq + x * Q_BYTES), ka = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES));
 #pragma unroll
       for (int k4 = 0; k4 < 4; ++k4)
-        umma(tmem + S2_COL + x * BN, desc_kmajor(qa) + 2 * k4, desc_kmajor(ka) + 2 * k4, idesc_qk, k4 ? 1u : 0u);
+        umma_f16(tmem + S2_COL + x * BN, make_desc_k128(qa) + 2 * k4, make_desc_k128(ka) + 2 * k4, idesc_qk, k4 ? 1u : 0u);
       umma_commit(smem_u32(&bars->s_full[x]));
     };
     auto issue_pv = [&](int x, int j) {
@@ -610,8 +510,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       for (int kb = 0; kb < 2; ++kb)          // 64 keys each
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4)        // 16 keys each; the first tile's first MMA starts the sum
-          umma(tmem + O2_COL + x * HD, desc_kmajor(pa + kb * TILE_BYTES) + 2 * k4,
-               desc_mnmajor(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (j > 0 || (kb | k4)) ? 1u : 0u);
+          umma_f16(tmem + O2_COL + x * HD, make_desc_k128(pa + kb * TILE_BYTES) + 2 * k4,
+               make_desc_mn128(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (j > 0 || (kb | k4)) ? 1u : 0u);
       umma_commit(smem_u32(&bars->o_full[x]));
       umma_commit(smem_u32(&bars->p_empty[x]));
     };
@@ -805,20 +705,6 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 }  // namespace two
 #endif
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
 }  // namespace
 
 // 1 when this head size has the tensor-memory kernel.

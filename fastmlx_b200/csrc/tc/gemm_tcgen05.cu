@@ -23,11 +23,12 @@
 // has in flight, frees its tensor memory and returns.
 #include <cuda.h>
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
+using namespace fmx_tc;
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr long long WAIT_CYCLES = 2000000000LL;        // about a second
 
 enum Epilogue { EPI_PLAIN = 0, EPI_SILU_MUL = 1, EPI_RESIDUAL = 2 };
 
@@ -38,78 +39,6 @@ template <int BN> struct Cfg {
   static constexpr int TMEM_COLS = BN > 128 ? 512 : 256;   // two accumulators; a power of two >= 32
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait: false when the phase did not complete within WAIT_CYCLES.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  const long long t0 = clock64();
-  for (;;) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-    if (clock64() - t0 > WAIT_CYCLES) return false;
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
-// 128-byte swizzle: start address, leading byte offset (unused for swizzled K-major: 1),
-// stride byte offset = 1024 (eight rows), version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-// Instruction descriptor for kind::f16: D = F32, A = B = BF16, both K-major, M x N.
-__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ unsigned pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -199,10 +128,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + (size_t)stage * cfg::STAGE_BYTES);
-        const uint64_t adesc = make_desc(sa), bdesc = make_desc(sa + cfg::A_BYTES);
+        const uint64_t adesc = make_desc_k128(sa), bdesc = make_desc_k128(sa + cfg::A_BYTES);
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k)     // 32 bytes further along K: +2 in units of 16 bytes
-          umma(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
         umma_commit(smem_u32(&empty_bar[stage]));
         if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
       }
@@ -280,44 +209,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// A row-major [rows, K] bfloat16 matrix with leading dimension ld (elements), read in boxes
-// of 64 x box_rows; rows and columns outside the matrix read as zero.
-int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
-  EncodeTiledFn enc = encode_fn();
-  if (enc == nullptr) return fmx_fail("gemm_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fmx_fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
-  return 0;
-}
-
 template <int BN, int EPI>
 int run(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, const void* residual,
         long long ldr, int M, int N, int K, int sms, int* status, cudaStream_t stream) {
   using cfg = Cfg<BN>;
   CUtensorMap map_a, map_w;
-  if (make_map(&map_a, A, M, K, lda, BM) || make_map(&map_w, W, N, K, ldw, BN)) return 1;
+  if (make_map_k128(&map_a, A, M, K, lda, BM) || make_map_k128(&map_w, W, N, K, ldw, BN)) return 1;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
