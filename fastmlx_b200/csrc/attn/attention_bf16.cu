@@ -560,19 +560,35 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   __syncthreads();
   if (!drew_last) return;
   __threadfence();
+  // Three rounds of loads instead of a chain: the splits' (max, sum) pairs go to shared memory
+  // in one coalesced sweep, each row's weights 2^(m_split - M) are worked out there, and the
+  // partial outputs are then read with independent loads.  The sums run in split order.
   const long long base = (((long long)r * nkv + g) * splits) * 16;
+  float* ml_s = reinterpret_cast<float*>(smem_raw);      // [splits][16][2]; the tiles' memory is free
+  float* w_s = ml_s + splits * 32;                       // [splits][16]
+  float* L_s = w_s + splits * 16;                        // [16]
+  for (int i = threadIdx.x; i < splits * 32; i += THREADS) ml_s[i] = __ldcg(&part_ml[base * 2 + i]);
+  __syncthreads();
+  for (int row = threadIdx.x; row < rep; row += THREADS) {
+    float M = -INFINITY;
+    for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, ml_s[(sp * 16 + row) * 2]);
+    const float Mu = M == -INFINITY ? 0.f : M;
+    float L = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float f = exp2f(ml_s[(sp * 16 + row) * 2] - Mu);
+      w_s[sp * 16 + row] = f;
+      L += f * ml_s[(sp * 16 + row) * 2 + 1];
+    }
+    L_s[row] = L;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < rep * HD; idx += THREADS) {
     const int row = idx / HD, d = idx - row * HD;
-    float M = -INFINITY;
-    for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, __ldcg(&part_ml[(base + (long long)sp * 16 + row) * 2]));
-    const float Mu = M == -INFINITY ? 0.f : M;
-    float L = 0.f, acc = 0.f;
-    for (int sp = 0; sp < splits; ++sp) {
-      const long long pi = base + (long long)sp * 16 + row;
-      const float f = exp2f(__ldcg(&part_ml[pi * 2]) - Mu);
-      L += f * __ldcg(&part_ml[pi * 2 + 1]);
-      acc += f * __ldcg(&part_o[pi * HD + d]);
-    }
+    const float* po = part_o + (base + row) * HD + d;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int sp = 0; sp < splits; ++sp) acc += w_s[sp * 16 + row] * __ldcg(po + (long long)sp * 16 * HD);
+    const float L = L_s[row];
     out[((long long)t * nh + g * rep + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
   if (threadIdx.x == 0) tickets[r * nkv + g] = 0;      // ready for the next launch
@@ -660,6 +676,7 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || splits <= 0)
     return fmx_fail("fmx_attn_decode: bad sizes rows=%d nh=%d nkv=%d page=%d splits=%d", rows, nh, nkv, page_size, splits);
   if (nh / nkv > 16) return fmx_fail("fmx_attn_decode: %d query heads per kv head is above 16", nh / nkv);
+  if (splits > 64) return fmx_fail("fmx_attn_decode: at most 64 splits (the combining block stages their statistics in shared memory), not %d", splits);
   if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_decode: too many rows or kv heads for one launch");
   const long long need = fmx_attn_decode_scratch_floats(rows, nkv, splits);
   if (need > 0 && (scratch == nullptr || scratch_floats < need))
