@@ -132,7 +132,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // its copies, so that the block-table reads of a tile overlap instead of queueing.
     const int* bt = block_tables + (long long)r * bt_stride;
     if (lane == 0) {
-      mbar_expect_tx(smem_u32(&bars->q_full), Q_BYTES);
+      // the box holds tok_per_tile x rep rows: all 128 when rep divides 128, else the last few
+      // rows of the tile are left as they are (they belong to no token and are never stored)
+      mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(tok_per_tile * rep * 128 * KB));
 #pragma unroll
       for (int kb = 0; kb < KB; ++kb)
         tma_load_3d(smem_u32(sq + kb * TILE_BYTES), &map_q, kb * 64, g * rep, t0 + tok0, smem_u32(&bars->q_full));
@@ -447,7 +449,9 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // its two copies, so that the block-table reads of a tile overlap instead of queueing.
     const int* bt = block_tables + (long long)r * bt_stride;
     if (lane == 0) {
-      mbar_expect_tx(smem_u32(&bars->q_full), 2 * Q_BYTES);
+      // a box holds tok_per_tile x rep rows: all 128 when rep divides 128, else the last few
+      // rows of a tile are left as they are (they belong to no token and are never stored)
+      mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(2 * tok_per_tile * rep * 128));
 #pragma unroll
       for (int x = 0; x < 2; ++x)             // a tile past the row's end reads as zeros
         tma_load_3d(smem_u32(sq + x * Q_BYTES), &map_q, 0, g * rep, t0 + (x ? tok0_b : tok0_a), smem_u32(&bars->q_full));
@@ -710,7 +714,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 // 1 when this head size has the tensor-memory kernel.
 FMX_EXPORT int fmx_attn_prefill_tc_available() { return 1; }
 
-// As fmx_attn_prefill, without a window, for nh / nkv in {1, 2, 4, 8, 16} and a page size
+// As fmx_attn_prefill, without a window, for up to 16 query heads per kv head and a page size
 // that divides 128 and is at least 8.  q rows (tokens) are T; the out-of-range part of the
 // last query tile reads as zeros.  variant 1: one query tile per CTA; otherwise two where the
 // head size has that kernel (64).
@@ -721,7 +725,7 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
   if (rows == 0 || max_q_len == 0) return 0;
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv) return fmx_fail("fmx_attn_prefill_tc: bad sizes rows=%d nh=%d nkv=%d", rows, nh, nkv);
   const int rep = nh / nkv;
-  if (rep > 16 || (rep & (rep - 1))) return fmx_fail("fmx_attn_prefill_tc: %d query heads per kv head is no power of two up to 16", rep);
+  if (rep > 16) return fmx_fail("fmx_attn_prefill_tc: %d query heads per kv head is above 16", rep);
   if (page_size < 8 || BN % page_size) return fmx_fail("fmx_attn_prefill_tc: a page of %d tokens does not tile 128 keys", page_size);
   if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_prefill_tc: too many rows or kv heads for one launch");
   if (q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)kv & 15)) return fmx_fail("fmx_attn_prefill_tc: q and the cache must be 16-byte aligned");

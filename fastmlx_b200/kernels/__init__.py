@@ -510,10 +510,10 @@ def _use_tc_attention(hd: int) -> bool:
 
 
 def tc_attention_ok(nh: int, nkv: int, hd: int, page_size: int, window: int) -> bool:
-    """Sizes the tensor-memory attention kernel takes: head size 64 or 128, a power of two (at
-    most 16) of query heads per kv head, a page size that divides 128 (at least 8), no window."""
+    """Sizes the tensor-memory attention kernel takes: head size 64 or 128, at most 16 query
+    heads per kv head, a page size that divides 128 (at least 8), no window."""
     rep = nh // nkv
-    return (hd in (64, 128) and window <= 0 and rep <= 16 and rep & (rep - 1) == 0
+    return (hd in (64, 128) and window <= 0 and rep <= 16
             and page_size >= 8 and 128 % page_size == 0)
 
 

@@ -564,7 +564,7 @@ def test_decode_attention_rotates_and_stores_by_itself(nh, nkv, hd, page_size, r
 
 
 TC_SHAPES = [(4, 1, 64, 16), (8, 2, 64, 16), (32, 8, 64, 16), (8, 8, 64, 32), (16, 1, 64, 128), (8, 2, 128, 16),
-             (24, 24, 128, 64), (16, 2, 128, 8)]
+             (24, 24, 128, 64), (16, 2, 128, 8), (24, 8, 128, 16), (6, 2, 64, 16), (5, 1, 64, 32), (7, 1, 128, 16)]
 
 
 @pytest.mark.parametrize("variant", [0, 1])
