@@ -356,15 +356,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 }
 
-#if FMX_HD == 64
 // ------------------------------------------------------------------------------------
-// Two query tiles per CTA (head size 64).  The CTA owns 256 packed query rows: tile A (rows
+// Two query tiles per CTA.  The CTA owns 256 packed query rows: tile A (rows
 // 0-127) and tile B (rows 128-255) share every K/V tile that TMA brings, and each has a
 // softmax group of four warps with one thread per query row, so no row statistic ever
 // crosses a thread.  While one group works on its scores the tensor core computes the other
 // tile's, and K and V are read from shared memory once for 256 rows.
-//   tensor memory: S_A 0..127, S_B 128..255, O_A 256..319, O_B 320..383.
-//   shared memory: Q_A, Q_B (16 KB each), three K/V stages (32 KB each), P_A, P_B (32 KB each).
+// Keys come in tiles of 128 at head size 64 and of 64 at head size 128, so that both fit:
+//   tensor memory: S_A, S_B (one column per key), then O_A, O_B (one per head dimension): 384 columns.
+//   shared memory: Q_A, Q_B, three K/V stages (32 KB each), P_A, P_B: 192 KB.
 // The outputs stay in tensor memory: every P V product accumulates onto them, and a row's
 // output is rescaled there only when its running maximum has grown by more than 2^8 since the
 // scale in use was fixed (probabilities then stay below 2^8, far inside bfloat16 and 32-bit
@@ -372,11 +372,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // softmax thread reads its row of scores twice from tensor memory, 64 columns at a time (once
 // for the maximum, once for the exponentials), and holds no output in registers.
 namespace two {
+constexpr int BN2 = HD == 64 ? 128 : 64;        // keys per tile
 constexpr int KV_ST = 3;
+constexpr int K2_BYTES = KB * BN2 * 128, V2_BYTES = K2_BYTES;      // KB blocks of [BN2 keys][64 dims]
+constexpr int PB = BN2 / 64;                    // 64-key blocks of a probability tile
+constexpr int P2_BYTES = PB * TILE_BYTES;       // PB blocks of [128 rows][64 keys]
 constexpr int THREADS2 = 320;                   // producer, MMA issuer, 4 + 4 softmax warps
 constexpr int GROUP_THREADS = 128;
-constexpr size_t SMEM2 = 2 * (size_t)Q_BYTES + (size_t)KV_ST * (K_BYTES + V_BYTES) + 2 * (size_t)P_BYTES + 1024 + 512;
-constexpr int S2_COL = 0, O2_COL = 256;
+constexpr size_t SMEM2 = 2 * (size_t)Q_BYTES + (size_t)KV_ST * (K2_BYTES + V2_BYTES) + 2 * (size_t)P2_BYTES + 1024 + 512;
+constexpr int S2_COL = 0, O2_COL = 2 * BN2;
 
 struct Bars2 {
   uint64_t q_full;
@@ -396,8 +400,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sq = smem;                                             // [2] query tiles
   unsigned char* skv = sq + 2 * Q_BYTES;                                // [stage][K | V]
-  unsigned char* sp = skv + (size_t)KV_ST * (K_BYTES + V_BYTES);        // [2] probabilities
-  Bars2* bars = reinterpret_cast<Bars2*>(sp + 2 * (size_t)P_BYTES);
+  unsigned char* sp = skv + (size_t)KV_ST * (K2_BYTES + V2_BYTES);        // [2] probabilities
+  Bars2* bars = reinterpret_cast<Bars2*>(sp + 2 * (size_t)P2_BYTES);
 
   // the last query tiles of a row see the most keys: they start first
   const int r = blockIdx.z, g = blockIdx.y, pair = gridDim.x - 1 - blockIdx.x;
@@ -438,10 +442,10 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const bool act_a = tok0_a < q_len && ctx >= 0, act_b = tok0_b < q_len && ctx >= 0;
   const int n_tok_a = act_a ? min(tok_per_tile, q_len - tok0_a) : 0, n_tok_b = act_b ? min(tok_per_tile, q_len - tok0_b) : 0;
   const int kend_a = ctx + tok0_a + n_tok_a, kend_b = ctx + tok0_b + n_tok_b;
-  const int n_tiles_a = act_a ? (kend_a + BN - 1) / BN : 0, n_tiles_b = act_b ? (kend_b + BN - 1) / BN : 0;
+  const int n_tiles_a = act_a ? (kend_a + BN2 - 1) / BN2 : 0, n_tiles_b = act_b ? (kend_b + BN2 - 1) / BN2 : 0;
   const int n_all = max(n_tiles_a, n_tiles_b);         // tile B sees at least what A sees
   const int kend_all = max(act_a ? kend_a : 0, act_b ? kend_b : 0);
-  const int pages_per_tile = BN / page_size;
+  const int pages_per_tile = BN2 / page_size;
 
   if (warp == 0 && n_all > 0) {
     // ------------------------------------------------------------------ producer
@@ -451,10 +455,13 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (lane == 0) {
       // a box holds tok_per_tile x rep rows: all 128 when rep divides 128, else the last few
       // rows of a tile are left as they are (they belong to no token and are never stored)
-      mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(2 * tok_per_tile * rep * 128));
+      mbar_expect_tx(smem_u32(&bars->q_full), (uint32_t)(2 * tok_per_tile * rep * 128 * KB));
 #pragma unroll
       for (int x = 0; x < 2; ++x)             // a tile past the row's end reads as zeros
-        tma_load_3d(smem_u32(sq + x * Q_BYTES), &map_q, 0, g * rep, t0 + (x ? tok0_b : tok0_a), smem_u32(&bars->q_full));
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_3d(smem_u32(sq + x * Q_BYTES + kb * TILE_BYTES), &map_q, kb * 64, g * rep, t0 + (x ? tok0_b : tok0_a),
+                      smem_u32(&bars->q_full));
     }
     int stage = 0;
     uint32_t phase = 0;
@@ -463,15 +470,15 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const uint32_t fb = smem_u32(&bars->kv_full[stage]);
       if (lane == 0) {
         ok = mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1);
-        if (ok) mbar_expect_tx(fb, K_BYTES + V_BYTES);
+        if (ok) mbar_expect_tx(fb, K2_BYTES + V2_BYTES);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       if (lane < pages_per_tile) {
         const int pi = lane;
-        unsigned char* sk = skv + (size_t)stage * (K_BYTES + V_BYTES);
-        unsigned char* sv = sk + K_BYTES;
-        const int key0 = j * BN + pi * page_size;
+        unsigned char* sk = skv + (size_t)stage * (K2_BYTES + V2_BYTES);
+        unsigned char* sv = sk + K2_BYTES;
+        const int key0 = j * BN2 + pi * page_size;
         long long krow = kv_rows, vrow = kv_rows;           // out of bounds: the box reads as zeros
         if (key0 < kend_all) {
           const int blk = key0 / page_size;
@@ -484,15 +491,18 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
         }
         const int off = pi * page_size * 128;               // rows of 128 bytes
-        tma_load_2d(smem_u32(sk + off), &map_kv, 0, (int)krow, fb);
-        tma_load_2d(smem_u32(sv + off), &map_kv, 0, (int)vrow, fb);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_2d(smem_u32(sk + kb * BN2 * 128 + off), &map_kv, kb * 64, (int)krow, fb);
+          tma_load_2d(smem_u32(sv + kb * BN2 * 128 + off), &map_kv, kb * 64, (int)vrow, fb);
+        }
       }
       if (++stage == KV_ST) { stage = 0; phase ^= 1; }
     }
     if (!ok && lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 21, blockIdx.x);
   } else if (warp == 1 && lane == 0 && n_all > 0) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc_qk = make_idesc(BM, BN, 0), idesc_pv = make_idesc(BM, HD, 1);
+    const uint32_t idesc_qk = make_idesc(BM, BN2, 0), idesc_pv = make_idesc(BM, HD, 1);
     bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
     tc_fence_after();
     // The two query tiles advance independently: whichever product has its inputs goes next
@@ -500,22 +510,25 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // probabilities), so one tile's softmax never waits for the other's.
     auto issue_qk = [&](int x, int j) {
       const int st = j % KV_ST;
-      const uint32_t qa = smem_u32(sq + x * Q_BYTES), ka = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES));
+      const uint32_t qa = smem_u32(sq + x * Q_BYTES), ka = smem_u32(skv + (size_t)st * (K2_BYTES + V2_BYTES));
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4)
-        umma_f16(tmem + S2_COL + x * BN, make_desc_k128(qa) + 2 * k4, make_desc_k128(ka) + 2 * k4, idesc_qk, k4 ? 1u : 0u);
+      for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+          umma_f16(tmem + S2_COL + x * BN2, make_desc_k128(qa + kb * TILE_BYTES) + 2 * k4,
+                   make_desc_k128(ka + kb * BN2 * 128) + 2 * k4, idesc_qk, (kb | k4) ? 1u : 0u);
       umma_commit(smem_u32(&bars->s_full[x]));
     };
     auto issue_pv = [&](int x, int j) {
       const int st = j % KV_ST;
-      const uint32_t pa = smem_u32(sp + (size_t)x * P_BYTES);
-      const uint32_t va = smem_u32(skv + (size_t)st * (K_BYTES + V_BYTES) + K_BYTES);
+      const uint32_t pa = smem_u32(sp + (size_t)x * P2_BYTES);
+      const uint32_t va = smem_u32(skv + (size_t)st * (K2_BYTES + V2_BYTES) + K2_BYTES);
 #pragma unroll
-      for (int kb = 0; kb < 2; ++kb)          // 64 keys each
+      for (int kb = 0; kb < PB; ++kb)         // 64 keys each
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4)        // 16 keys each; the first tile's first MMA starts the sum
           umma_f16(tmem + O2_COL + x * HD, make_desc_k128(pa + kb * TILE_BYTES) + 2 * k4,
-               make_desc_mn128(va + (kb * 64 + k4 * 16) * 128, TILE_BYTES), idesc_pv, (j > 0 || (kb | k4)) ? 1u : 0u);
+                   make_desc_mn128(va + (kb * 64 + k4 * 16) * 128, BN2 * 128), idesc_pv, (j > 0 || (kb | k4)) ? 1u : 0u);
       umma_commit(smem_u32(&bars->o_full[x]));
       umma_commit(smem_u32(&bars->p_empty[x]));
     };
@@ -562,7 +575,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int lim = rvalid ? ctx + tok0 + tok : -1;      // last key this row sees
     const float sl2 = scale * LOG2E;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t s_addr = lane_addr + S2_COL + x * BN;
+    const uint32_t s_addr = lane_addr + S2_COL + x * BN2;
     const uint32_t o_addr = lane_addr + O2_COL + x * HD;
     // m: the scale in use (log2 domain), fixed until the running maximum outgrows it by 2^8
     float m = -INFINITY, l = 0.f;
@@ -573,13 +586,13 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const int st = j % KV_ST;
       if (!mbar_wait(smem_u32(&bars->s_full[x]), (uint32_t)(j & 1))) { ok = false; break; }
       tc_fence_after();
-      const int key0 = j * BN;
-      const bool need_mask = key0 + BN - 1 > ctx + tok0;     // some row of the tile does not see the whole tile
+      const int key0 = j * BN2;
+      const bool need_mask = key0 + BN2 - 1 > ctx + tok0;     // some row of the tile does not see the whole tile
       // first pass: the row's maximum (tiles left of the diagonal need no mask)
       float mx = -INFINITY;
       if (!need_mask) {
 #pragma unroll
-        for (int c = 0; c < BN; c += 64) {
+        for (int c = 0; c < BN2; c += 64) {
           uint32_t v[64];
           tmem_ld64(s_addr + c, v);
           tmem_ld_wait();
@@ -588,7 +601,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < BN; c += 64) {
+        for (int c = 0; c < BN2; c += 64) {
           uint32_t v[64];
           tmem_ld64(s_addr + c, v);
           tmem_ld_wait();
@@ -627,11 +640,11 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       auto second_pass = [&](auto masked) {
         constexpr bool MASKED = decltype(masked)::value;
 #pragma unroll
-        for (int c = 0; c < BN; c += 64) {
+        for (int c = 0; c < BN2; c += 64) {
           uint32_t v[64];
           tmem_ld64(s_addr + c, v);
           tmem_ld_wait();
-          unsigned char* prow = sp + (size_t)x * P_BYTES + (c >> 6) * TILE_BYTES + row * 128;
+          unsigned char* prow = sp + (size_t)x * P2_BYTES + (c >> 6) * TILE_BYTES + row * 128;
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
             float pr[8];
@@ -657,15 +670,17 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tc_fence_before();
       mbar_arrive(smem_u32(&bars->s_empty[x]));          // the scores have been read twice: free for tile j + 1
       l += sum;
-      if (key0 + BN > kend_all) {
+      if (key0 + BN2 > kend_all) {
         // keys past the last visible one share pages with stale rows: their values must be
         // zeros, since 0 * NaN would poison the product (both groups write the same zeros)
         if (!mbar_wait(smem_u32(&bars->kv_full[st]), (uint32_t)((j / KV_ST) & 1))) { ok = false; break; }
-        unsigned char* sv = skv + (size_t)st * (K_BYTES + V_BYTES) + K_BYTES;
-        if (key0 + row >= kend_all) {
+        unsigned char* sv = skv + (size_t)st * (K2_BYTES + V2_BYTES) + K2_BYTES;
+        if (row < BN2 && key0 + row >= kend_all) {
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch)
-            *reinterpret_cast<uint4*>(sv + row * 128 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
+          for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              *reinterpret_cast<uint4*>(sv + kb * BN2 * 128 + row * 128 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -707,7 +722,6 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   }
 }
 }  // namespace two
-#endif
 
 }  // namespace
 
@@ -716,8 +730,8 @@ FMX_EXPORT int fmx_attn_prefill_tc_available() { return 1; }
 
 // As fmx_attn_prefill, without a window, for up to 16 query heads per kv head and a page size
 // that divides 128 and is at least 8.  q rows (tokens) are T; the out-of-range part of the
-// last query tile reads as zeros.  variant 1: one query tile per CTA; otherwise two where the
-// head size has that kernel (64).
+// last query tile reads as zeros.  variant 1: one query tile per CTA; otherwise two (where the
+// page size divides that kernel's key tile: 128 keys at head size 64, 64 at 128).
 FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, const void* kv, const int* block_tables,
                                    int bt_stride, const int* row_start, const int* row_ctx, void* out, int rows,
                                    int max_q_len, int nh, int nkv, int page_size, long long num_pages, float scale,
@@ -761,8 +775,7 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
     configured = true;
   }
   const int tok_per_tile = BM / rep;
-#if FMX_HD == 64
-  if (variant != 1) {                         // two query tiles per CTA
+  if (variant != 1 && two::BN2 % page_size == 0) {      // two query tiles per CTA
     static bool configured2 = false;
     if (!configured2) {
       cudaError_t e2 = cudaFuncSetAttribute(two::attn_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -778,7 +791,6 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
     if (e2 != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launch failed: %s", cudaGetErrorString(e2));
     return 0;
   }
-#endif
   dim3 grid((max_q_len + tok_per_tile - 1) / tok_per_tile, nkv, rows);
   cudaError_t e = fmx_launch(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, map_q, map_kv, block_tables,
                              bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size, num_pages, kv_rows, scale, status);

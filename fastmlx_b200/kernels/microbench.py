@@ -99,7 +99,7 @@ def main(argv=None) -> int:
         if k.tc_attention_ok(a.nh, a.nkv, a.hd, a.page, 0):
             impls.append(("tcgen05, one query tile per CTA",
                           lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, variant=1)))
-            if a.hd == 64:
+            if (128 if a.hd == 64 else 64) % a.page == 0:
                 impls.append(("tcgen05, two query tiles per CTA",
                               lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, variant=0)))
         for name, f in impls:
