@@ -25,7 +25,22 @@ __device__ Best block_argmax(const float* row, const unsigned char* keep, int V)
   __shared__ Best part[SBLOCK / 32];
   __shared__ Best result;
   Best b{-INFINITY, -1};
-  for (int i = threadIdx.x; i < V; i += SBLOCK) {
+  int done = 0;
+  if (keep == nullptr && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // four logits per load, several loads in flight; a thread meets its indices in rising order
+    const int V4 = V / 4;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < V4; i += SBLOCK) {
+      const float4 v = row4[i];
+      const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (b.i < 0 || e[j] > b.v) b = Best{e[j], 4 * i + j};
+    }
+    done = 4 * V4;
+  }
+  for (int i = done + threadIdx.x; i < V; i += SBLOCK) {
     if (keep && !keep[i]) continue;
     const float v = row[i];
     if (b.i < 0 || v > b.v) b = Best{v, i};
