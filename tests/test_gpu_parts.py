@@ -1,5 +1,6 @@
 """Each part alone against the plain functions; a schedule that runs a layer twice and lets
-a layer read another layer's cache; and a toy mixer with state of its own, defined here,
+a layer read another layer's cache; and toy parts defined here (a mixer with state of its own,
+a feed-forward that routes tokens to experts, a position encoding that does not rotate),
 registered, built, loaded and stepped through the public interfaces only."""
 from dataclasses import dataclass
 
@@ -317,3 +318,133 @@ def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
             assert o.output_token_ids == seq[len(p):]
     finally:
         registry.unregister(["toy_decay", "ToyDecayForCausalLM"])
+
+
+# ----------------------------------------------------------------------------- a toy routed feed-forward, a toy position encoding
+def make_routed():
+    """Public interfaces only: a feed-forward that sends each token to the one expert its router
+    prefers (router logits in 32-bit, the expert's output scaled by the router's probability),
+    and a position encoding that, instead of rotating, adds a position-dependent sinusoid to q
+    and k before k and v are stored."""
+    from fastmlx_b200.parts import (Embedding, FeedForward, GQAAttention, Linear, LMHead, Model, PositionEncoding,
+                                    PreNormBlock, RMSNorm, SwiGLU)
+
+    class TopOneExperts(FeedForward):
+        supports_cuda_graph = False                      # it sorts tokens by expert on the host
+
+        def __init__(self, width, hidden, n_experts, name):
+            self.router = Linear(width, [(name + ".router", n_experts)])
+            self.experts = [SwiGLU(width, hidden, f"{name}.experts.{e}") for e in range(n_experts)]
+
+        def children(self):
+            return (self.router, *self.experts)
+
+        def forward(self, x, ctx):
+            logits = self.router.forward(x).float()
+            prob = torch.softmax(logits, dim=-1)
+            choice = torch.argmax(logits, dim=-1)
+            out = torch.zeros_like(x)
+            for e, expert in enumerate(self.experts):
+                idx = torch.nonzero(choice == e).flatten()
+                if idx.numel():
+                    y = expert.forward(x.index_select(0, idx).contiguous(), None)
+                    out.index_copy_(0, idx, (y.float() * prob[idx, e:e + 1]).to(x.dtype))
+            return out
+
+    class AddedSinusoid(PositionEncoding):
+        def __init__(self, head_dim, period):
+            self.head_dim, self.period = head_dim, period
+
+        def apply_and_store(self, qkv, ctx, cache, nh, nkv, hd):
+            ang = ctx.positions.to(torch.float32)[:, None] * (2 * torch.pi / self.period) + \
+                torch.arange(hd, device=qkv.device, dtype=torch.float32)[None, :]
+            bump = (0.5 * torch.sin(ang)).to(qkv.dtype)                              # [T, hd]
+            heads = qkv[:, :(nh + nkv) * hd].view(qkv.shape[0], nh + nkv, hd)
+            heads += bump[:, None, :]
+            g = ctx.groups[cache.group]
+            self.rt.k.rope_kv_write(qkv, ctx.positions, None, 0, False, g.slot_mapping if cache.writable else None,
+                                    cache.kv if cache.writable else None, nh, nkv, hd, ctx.status)
+
+    @dataclass(frozen=True)
+    class RoutedCfg:
+        vocab_size: int
+        width: int
+        experts: int
+        period: float
+        eos_token_id: int = -1
+
+        @staticmethod
+        def from_dict(d):
+            return RoutedCfg(int(d["vocab_size"]), int(d["width"]), int(d["experts"]), float(d["period"]))
+
+    def build(cfg):
+        d = cfg.width
+        blocks = [PreNormBlock(GQAAttention(d, 3, 1, 16, AddedSinusoid(16, cfg.period), f"l{i}.attn"),
+                               TopOneExperts(d, 40, cfg.experts, f"l{i}.moe"), RMSNorm(d, 1e-5, f"l{i}.n1"),
+                               RMSNorm(d, 1e-5, f"l{i}.n2")) for i in range(2)]
+        return Model(Embedding(cfg.vocab_size, d, "emb"), blocks, RMSNorm(d, 1e-5, "norm"),
+                     LMHead(cfg.vocab_size, d, "head"), vocab_size=cfg.vocab_size, max_positions=512)
+
+    return RoutedCfg, build
+
+
+def plain_routed(W, toks, experts, period):
+    T = len(toks)
+    pos = torch.arange(T, dtype=torch.float64)
+    h = pl.embedding(torch.tensor(toks), W["emb.weight"])
+    bump = 0.5 * torch.sin((pos[:, None] * (2 * torch.pi / period)).float() + torch.arange(16, dtype=torch.float32)[None, :]).double()
+    for i in range(2):
+        x = pl.rms_norm(h, W[f"l{i}.n1.weight"], 1e-5)
+        q = pl.linear(x, W[f"l{i}.attn.q_proj.weight"]).view(T, 3, 16) + bump[:, None, :]
+        k = pl.linear(x, W[f"l{i}.attn.k_proj.weight"]).view(T, 1, 16) + bump[:, None, :]
+        v = pl.linear(x, W[f"l{i}.attn.v_proj.weight"]).view(T, 1, 16)
+        h = h + pl.linear(pl.attention(q, k, v, 0.25).reshape(T, 48), W[f"l{i}.attn.o_proj.weight"])
+        x = pl.rms_norm(h, W[f"l{i}.n2.weight"], 1e-5)
+        logits = pl.linear(x, W[f"l{i}.moe.router.weight"])
+        prob = torch.softmax(logits, dim=-1)
+        choice = torch.argmax(logits, dim=-1)
+        y = torch.zeros_like(h)
+        for t in range(T):
+            e = int(choice[t])
+            y[t] = prob[t, e] * pl.swiglu(x[t:t + 1], W[f"l{i}.moe.experts.{e}.gate_proj.weight"],
+                                          W[f"l{i}.moe.experts.{e}.up_proj.weight"],
+                                          W[f"l{i}.moe.experts.{e}.down_proj.weight"])[0]
+        h = h + y
+    return pl.linear(pl.rms_norm(h, W["norm.weight"], 1e-5), W["head.weight"]), choice
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):
+    """Neither part exists in the package: both are defined above, registered as an architecture
+    of their own, loaded from a written model folder and replayed under every cut."""
+    from fastmlx_b200 import Engine, SamplingParams, registry, write_random_model
+    from fastmlx_b200.engine.replay import Replayer
+    RoutedCfg, build = make_routed()
+    registry.register(["toy_routed"], RoutedCfg.from_dict, build, replace=True)
+    try:
+        config = {"model_type": "toy_routed", "vocab_size": 61, "width": 48, "experts": 3, "period": 37.0}
+        d = write_random_model(str(tmp_path / "routed"), config, seed=9)
+        W = tiny.load_plain_weights(d)
+        prompts = {f"r{i}": tiny.rand_tokens(n, 61, 20 + i) for i, n in enumerate([23, 40, 5, 33])}
+        ref, used = {}, set()
+        for r, t in prompts.items():
+            ref[r], choice = plain_routed(W, t, 3, 37.0)
+            used |= set(choice.tolist())
+        assert used == {0, 1, 2}, "the test should exercise every expert"
+        rp = Replayer(d, "float32", 256, page_size=8)
+        assert not rp.model.graph_safe
+        for cut in (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
+            steps = cut(prompts)
+            rows = traces.collect(steps, [rp.step(s) for s in steps])
+            for r, t in prompts.items():
+                got = torch.tensor([rows[r][i].tolist() for i in range(len(t))], dtype=torch.float64)
+                assert (got - ref[r]).abs().max().item() / ref[r].abs().max().item() < 1e-5, (cut.__name__, r)
+            rp.manager.check()
+        eng = Engine(d, dtype="float32", block_size=8, max_cache_tokens=512, max_concurrent_requests=2)
+        outs = eng.generate([prompts["r0"], prompts["r2"]], SamplingParams(max_tokens=5, temperature=0.0))
+        for p, o in zip([prompts["r0"], prompts["r2"]], outs):
+            seq = list(p)
+            for _ in range(5):
+                seq.append(int(torch.argmax(plain_routed(W, seq, 3, 37.0)[0][-1])))
+            assert o.output_token_ids == seq[len(p):]
+    finally:
+        registry.unregister(["toy_routed"])
