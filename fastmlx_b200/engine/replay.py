@@ -54,7 +54,12 @@ class Replayer:
                 if req is None:
                     req = self.manager.add_request(rid)
                     fresh.append(rid)
-                entries.append(StepEntry(req, [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])]))
+                tokens = [int(t) for t in e.get("tokens", [])]
+                if not tokens:                         # a request named without tokens runs nothing
+                    if e.get("want"):
+                        raise ValueError(f"request {rid!r} asks for logits of a step that brings it no tokens")
+                    continue
+                entries.append(StepEntry(req, tokens, [int(w) for w in e.get("want", [])]))
             logits = self.step_fn.run(entries) if entries else None
         except BaseException:
             for rid in fresh:
