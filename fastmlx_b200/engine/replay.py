@@ -41,7 +41,8 @@ class Replayer:
         self.manager = CacheManager(self.model.cache_needs(), page_size=page_size,
                                     num_pages=pool_pages(max_tokens, page_size), max_requests=max_live,
                                     dtype=self.rt.dtype, device=self.rt.device)
-        self.step_fn = StepFunction(self.model, self.manager, self.rt)
+        # replay feeds what the trace says: positions past max_position_embeddings are the trace's business
+        self.step_fn = StepFunction(self.model, self.manager, self.rt, position_limit=False)
 
     def step(self, record: dict):
         """Run one trace record; -> float32 numpy [wanted, vocab] or None."""

@@ -80,8 +80,12 @@ class _DecodeGraph:
 
 
 class StepFunction:
-    def __init__(self, model, manager: CacheManager, rt, cuda_graphs: bool = False, max_graph_rows: int = 256):
+    def __init__(self, model, manager: CacheManager, rt, cuda_graphs: bool = False, max_graph_rows: int = 256,
+                 position_limit: bool = True):
+        """position_limit: refuse a step that would take a request past the model's
+        max_position_embeddings (the serving policy); replay turns it off and runs what it is given."""
         self.model, self.manager, self.rt = model, manager, rt
+        self.position_limit = bool(position_limit)
         self.cuda_graphs = bool(cuda_graphs) and rt.device.type == "cuda" and bool(getattr(model, "graph_safe", False))
         self.max_graph_rows = max_graph_rows
         self.graphs: dict[tuple[int, int], _DecodeGraph] = {}
@@ -130,7 +134,7 @@ class StepFunction:
             if id(e.request) in seen:
                 raise StepError("a request appears twice in one step")
             seen.add(id(e.request))
-            limit = self.model.max_positions
+            limit = self.model.max_positions if self.position_limit else 0
             if limit and e.request.length + len(e.tokens) > limit:
                 raise StepError(f"request {e.request.request_id!r} would pass max_position_embeddings ({limit})")
         taken = []

@@ -144,6 +144,24 @@ def test_long_decoding(models, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_runs_past_max_position_embeddings(models, dtype):
+    """Replay feeds what the trace says: a sequence longer than the configuration's
+    max_position_embeddings is run (rotary positions have no table to run out of); serving
+    refuses such a request in the scheduler instead."""
+    d, _, _ = models["A"]
+    cfg = tiny.TINY_A
+    n = cfg["max_position_embeddings"] + 40
+    toks = tiny.rand_tokens(n, cfg["vocab_size"], 78)
+    W = tiny.load_plain_weights(d)
+    ref = plain_llama.forward(cfg, W, toks, round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:n - 20], "want": list(range(n - 20))}], "end": []}]
+    steps += [{"step": i - (n - 21), "entries": [{"id": "x", "tokens": [toks[i]], "want": [0]}], "end": []} for i in range(n - 20, n)]
+    steps[-1]["end"] = ["x"]
+    outs, _ = _run(d, dtype, steps, 256, 16)
+    _compare(steps, outs, {"x": toks}, {"x": ref}, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_first_tokens(models, name, dtype):
     """Sequences of one and two tokens, and a first step of a single token."""
