@@ -24,7 +24,7 @@ from .batch import StepEntry
 from .loading import load_model
 from .step import StepFunction
 
-MAX_LIVE = 4
+MAX_LIVE = 8          # request slots; traces keep up to four live, a step may name one more while another ends
 
 
 def pool_pages(max_tokens: int, page_size: int) -> int:
