@@ -68,20 +68,24 @@ FMX_EXPORT int fmx_gather_rows(const void* table, const int* ids, void* out, int
   return 0;
 }
 
-// residual' = round(residual + x) (32-bit sum, when residual is given); out = residual' *
-// 1/sqrt(mean(residual'^2) + eps) * w.  One block per row; the sum of squares is taken in
-// a fixed order that depends on the row's width only.
-template <typename T, int BLOCK>
-__global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const float* __restrict__ w,
-                                   T* __restrict__ out, int d, float eps) {
+// residual' = round(residual + x) (32-bit sum, when residual is given; rounded to the residual's
+// own type, which may be float beside bfloat16 activations: the stream then never rounds); out =
+// residual' * 1/sqrt(mean(residual'^2) + eps) * w.  `init`: residual' = x (the stream's first
+// value); x may be null when a residual is given (residual' = residual).  One block per row; the
+// sum of squares is taken in a fixed order that depends on the row's width only.
+template <typename T, typename TR, int BLOCK>
+__global__ void add_rmsnorm_kernel(const T* x, TR* residual, const float* __restrict__ w, T* __restrict__ out, int d,
+                                   float eps, int init) {
+  pdl_wait();
+  pdl_trigger();
   const long long row = blockIdx.x;
-  const T* xr = x + row * d;
-  T* rr = residual ? residual + row * d : nullptr;
+  const T* xr = x ? x + row * d : nullptr;
+  TR* rr = residual ? residual + row * d : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += BLOCK) {
-    float v = to_f(xr[i]);
+    float v = xr ? to_f(xr[i]) : 0.f;
     if (rr) {
-      const T h = from_f<T>(v + to_f(rr[i]));
+      const TR h = from_f<TR>(init ? v : v + to_f(rr[i]));
       rr[i] = h;
       v = to_f(h);
     }
@@ -89,40 +93,65 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
   }
   ss = block_sum<BLOCK>(ss);
   const float rstd = 1.0f / sqrtf(ss / (float)d + eps);
-  const T* src = rr ? rr : xr;
   T* o = out + row * d;
-  for (int i = threadIdx.x; i < d; i += BLOCK) o[i] = from_f<T>(to_f(src[i]) * rstd * w[i]);
+  for (int i = threadIdx.x; i < d; i += BLOCK) o[i] = from_f<T>((rr ? to_f(rr[i]) : to_f(xr[i])) * rstd * w[i]);
 }
 
 // bfloat16 rows whose width is a multiple of 8: 16-byte loads, the row kept in registers
 // between the sum of squares and the scaling (up to CH chunks of 8 per thread).  The sum of
 // squares runs over a thread's elements in index order, then over the block in a fixed tree.
-template <int BLOCK, int CH>
+// RES_F32: the residual stream is float (two 16-byte accesses per eight elements).
+template <int BLOCK, int CH, bool RES_F32>
 __global__ void __launch_bounds__(BLOCK)
-add_rmsnorm_bf16_vec_kernel(const bf16* x, bf16* residual, const float* __restrict__ w, bf16* out, int d, float eps) {
+add_rmsnorm_bf16_vec_kernel(const bf16* x, void* residual, const float* __restrict__ w, bf16* out, int d, float eps,
+                            int init) {
   pdl_wait();
   pdl_trigger();
   const long long row = blockIdx.x;
   const int nvec = d / 8;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
-  uint4* rr = residual ? reinterpret_cast<uint4*>(residual + row * d) : nullptr;
+  const uint4* xr = x ? reinterpret_cast<const uint4*>(x + row * d) : nullptr;
+  uint4* rr = (residual && !RES_F32) ? reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(residual) + row * d) : nullptr;
+  float4* rf = (residual && RES_F32) ? reinterpret_cast<float4*>(reinterpret_cast<float*>(residual) + row * d) : nullptr;
   float v[CH][8];
   float ss = 0.f;
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
     const int i = threadIdx.x + c * BLOCK;
     if (i < nvec) {
-      uint4 a = xr[i];
-      const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
-      if (rr) {
-        uint4 b = rr[i];
+      float xv[8];
+      if (xr) {
+        uint4 a = xr[i];
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 fa = __bfloat1622float2(ap[e]);
+          xv[2 * e] = fa.x;
+          xv[2 * e + 1] = fa.y;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xv[e] = 0.f;
+      }
+      if (RES_F32 && rf) {
+        float4 r0 = make_float4(0.f, 0.f, 0.f, 0.f), r1 = r0;
+        if (!init) {
+          r0 = rf[2 * i];
+          r1 = rf[2 * i + 1];
+        }
+        v[c][0] = xv[0] + r0.x; v[c][1] = xv[1] + r0.y; v[c][2] = xv[2] + r0.z; v[c][3] = xv[3] + r0.w;
+        v[c][4] = xv[4] + r1.x; v[c][5] = xv[5] + r1.y; v[c][6] = xv[6] + r1.z; v[c][7] = xv[7] + r1.w;
+        rf[2 * i] = make_float4(v[c][0], v[c][1], v[c][2], v[c][3]);
+        rf[2 * i + 1] = make_float4(v[c][4], v[c][5], v[c][6], v[c][7]);
+      } else if (rr) {
+        uint4 b = make_uint4(0u, 0u, 0u, 0u);
+        if (!init) b = rr[i];
         const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
         uint4 hsum;
         __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&hsum);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float2 fa = __bfloat1622float2(ap[e]), fb = __bfloat1622float2(bp[e]);
-          hp[e] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+          const float2 fb = __bfloat1622float2(bp[e]);
+          hp[e] = __floats2bfloat162_rn(xv[2 * e] + fb.x, xv[2 * e + 1] + fb.y);
           const float2 fh = __bfloat1622float2(hp[e]);
           v[c][2 * e] = fh.x;
           v[c][2 * e + 1] = fh.y;
@@ -130,11 +159,7 @@ add_rmsnorm_bf16_vec_kernel(const bf16* x, bf16* residual, const float* __restri
         rr[i] = hsum;
       } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 fa = __bfloat1622float2(ap[e]);
-          v[c][2 * e] = fa.x;
-          v[c][2 * e + 1] = fa.y;
-        }
+        for (int e = 0; e < 8; ++e) v[c][e] = xv[e];
       }
 #pragma unroll
       for (int e = 0; e < 8; ++e) ss = fmaf(v[c][e], v[c][e], ss);
@@ -162,25 +187,47 @@ add_rmsnorm_bf16_vec_kernel(const bf16* x, bf16* residual, const float* __restri
 
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
+template <bool RES_F32>
+static void launch_add_rmsnorm_vec(const void* x, void* residual, const float* w, void* out, int rows, int d, float eps,
+                                   int init, cudaStream_t stream) {
+  if (d <= 128 * 8)
+    fmx_launch(add_rmsnorm_bf16_vec_kernel<128, 1, RES_F32>, dim3(rows), dim3(128), 0, stream, (const bf16*)x, residual, w,
+               (bf16*)out, d, eps, init);
+  else if (d <= 256 * 8)
+    fmx_launch(add_rmsnorm_bf16_vec_kernel<256, 1, RES_F32>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, residual, w,
+               (bf16*)out, d, eps, init);
+  else
+    fmx_launch(add_rmsnorm_bf16_vec_kernel<256, 4, RES_F32>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, residual, w,
+               (bf16*)out, d, eps, init);
+}
+
+// x, out: `dtype`; residual: `res_dtype` (float beside bfloat16 activations keeps the stream
+// unrounded), or null.  init != 0: the residual is written, not read (the stream's first value).
+// x may be null when there is a residual.
 FMX_EXPORT int fmx_add_rmsnorm(const void* x, void* residual, const float* w, void* out, int rows, int d, float eps,
-                               int dtype, cudaStream_t stream) {
+                               int dtype, int res_dtype, int init, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (rows < 0 || d <= 0) return fmx_fail("fmx_add_rmsnorm: bad sizes rows=%d d=%d", rows, d);
+  if (x == nullptr && (residual == nullptr || init)) return fmx_fail("fmx_add_rmsnorm: nothing to normalise");
+  if (residual != nullptr && res_dtype != dtype && !(dtype == FMX_BF16 && res_dtype == FMX_F32))
+    return fmx_fail("fmx_add_rmsnorm: a residual of type %d beside activations of type %d", res_dtype, dtype);
+  const bool res_f32 = residual != nullptr && res_dtype == FMX_F32;
   if (dtype == FMX_F32)
-    add_rmsnorm_kernel<float, 256><<<rows, 256, 0, stream>>>((const float*)x, (float*)residual, w, (float*)out, d, eps);
+    fmx_launch(add_rmsnorm_kernel<float, float, 256>, dim3(rows), dim3(256), 0, stream, (const float*)x, (float*)residual, w,
+               (float*)out, d, eps, init);
   else if (dtype == FMX_BF16) {
-    const bool vec = d % 8 == 0 && aligned16(x) && aligned16(out) && aligned16(w) && (!residual || aligned16(residual));
-    if (vec && d <= 128 * 8)
-      fmx_launch(add_rmsnorm_bf16_vec_kernel<128, 1>, dim3(rows), dim3(128), 0, stream, (const bf16*)x, (bf16*)residual, w,
-                 (bf16*)out, d, eps);
-    else if (vec && d <= 256 * 8)
-      fmx_launch(add_rmsnorm_bf16_vec_kernel<256, 1>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, (bf16*)residual, w,
-                 (bf16*)out, d, eps);
-    else if (vec && d <= 256 * 8 * 4)
-      fmx_launch(add_rmsnorm_bf16_vec_kernel<256, 4>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, (bf16*)residual, w,
-                 (bf16*)out, d, eps);
+    const bool vec = d % 8 == 0 && d <= 256 * 8 * 4 && aligned16(x) && aligned16(out) && aligned16(w) &&
+                     (!residual || aligned16(residual));
+    if (vec && res_f32)
+      launch_add_rmsnorm_vec<true>(x, residual, w, out, rows, d, eps, init, stream);
+    else if (vec)
+      launch_add_rmsnorm_vec<false>(x, residual, w, out, rows, d, eps, init, stream);
+    else if (res_f32)
+      fmx_launch(add_rmsnorm_kernel<bf16, float, 256>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, (float*)residual, w,
+                 (bf16*)out, d, eps, init);
     else
-      add_rmsnorm_kernel<bf16, 256><<<rows, 256, 0, stream>>>((const bf16*)x, (bf16*)residual, w, (bf16*)out, d, eps);
+      fmx_launch(add_rmsnorm_kernel<bf16, bf16, 256>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, (bf16*)residual, w,
+                 (bf16*)out, d, eps, init);
   } else
     return fmx_fail("fmx_add_rmsnorm: unknown dtype %d", dtype);
   FMX_LAUNCH_CHECK();

@@ -69,15 +69,25 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, status, out_dtype=None) ->
     return gather_rows(table, ids, status, BAD_TOKEN)
 
 
-def add_rmsnorm(x: torch.Tensor, residual, weight: torch.Tensor, eps: float):
+def add_rmsnorm(x, residual, weight: torch.Tensor, eps: float, stream_dtype=None, out_dtype=None):
     """-> (norm(residual + x) * weight, residual + x); the sum replaces `residual` in place.
-    Without a residual, x itself is the stream and is returned as such."""
+    Without a residual, x is the stream's first value: it is returned as the stream, as it is or,
+    when `stream_dtype` is float32 beside bfloat16 activations, as a 32-bit copy that the later
+    sums then never round.  x may be None when there is a residual (the stream itself is
+    normalised; `out_dtype` then names the activations' type)."""
     _need_cuda(x, residual, weight)
-    assert x.dim() == 2 and x.is_contiguous() and weight.dtype == torch.float32
-    assert residual is None or (residual.shape == x.shape and residual.is_contiguous() and residual.dtype == x.dtype)
-    out = torch.empty_like(x)
-    call("common", "fmx_add_rmsnorm", x.data_ptr(), _ptr(residual), weight.data_ptr(), out.data_ptr(),
-         x.shape[0], x.shape[1], float(eps), _dt(x), _stream())
+    assert weight.dtype == torch.float32
+    ref = x if x is not None else residual
+    assert ref is not None and ref.dim() == 2 and ref.is_contiguous()
+    act = x.dtype if x is not None else (out_dtype or residual.dtype)
+    init = 0
+    if residual is None and stream_dtype is not None and stream_dtype != act:
+        residual = torch.empty(ref.shape, dtype=stream_dtype, device=ref.device)
+        init = 1
+    assert residual is None or (residual.shape == ref.shape and residual.is_contiguous())
+    out = torch.empty(ref.shape, dtype=act, device=ref.device)
+    call("common", "fmx_add_rmsnorm", _ptr(x), _ptr(residual), weight.data_ptr(), out.data_ptr(), ref.shape[0], ref.shape[1],
+         float(eps), _dt(out), _dt(residual) if residual is not None else _dt(out), init, _stream())
     return out, (residual if residual is not None else x)
 
 

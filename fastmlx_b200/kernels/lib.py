@@ -22,7 +22,7 @@ _SIGNATURES = {
     "common": {
         "fmx_gather_rows": [_P, _P, _P, _I, _I, _L, _I, _P, _I, _P],
         "fmx_gather_rows_f32_to_bf16": [_P, _P, _P, _I, _I, _L, _P, _I, _P],
-        "fmx_add_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
+        "fmx_add_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _P],
         "fmx_silu_mul": [_P, _P, _I, _I, _I, _I, _P],
         "fmx_gemm_simple": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
         "fmx_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _L, _I, _P, _P],

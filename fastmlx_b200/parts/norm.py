@@ -1,6 +1,8 @@
 """RMSNorm with the residual sum fused in front of it."""
 from __future__ import annotations
 
+import torch
+
 from .base import Norm, Runtime, WeightSpec, to_f32_vector
 
 
@@ -22,9 +24,11 @@ class RMSNorm(Norm):
         return self.weight.numel() * 4
 
     def forward(self, x, residual):
-        if x is None:
-            x, residual = residual, None
-        return self.rt.k.add_rmsnorm(x, residual, self.weight, self.eps)
+        # Beside bfloat16 activations the stream (the running sum of every layer's output) is kept
+        # in 32-bit: each layer's contribution is small against it, and rounding the sum to
+        # bfloat16 twice a layer is what a deep model's logits would feel most.
+        return self.rt.k.add_rmsnorm(x, residual, self.weight, self.eps, stream_dtype=torch.float32,
+                                     out_dtype=self.rt.dtype)
 
     def fold(self):
         """(weight, eps) for a kernel that normalises its input rows itself."""

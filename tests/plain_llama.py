@@ -195,12 +195,12 @@ def forward(cfg: dict, W: dict, tokens, round_to=None, return_hidden: bool = Fal
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
         x = _rnd(rms_norm(h, W[p + "input_layernorm.weight"], eps), round_to)
-        h = _rnd(h + attention_block(x, W, p, cfg, positions, inv_freq, round_to), round_to)
+        h = h + attention_block(x, W, p, cfg, positions, inv_freq, round_to)      # the stream itself is never rounded
         y = _rnd(rms_norm(h, W[p + "post_attention_layernorm.weight"], eps), round_to)
         y = swiglu(y, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
                    W[p + "mlp.down_proj.weight"], mbias(p, "mlp.gate_proj"),
                    mbias(p, "mlp.up_proj"), mbias(p, "mlp.down_proj"), round_to)
-        h = _rnd(h + y, round_to)
+        h = h + y
     hn = _rnd(rms_norm(h, W["model.norm.weight"], eps), round_to)
     head = W["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else W["lm_head.weight"]
     logits = linear(hn, head)

@@ -24,15 +24,18 @@ def embedding(ids, table, status, out_dtype=None):
     return out.to(out_dtype) if out_dtype is not None else out
 
 
-def add_rmsnorm(x, residual, weight, eps):
+def add_rmsnorm(x, residual, weight, eps, stream_dtype=None, out_dtype=None):
+    act = x.dtype if x is not None else (out_dtype or residual.dtype)
     if residual is not None:
-        h = (x.to(F64) + residual.to(F64)).to(x.dtype)
-        residual.copy_(h)
+        h = residual.to(F64) if x is None else (x.to(F64) + residual.to(F64))
+        residual.copy_(h.to(residual.dtype))
+    elif stream_dtype is not None and stream_dtype != act:
+        residual = x.to(stream_dtype)
     else:
         residual = x
     h = residual.to(F64)
     out = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * weight.to(F64)
-    return out.to(x.dtype), residual
+    return out.to(act), residual
 
 
 def silu_mul(gate_up, block=None):

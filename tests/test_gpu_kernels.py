@@ -82,6 +82,33 @@ def test_add_rmsnorm(dtype, rows, d, eps, with_residual):
         assert res_out.data_ptr() == xd.data_ptr()
 
 
+@pytest.mark.parametrize("rows,d,eps", [(1, 64, 1e-5), (5, 192, 1e-6), (33, 80, 1e-3), (4, 2048, 1e-5), (3, 1000, 1e-5), (2, 5, 0.0),
+                                        (8, 8192, 1e-5), (3, 8200, 1e-5)])
+def test_add_rmsnorm_with_a_32_bit_stream(rows, d, eps):
+    """bfloat16 activations beside a stream kept in 32-bit: the first call makes the stream from
+    x, later calls add to it without rounding it, and the stream alone can be normalised."""
+    x = rnd(rows, d, dtype=torch.bfloat16, seed=1, scale=3.0)
+    y = rnd(rows, d, dtype=torch.bfloat16, seed=2, scale=0.01)          # small against the stream, as a layer's output is
+    w = 1 + rnd(d, seed=3, scale=0.1)
+    wd = w.to(DEV)
+    ref0, ref_stream = plain_ops.add_rmsnorm(x.clone(), None, w, eps, stream_dtype=torch.float32)
+    out0, stream = k().add_rmsnorm(x.to(DEV), None, wd, eps, stream_dtype=torch.float32)
+    assert stream.dtype == torch.float32 and out0.dtype == torch.bfloat16
+    assert torch.equal(stream.cpu(), x.float())
+    close(out0, ref0, torch.bfloat16, "norm of the first value")
+    for i in range(3):
+        ref1, ref_stream = plain_ops.add_rmsnorm(y.clone(), ref_stream, w, eps)
+        out1, stream2 = k().add_rmsnorm(y.to(DEV), stream, wd, eps)
+        assert stream2.data_ptr() == stream.data_ptr()
+        close(stream, ref_stream, torch.float32, "32-bit stream")
+        close(out1, ref1, torch.bfloat16, "norm over a 32-bit stream")
+    # three additions of a value that bfloat16 would have lost against the stream
+    assert (stream.cpu() - x.float() - 3 * y.float()).abs().max() < 1e-5 * x.float().abs().max()
+    ref2, _ = plain_ops.add_rmsnorm(None, ref_stream.clone(), w, eps, out_dtype=torch.bfloat16)
+    out2, _ = k().add_rmsnorm(None, stream, wd, eps, out_dtype=torch.bfloat16)
+    close(out2, ref2, torch.bfloat16, "norm of the stream alone")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,I", [(1, 176), (7, 512), (3, 200), (65, 8192), (2, 1)])
 def test_silu_mul(dtype, rows, I):
