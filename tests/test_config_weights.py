@@ -14,7 +14,7 @@ from fastmlx_b200.config import ConfigError, LlamaConfig
 from fastmlx_b200.weights import WeightError, load_checkpoint, shard_files, write_random_model
 from fastmlx_b200.weights import safetensors_io as st
 
-REF = os.environ.get("FASTMLX_REFERENCE", "/root/reference")
+REF = tiny.reference_dir()
 needs_ref = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "compute", "testdata")),
                                reason="the reference checkout is not present")
 

@@ -4,13 +4,15 @@ import json
 import os
 
 import pytest
+
+import tiny
 import torch
 
 import plain_sampling as ps
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-REF = os.environ.get("FASTMLX_REFERENCE", "/root/reference")
+REF = tiny.reference_dir()
 HAVE_REF = os.path.isdir(os.path.join(REF, "compute", "testdata"))
 
 

@@ -5,10 +5,12 @@ import os
 
 import pytest
 
+import tiny
+
 import plain_sampling as ps
 from fastmlx_b200.sampling import SamplingParams, uniform_for
 
-REF = os.environ.get("FASTMLX_REFERENCE", "/root/reference")
+REF = tiny.reference_dir()
 needs_ref = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "compute", "testdata")),
                                reason="the reference checkout is not present")
 

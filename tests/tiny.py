@@ -52,3 +52,12 @@ def load_plain_weights(model_dir):
 def rand_tokens(n, vocab, seed):
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def reference_dir() -> str:
+    """Where tamnd/fastmlx's checkout lies, if anywhere: $FASTMLX_REFERENCE, or a folder
+    `reference` beside this repository.  Its test data are golden vectors for a few tests,
+    which are skipped without it."""
+    import os
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return os.environ.get("FASTMLX_REFERENCE") or os.path.join(os.path.dirname(here), "reference")
