@@ -1,21 +1,33 @@
 // Paged causal attention for prompt portions on the fifth-generation tensor cores
 // (head sizes 64 and 128; compile with -DFMX_HD=<head size>).
 //
-// A CTA owns 128 packed query rows of one request and one kv head (row i = token i / rep,
-// query head g*rep + i % rep) and walks over the keys in tiles of 128.
+// Query rows are "packed": row i of a tile stands for token i / rep and query head
+// g*rep + i % rep (rep = query heads per kv head), so that all rows of a tile read the same
+// keys and values; a tile holds 128 / rep tokens (its last rows are idle when rep does not
+// divide 128).  Two kernels:
+//
+//  * two query tiles per CTA (the default; further down, namespace `two`): tiles A and B share
+//    every K/V tile, each with its own softmax group of four warps and one thread per row;
+//  * one query tile per CTA (below): eight softmax warps, two threads per row.  It remains
+//    for page sizes that do not divide the other kernel's key tile.
+//
+// The one-tile kernel: a CTA owns 128 packed query rows of one request and one kv head and
+// walks over the keys in tiles of 128.
 //   warp 0           : producer.  One 3-D TMA load brings the query tile; per key tile, one
-//                      2-D TMA load per page (one lane per page) brings K and one brings V (a page of a kv head is
-//                      a contiguous [page_size, hd] block of the cache), all with the 128-byte
+//                      2-D TMA load per page (one lane per page, so that the block-table reads
+//                      of a tile overlap) brings K and one brings V (a page of a kv head is a
+//                      contiguous [page_size, hd] block of the cache), all with the 128-byte
 //                      swizzle the MMA expects.  Pages beyond the last visible key are replaced
 //                      by an out-of-bounds box, which TMA fills with zeros.
 //   warp 1, one lane : MMA issuer.  S_j = Q K_j^T (tcgen05.mma, both operands K-major) into one
 //                      of two score buffers in tensor memory, then, one tile behind, O_j = P_j V_j
 //                      (P from shared memory, V as an MN-major operand) into one of two output
 //                      buffers: the tensor core computes S_{j+1} while the softmax of tile j runs.
-//   warps 2-5        : softmax and epilogue, one thread per query row.  Scores come from tensor
-//                      memory (tcgen05.ld), running maximum and sum are 32-bit, probabilities go
-//                      to shared memory in bfloat16, the per-tile outputs are rescaled and summed
-//                      in registers.
+//   warps 2-9        : softmax and epilogue, two threads per query row (64 keys and half of the
+//                      head dimension each; the halves' maxima meet through shared memory).
+//                      Scores come from tensor memory (tcgen05.ld), running maximum and sum are
+//                      32-bit, probabilities go to shared memory in bfloat16, the per-tile outputs
+//                      are rescaled and summed in registers.
 // Every barrier wait is bounded by time; a wait that runs out leaves FMX_WAIT_EXPIRED in the
 // status word and the CTA frees its tensor memory and returns.  No cluster, no multicast.
 #include <cuda.h>
