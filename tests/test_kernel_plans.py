@@ -25,3 +25,10 @@ def test_stream_plan_covers_every_unit_once():
             while c_hi + 1 < ctas and start(c_hi + 1) <= t1: c_hi += 1
             assert (c_lo, c_hi) == (owner[t0], owner[t1])
             assert sorted(set(owner[t0:t1 + 1])) == list(range(c_lo, c_hi + 1))
+
+
+def test_short_prompts_go_to_the_library_product():
+    """Fewer tiles than about a round of the SMs: the whole-tile kernel would leave most idle."""
+    from fastmlx_b200 import kernels as k
+    assert k.tc_fills_the_gpu(2048, 2048) and k.tc_fills_the_gpu(2048, 3072) and k.tc_fills_the_gpu(512, 16384)
+    assert not k.tc_fills_the_gpu(512, 2048) and not k.tc_fills_the_gpu(1024, 3072) and not k.tc_fills_the_gpu(128, 8192)
