@@ -234,8 +234,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
                     long long num_pages, float scale, int window, int* status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-  // the last query tiles of a row see the most keys: they start first
-  const int r = blockIdx.z, g = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+  // The last query tiles of a row see the most keys.  Blocks start in the order x, y, z: with the
+  // tile index in z the longest blocks of every head and row start first.
+  const int r = blockIdx.y, g = blockIdx.x, tile = gridDim.z - 1 - blockIdx.z;
   const int rep = nh / nkv;
   const int t0 = row_start[r], q_len = row_start[r + 1] - t0, ctx = row_ctx[r];
   const int n_packed = q_len * rep;
@@ -654,7 +655,9 @@ FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* k
     configured = true;
   }
   const int rep = nh / nkv;
-  dim3 grid(((long long)max_q_len * rep + BM - 1) / BM, nkv, rows);
+  const long long tiles = ((long long)max_q_len * rep + BM - 1) / BM;
+  if (tiles > 65535) return fmx_fail("fmx_attn_prefill: %d query tokens in one row are too many for one launch", max_q_len);
+  dim3 grid(nkv, rows, (unsigned)tiles);
   attn_prefill_kernel<<<grid, THREADS, prefill_smem(), stream>>>(
       (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv,
       page_size, num_pages, scale, window, status);

@@ -93,8 +93,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   unsigned char* sp = skv + (size_t)KV_STAGES * (K_BYTES + V_BYTES);   // [P_BUFS]
   Bars* bars = reinterpret_cast<Bars*>(sp + (size_t)P_BUFS * P_BYTES);
 
-  // the last query tiles of a row see the most keys: they start first
-  const int r = blockIdx.z, g = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+  // The last query tiles of a row see the most keys.  Blocks start in the order x, y, z: with the
+  // tile index in z the longest blocks of every head and row start first and the short ones fill in
+  // behind them (with it in x, the last heads' long blocks started late and ran on alone).
+  const int r = blockIdx.y, g = blockIdx.x, tile = gridDim.z - 1 - blockIdx.z;
   const int rep = nh / nkv;
   const int tok_per_tile = BM / rep;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -415,8 +417,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   unsigned char* sp = skv + (size_t)KV_ST * (K2_BYTES + V2_BYTES);        // [2] probabilities
   Bars2* bars = reinterpret_cast<Bars2*>(sp + 2 * (size_t)P2_BYTES);
 
-  // the last query tiles of a row see the most keys: they start first
-  const int r = blockIdx.z, g = blockIdx.y, pair = gridDim.x - 1 - blockIdx.x;
+  // the pairs that see the most keys start first, for every head and row (see the one-tile kernel)
+  const int r = blockIdx.y, g = blockIdx.x, pair = gridDim.z - 1 - blockIdx.z;
   const int rep = nh / nkv;
   const int tok_per_tile = BM / rep;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -754,6 +756,8 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
   if (rep > 16) return fmx_fail("fmx_attn_prefill_tc: %d query heads per kv head is above 16", rep);
   if (page_size < 8 || BN % page_size) return fmx_fail("fmx_attn_prefill_tc: a page of %d tokens does not tile 128 keys", page_size);
   if (rows > 65535 || nkv > 65535) return fmx_fail("fmx_attn_prefill_tc: too many rows or kv heads for one launch");
+  if ((long long)max_q_len * (nh / nkv) > 65535LL * BM)
+    return fmx_fail("fmx_attn_prefill_tc: %d query tokens in one row are too many for one launch", max_q_len);
   if (q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)kv & 15)) return fmx_fail("fmx_attn_prefill_tc: q and the cache must be 16-byte aligned");
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return fmx_fail("fmx_attn_prefill_tc: cuTensorMapEncodeTiled is not available from this driver");
@@ -796,14 +800,14 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
                                              cudaGetErrorString(e2));
       configured2 = true;
     }
-    dim3 grid2((max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile), nkv, rows);
+    dim3 grid2(nkv, rows, (max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile));
     cudaError_t e2 = fmx_launch(two::attn_prefill_tc2_kernel, grid2, dim3(two::THREADS2), two::SMEM2, stream, map_q, map_kv,
                                 block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size, num_pages,
                                 kv_rows, scale, status);
     if (e2 != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launch failed: %s", cudaGetErrorString(e2));
     return 0;
   }
-  dim3 grid((max_q_len + tok_per_tile - 1) / tok_per_tile, nkv, rows);
+  dim3 grid(nkv, rows, (max_q_len + tok_per_tile - 1) / tok_per_tile);
   cudaError_t e = fmx_launch(attn_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, map_q, map_kv, block_tables,
                              bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size, num_pages, kv_rows, scale, status);
   if (e != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launch failed: %s", cudaGetErrorString(e));

@@ -586,6 +586,32 @@ def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window, rope=None) 
 
 
 # ----------------------------------------------------------------------------- sampling
+ARGMAX_ROWS, ARGMAX_CHUNKS = 1024, 32      # the split greedy choice's workspace: rows x chunks pairs
+ARGMAX_MIN_CHUNK = 4096                    # logits per block at least
+_argmax_ws: dict = {}
+
+
+def argmax_workspace(device):
+    """Chunk results and tickets of the split greedy choice, one pair per device, made once;
+    the tickets are zero between launches."""
+    ws = _argmax_ws.get(device)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the greedy choice's workspace must exist before a CUDA graph is captured")
+        ws = (torch.empty(ARGMAX_ROWS * ARGMAX_CHUNKS * 2, dtype=torch.int32, device=device),
+              torch.zeros(ARGMAX_ROWS, dtype=torch.int32, device=device))
+        _argmax_ws[device] = ws
+    return ws
+
+
+def argmax_chunks(rows: int, V: int) -> int:
+    """Blocks per row of the greedy choice: enough to fill the SMs about once, each with at
+    least ARGMAX_MIN_CHUNK logits; 1 = the one-block kernel."""
+    if rows > ARGMAX_ROWS:
+        return 1
+    return max(1, min(ARGMAX_CHUNKS, V // ARGMAX_MIN_CHUNK, -(-NUM_SMS // max(rows, 1))))
+
+
 def sample(logits: torch.Tensor, temperature=None, uniform=None, keep=None) -> torch.Tensor:
     """Row-wise token choice: argmax where temperature <= 0 (or None), else a draw from
     softmax(logits / temperature) among keep != 0 by the given uniform numbers."""
@@ -595,8 +621,11 @@ def sample(logits: torch.Tensor, temperature=None, uniform=None, keep=None) -> t
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     if keep is not None:
         assert keep.dtype == torch.uint8 and keep.shape == logits.shape and keep.stride(1) == 1
+    chunks = argmax_chunks(rows, V) if temperature is None and keep is None else 1
+    partial, tickets = argmax_workspace(logits.device) if chunks > 1 else (None, None)
     call("common", "fmx_sample", logits.data_ptr(), logits.stride(0), rows, V, _ptr(temperature), _ptr(uniform),
-         _ptr(keep), keep.stride(0) if keep is not None else 0, out.data_ptr(), _stream())
+         _ptr(keep), keep.stride(0) if keep is not None else 0, out.data_ptr(), chunks, _ptr(partial), ARGMAX_CHUNKS,
+         _ptr(tickets), ARGMAX_ROWS, _stream())
     return out
 
 

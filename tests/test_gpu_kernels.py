@@ -695,6 +695,32 @@ def test_argmax_first_index_on_ties(V):
     assert got[1] == 7 and got[2] == 0 and got[3] == V - 1
 
 
+@pytest.mark.parametrize("rows,V,pad", [(1, 128256, 0), (8, 128256, 0), (3, 50001, 0), (64, 32003, 1), (100, 20000, 3),
+                                        (2, 8192, 0)])
+def test_argmax_in_chunks(rows, V, pad):
+    """Large vocabularies: a row is cut over several blocks.  Equal maxima on both sides of every
+    chunk border, rows that do not start on 16 bytes (pad), a width that is no multiple of 4."""
+    kk = k()
+    chunks = kk.argmax_chunks(rows, V)
+    assert chunks > 1
+    chunk = ((V + chunks - 1) // chunks + 3) // 4 * 4
+    buf = rnd(rows, V + pad, seed=11)
+    logits = buf[:, :V]
+    for r in range(rows):
+        border = chunk * (1 + r % (chunks - 1))
+        if r % 3 == 0 and border < V:
+            logits[r, border - 1] = logits[r, border] = 70.0          # a tie across a border
+        elif r % 3 == 1:
+            logits[r, V - 1] = 70.0                                   # the ragged end
+        else:
+            logits[r, min(V - 1, border + 1)] = 70.0
+    dev = buf.to(DEV)[:, :V]
+    for _ in range(3):                                                # the tickets come back to zero
+        got = kk.argmax(dev).cpu()
+        assert got.tolist() == plain_ops.argmax(logits).tolist()
+    assert int(kk.argmax_workspace(dev.device)[1].abs().sum()) == 0
+
+
 @pytest.mark.parametrize("V", [131, 320, 5000, 128256])
 def test_temperature_sampling_matches_inverse_cdf(V):
     rows = 24
