@@ -377,8 +377,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // crosses a thread.  While one group works on its scores the tensor core computes the other
 // tile's, and K and V are read from shared memory once for 256 rows.
 // Keys come in tiles of 128 at head size 64 and of 64 at head size 128, so that both fit:
-//   tensor memory: S_A, S_B (one column per key), then O_A, O_B (one per head dimension): 384 columns.
-//   shared memory: Q_A, Q_B, three K/V stages (32 KB each), P_A, P_B: 192 KB.
+//   tensor memory: S_A, S_B (one column per key), O_A, O_B (one per head dimension), P_A, P_B (the
+//     probabilities in bfloat16, two keys per column): 512 columns at head size 64, 448 at 128.
+//   shared memory: Q_A, Q_B, three K/V stages (32 KB each): 128 KB.
+// The P V product reads P from tensor memory (A operand) and only V from shared memory: with P in
+// shared memory, the tensor core's operand reads and the softmax threads' stores together asked
+// more of shared memory's 128 bytes a clock than the exponentials ask of their unit.
 // The outputs stay in tensor memory: every P V product accumulates onto them, and a row's
 // output is rescaled there only when its running maximum has grown by more than 2^8 since the
 // scale in use was fixed (probabilities then stay below 2^8, far inside bfloat16 and 32-bit
@@ -389,12 +393,11 @@ namespace two {
 constexpr int BN2 = HD == 64 ? 128 : 64;        // keys per tile
 constexpr int KV_ST = 3;
 constexpr int K2_BYTES = KB * BN2 * 128, V2_BYTES = K2_BYTES;      // KB blocks of [BN2 keys][64 dims]
-constexpr int PB = BN2 / 64;                    // 64-key blocks of a probability tile
-constexpr int P2_BYTES = PB * TILE_BYTES;       // PB blocks of [128 rows][64 keys]
 constexpr int THREADS2 = 320;                   // producer, MMA issuer, 4 + 4 softmax warps
 constexpr int GROUP_THREADS = 128;
-constexpr size_t SMEM2 = 2 * (size_t)Q_BYTES + (size_t)KV_ST * (K2_BYTES + V2_BYTES) + 2 * (size_t)P2_BYTES + 1024 + 512;
-constexpr int S2_COL = 0, O2_COL = 2 * BN2;
+constexpr size_t SMEM2 = 2 * (size_t)Q_BYTES + (size_t)KV_ST * (K2_BYTES + V2_BYTES) + 1024 + 512;
+constexpr int S2_COL = 0, O2_COL = 2 * BN2, P2_COL = O2_COL + 2 * HD;   // P: two keys per column, BN2 / 2 columns a tile
+static_assert(P2_COL + BN2 <= TMEM_COLS, "scores, outputs and probabilities must fit tensor memory");
 
 struct Bars2 {
   uint64_t q_full;
@@ -414,8 +417,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sq = smem;                                             // [2] query tiles
   unsigned char* skv = sq + 2 * Q_BYTES;                                // [stage][K | V]
-  unsigned char* sp = skv + (size_t)KV_ST * (K2_BYTES + V2_BYTES);        // [2] probabilities
-  Bars2* bars = reinterpret_cast<Bars2*>(sp + 2 * (size_t)P2_BYTES);
+  Bars2* bars = reinterpret_cast<Bars2*>(skv + (size_t)KV_ST * (K2_BYTES + V2_BYTES));
 
   // the pairs that see the most keys start first, for every head and row (see the one-tile kernel)
   const int r = blockIdx.y, g = blockIdx.x, pair = gridDim.z - 1 - blockIdx.z;
@@ -524,25 +526,24 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // probabilities), so one tile's softmax never waits for the other's.
     auto issue_qk = [&](int x, int j) {
       const int st = j % KV_ST;
-      const uint32_t qa = smem_u32(sq + x * Q_BYTES), ka = smem_u32(skv + (size_t)st * (K2_BYTES + V2_BYTES));
+      const uint32_t q_lo = desc_lo_k128(smem_u32(sq + x * Q_BYTES));
+      const uint32_t k_lo = desc_lo_k128(smem_u32(skv + (size_t)st * (K2_BYTES + V2_BYTES)));
 #pragma unroll
       for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4)
-          umma_f16(tmem + S2_COL + x * BN2, make_desc_k128(qa + kb * TILE_BYTES) + 2 * k4,
-                   make_desc_k128(ka + kb * BN2 * 128) + 2 * k4, idesc_qk, (kb | k4) ? 1u : 0u);
+          umma_f16(tmem + S2_COL + x * BN2, desc_sw128(q_lo + (kb * TILE_BYTES >> 4) + 2 * k4),
+                   desc_sw128(k_lo + (kb * BN2 * 128 >> 4) + 2 * k4), idesc_qk, (kb | k4) ? 1u : 0u);
       umma_commit(smem_u32(&bars->s_full[x]));
     };
     auto issue_pv = [&](int x, int j) {
       const int st = j % KV_ST;
-      const uint32_t pa = smem_u32(sp + (size_t)x * P2_BYTES);
-      const uint32_t va = smem_u32(skv + (size_t)st * (K2_BYTES + V2_BYTES) + K2_BYTES);
+      const uint32_t pa = tmem + P2_COL + x * (BN2 / 2);
+      const uint32_t v_lo = desc_lo_mn128(smem_u32(skv + (size_t)st * (K2_BYTES + V2_BYTES) + K2_BYTES), BN2 * 128);
 #pragma unroll
-      for (int kb = 0; kb < PB; ++kb)         // 64 keys each
-#pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)        // 16 keys each; the first tile's first MMA starts the sum
-          umma_f16(tmem + O2_COL + x * HD, make_desc_k128(pa + kb * TILE_BYTES) + 2 * k4,
-                   make_desc_mn128(va + (kb * 64 + k4 * 16) * 128, BN2 * 128), idesc_pv, (j > 0 || (kb | k4)) ? 1u : 0u);
+      for (int k = 0; k < BN2 / 16; ++k)      // 16 keys each; the first tile's first MMA starts the sum
+        umma_f16_ts(tmem + O2_COL + x * HD, pa + 8 * k, desc_sw128(v_lo + (k * 16 * 128 >> 4)), idesc_pv,
+                    (j > 0 || k) ? 1u : 0u);
       umma_commit(smem_u32(&bars->o_full[x]));
       umma_commit(smem_u32(&bars->p_empty[x]));
     };
@@ -591,6 +592,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_addr = lane_addr + S2_COL + x * BN2;
     const uint32_t o_addr = lane_addr + O2_COL + x * HD;
+    const uint32_t p_addr = lane_addr + P2_COL + x * (BN2 / 2);
     // m: the scale in use (log2 domain), fixed until the running maximum outgrows it by 2^8
     float m = -INFINITY, l = 0.f;
     bool ok = true;
@@ -648,8 +650,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       const float m_use = m == -INFINITY ? 0.f : m;
       if (!mbar_wait(smem_u32(&bars->p_empty[x]), (uint32_t)((j & 1) ^ 1))) { ok = false; break; }
-      // second pass: probabilities to shared memory (K-major, 128-byte rows, swizzled by row);
-      // 64 columns are one 128-byte row of one k block
+      // second pass: probabilities to tensor memory, two keys per column: the P V product reads
+      // them from there, and shared memory carries K, V and Q only
       float sum = 0.f;
       auto second_pass = [&](auto masked) {
         constexpr bool MASKED = decltype(masked)::value;
@@ -658,26 +660,20 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           uint32_t v[64];
           tmem_ld64(s_addr + c, v);
           tmem_ld_wait();
-          unsigned char* prow = sp + (size_t)x * P2_BYTES + (c >> 6) * TILE_BYTES + row * 128;
+          uint32_t w[32];
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            float pr[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int col = c + 8 * ch + i;
-              float sc = fmaf(__uint_as_float(v[8 * ch + i]), sl2, -m_use);
-              if (MASKED && key0 + col > lim) sc = -INFINITY;
-              pr[i] = fast_exp2(sc);
-              sum += pr[i];
-            }
-            uint4 w;
-            w.x = pack2(pr[0], pr[1]);
-            w.y = pack2(pr[2], pr[3]);
-            w.z = pack2(pr[4], pr[5]);
-            w.w = pack2(pr[6], pr[7]);
-            *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = w;
+          for (int i = 0; i < 64; i += 2) {
+            float sc0 = fmaf(__uint_as_float(v[i]), sl2, -m_use), sc1 = fmaf(__uint_as_float(v[i + 1]), sl2, -m_use);
+            if (MASKED && key0 + c + i > lim) sc0 = -INFINITY;
+            if (MASKED && key0 + c + i + 1 > lim) sc1 = -INFINITY;
+            const float p0 = fast_exp2(sc0), p1 = fast_exp2(sc1);
+            sum += p0;
+            sum += p1;
+            w[i >> 1] = pack2(p0, p1);
           }
+          tmem_st32(p_addr + (c >> 1), w);
         }
+        tmem_st_wait();
       };
       if (need_mask) second_pass(std::true_type{});
       else second_pass(std::false_type{});

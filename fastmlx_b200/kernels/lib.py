@@ -40,6 +40,7 @@ _SIGNATURES = {
     "tc": {
         "fmx_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
         "fmx_gemm_stream": [_P, _L, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P, _L, _P, _P],
+        "fmx_mma_rate": [_I, _I, _I, _I, _I, _P, _P],
     },
     "attn": {
         "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],

@@ -4,6 +4,7 @@ launches), for tuning and for profiler captures on a small case.
     python -m fastmlx_b200.kernels.microbench --kernel attn_decode --batch 8 --ctx 8192
     python -m fastmlx_b200.kernels.microbench --kernel attn_prefill --batch 1 --qlen 2048
     python -m fastmlx_b200.kernels.microbench --kernel skinny_gemm --M 8 --N 2048 --K 8192
+    python -m fastmlx_b200.kernels.microbench --kernel mma_rate
 """
 from __future__ import annotations
 
@@ -56,7 +57,7 @@ def _attention_inputs(a, qlen):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "skinny_gemm", "gemm"])
+    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "skinny_gemm", "gemm", "mma_rate"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192, help="tokens already in the cache")
     ap.add_argument("--qlen", type=int, default=2048, help="tokens per row (attn_prefill)")
@@ -76,6 +77,22 @@ def main(argv=None) -> int:
     ap.add_argument("--launches", type=int, default=10, help="kernel launches per graph")
     ap.add_argument("--replays", type=int, default=5)
     a = ap.parse_args(argv)
+    if a.kernel == "mma_rate":
+        # clocks per tcgen05.mma of 128 x N x 16 issued back to back by one thread
+        from .lib import call
+        out = torch.zeros(3, dtype=torch.int64, device="cuda")
+        iters = 2000
+        for n, tm, mn in [(64, 0, 0), (128, 0, 0), (256, 0, 0), (64, 0, 1), (128, 0, 1), (64, 1, 1), (128, 1, 1), (128, 1, 0),
+                          (256, 1, 0)]:
+            per = []
+            for fixed in (1, 0):
+                for _ in range(2):
+                    call("tc", "fmx_mma_rate", n, tm, mn, fixed, iters, out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+                issued, done, expired = out.cpu().tolist()
+                per.append(f"{done / (4 * iters):.1f}" + (" (the wait ran out)" if expired else ""))
+            print(f"mma_rate N={n} A in {'tensor' if tm else 'shared'} memory, B {'MN' if mn else 'K'}-major: "
+                  f"{per[0]} clocks per product back to back, {per[1]} with descriptor arithmetic in between")
+        return 0
     if a.kernel == "attn_decode":
         qkv, kv, ctx, grp = _attention_inputs(a, 1)
         splits = a.splits or k.decode_splits(a.batch, a.nkv, a.ctx + 1, a.hd)
