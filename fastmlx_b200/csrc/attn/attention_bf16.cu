@@ -381,6 +381,19 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
       fetched = s + 1;
     }
   }
+  // The last stage of the ring is free until the first pass of the loop below: with rotation in
+  // this kernel it holds the rotated queries and the row's sines and cosines meanwhile.  Those
+  // depend on the position alone, so they too are ready before the kernel ahead has finished.
+  bf16* q_rot = stage_k(DECODE_STAGES - 1);            // [16][HD]
+  float* rope_sin = reinterpret_cast<float*>(q_rot + 16 * HD);
+  float* rope_cos = rope_sin + HD / 2;
+  static_assert(16 * HD * 2 + HD * 4 <= TILE * 2, "the rotated queries must fit one K tile");
+  const int half = rot / 2;
+  if (rope_mode > 0) {
+    const float fpos = (float)pos;
+    for (int j = threadIdx.x; j < half; j += THREADS) sincosf(fpos * inv_freq[j], &rope_sin[j], &rope_cos[j]);
+    __syncthreads();
+  }
   pdl_wait();
 
   const bf16* qbase = q + (long long)t * q_stride + (long long)g * rep * HD;
@@ -388,16 +401,7 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   if (rope_mode > 0) {
     // q, k and v arrive as the projection left them: rotate the queries into shared memory, and
     // let the block whose keys include the row's new one rotate that key and store it and
-    // its value in the cache, as the separate kernel would have.  The last stage of the ring
-    // is free until the first pass of the loop below: it holds the rotated queries meanwhile.
-    bf16* q_rot = stage_k(DECODE_STAGES - 1);          // [16][HD]
-    float* rope_sin = reinterpret_cast<float*>(q_rot + 16 * HD);
-    float* rope_cos = rope_sin + HD / 2;
-    static_assert(16 * HD * 2 + HD * 4 <= TILE * 2, "the rotated queries must fit one K tile");
-    const int half = rot / 2;
-    const float fpos = (float)pos;
-    for (int j = threadIdx.x; j < half; j += THREADS) sincosf(fpos * inv_freq[j], &rope_sin[j], &rope_cos[j]);
-    __syncthreads();
+    // its value in the cache, as the separate kernel would have.
     const bf16* row = q + (long long)t * q_stride;
     for (int it = threadIdx.x; it < rep * (HD / 2); it += THREADS) {
       const int h = it / (HD / 2), j = it - h * (HD / 2);
@@ -555,12 +559,14 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   // The block that draws the last ticket of this (row, kv head) combines the splits, in split
   // order.  Nobody waits: the others are done once their partial is written.
   __shared__ int drew_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) drew_last = atomicAdd(&tickets[r * nkv + g], 1) == splits - 1;
+  __syncthreads();                                   // the block's partial is written ...
+  if (threadIdx.x == 0) {
+    __threadfence();                                 // ... and, through the barrier, ordered before the ticket
+    drew_last = atomicAdd(&tickets[r * nkv + g], 1) == splits - 1;
+    if (drew_last) __threadfence();                  // the others' partials, before this block's loads
+  }
   __syncthreads();
   if (!drew_last) return;
-  __threadfence();
   // Three rounds of loads instead of a chain: the splits' (max, sum) pairs go to shared memory
   // in one coalesced sweep, each row's weights 2^(m_split - M) are worked out there, and the
   // partial outputs are then read with independent loads.  The sums run in split order.
