@@ -376,28 +376,39 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // softmax group of four warps with one thread per query row, so no row statistic ever
 // crosses a thread.  While one group works on its scores the tensor core computes the other
 // tile's, and K and V are read from shared memory once for 256 rows.
-// Keys come in tiles of 128 at head size 64 and of 64 at head size 128, so that both fit:
-//   tensor memory: S_A, S_B (one column per key), O_A, O_B (one per head dimension), P_A, P_B (the
-//     probabilities in bfloat16, two keys per column): 512 columns at head size 64, 448 at 128.
-//   shared memory: Q_A, Q_B, three K/V stages (32 KB each): 128 KB.
-// The P V product reads P from tensor memory (A operand) and only V from shared memory: with P in
-// shared memory, the tensor core's operand reads and the softmax threads' stores together asked
-// more of shared memory's 128 bytes a clock than the exponentials ask of their unit.
-// The outputs stay in tensor memory: every P V product accumulates onto them, and a row's
+// Head size 64: keys in tiles of 128; tensor memory holds S_A, S_B (one column per key), O_A, O_B
+// (one per head dimension) and P_A, P_B (the probabilities in bfloat16, two keys per column), 512
+// columns; shared memory Q_A, Q_B and three K/V stages of 32 KB.  A softmax thread reads its row
+// of scores twice, 64 columns at a time (once for the maximum, once for the exponentials); the
+// next Q K^T of its query tile starts when it has.
+// Head size 128: scores and outputs alone would fill tensor memory at 128 keys a tile, so keys come
+// in tiles of 64 and every query tile has two score buffers: the Q K^T of tile j + 1 runs while
+// the softmax works on tile j.  A row of 64 scores is taken into registers at once; the
+// probabilities are written over the first half of the tile's own scores, which stay held until
+// the P V product has read them.  Two threads issue the products there, one the scores and one
+// P V: with one, a product whose inputs were ready waited behind the other three kinds, since an
+// issue call lasts as long as the tensor pipe is busy (8 x 256 tokens over 4,096 cached: 228 us
+// with one score buffer, 214 with two, 179 with two issuers as well; the same two changes at head
+// size 64 lose to its 128-key tiles, 144 against 134 us).
+// In both, the P V product reads P from tensor memory (A operand) and V from shared memory, and the
+// outputs stay in tensor memory: every P V product accumulates onto them, and a row's
 // output is rescaled there only when its running maximum has grown by more than 2^8 since the
 // scale in use was fixed (probabilities then stay below 2^8, far inside bfloat16 and 32-bit
-// range; the final division by the row sum, kept at the same scale, undoes it exactly).  A
-// softmax thread reads its row of scores twice from tensor memory, 64 columns at a time (once
-// for the maximum, once for the exponentials), and holds no output in registers.
+// range; the final division by the row sum, kept at the same scale, undoes it exactly).
 namespace two {
-constexpr int BN2 = HD == 64 ? 128 : 64;        // keys per tile
-constexpr int KV_ST = 3;
+// DB: two score buffers per query tile and two issuing threads (head size 128, see above).
+#ifndef FMX_ATTN_DB
+#define FMX_ATTN_DB (FMX_HD == 128)
+#endif
+constexpr bool DB = FMX_ATTN_DB;
+constexpr int BN2 = DB ? 64 : (HD == 64 ? 128 : 64);   // keys per tile
+constexpr int KV_ST = DB ? 4 : 3;
 constexpr int K2_BYTES = KB * BN2 * 128, V2_BYTES = K2_BYTES;      // KB blocks of [BN2 keys][64 dims]
-constexpr int THREADS2 = 320;                   // producer, MMA issuer, 4 + 4 softmax warps
+constexpr int THREADS2 = DB ? 352 : 320;        // producer, MMA issuer, 4 + 4 softmax warps; DB: a second issuer
 constexpr int GROUP_THREADS = 128;
 constexpr size_t SMEM2 = 2 * (size_t)Q_BYTES + (size_t)KV_ST * (K2_BYTES + V2_BYTES) + 1024 + 512;
-constexpr int S2_COL = 0, O2_COL = 2 * BN2, P2_COL = O2_COL + 2 * HD;   // P: two keys per column, BN2 / 2 columns a tile
-static_assert(P2_COL + BN2 <= TMEM_COLS, "scores, outputs and probabilities must fit tensor memory");
+constexpr int S2_COL = 0, O2_COL = DB ? 4 * BN2 : 2 * BN2, P2_COL = O2_COL + 2 * HD;   // P: two keys per column
+static_assert((DB ? O2_COL + 2 * HD : P2_COL + BN2) <= TMEM_COLS, "scores, outputs and probabilities must fit tensor memory");
 
 struct Bars2 {
   uint64_t q_full;
@@ -405,6 +416,7 @@ struct Bars2 {
   uint64_t s_full[2], s_empty[2];               // per query tile
   uint64_t p_full[2], p_empty[2];
   uint64_t o_full[2];                           // per query tile: a P V product has landed
+  uint64_t sd_full[2][2], pd_full[2][2], pv_done[2][2];   // DB: per query tile and score buffer
   uint32_t tmem_slot;
 };
 
@@ -437,6 +449,11 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(smem_u32(&bars->p_full[x]), GROUP_THREADS);
       mbar_init(smem_u32(&bars->p_empty[x]), 1);
       mbar_init(smem_u32(&bars->o_full[x]), 1);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(smem_u32(&bars->sd_full[x][b]), 1);
+        mbar_init(smem_u32(&bars->pd_full[x][b]), GROUP_THREADS);
+        mbar_init(smem_u32(&bars->pv_done[x][b]), 1);
+      }
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -516,8 +533,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (++stage == KV_ST) { stage = 0; phase ^= 1; }
     }
     if (!ok && lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 21, blockIdx.x);
-  } else if (warp == 1 && lane == 0 && n_all > 0) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if ((warp == 1 || (DB && warp == 10)) && lane == 0 && n_all > 0) {
+    // ------------------------------------------------------------------ MMA issuer(s)
     const uint32_t idesc_qk = make_idesc(BM, BN2, 0), idesc_pv = make_idesc(BM, HD, 1);
     bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
     tc_fence_after();
@@ -547,15 +564,58 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       umma_commit(smem_u32(&bars->o_full[x]));
       umma_commit(smem_u32(&bars->p_empty[x]));
     };
+    // DB: tile j of query tile x uses score buffer j & 1 for the (j >> 1)-th time; the buffer is
+    // free again when the P V product of tile j - 2 has read its probabilities out of it.
+    auto issue_qk_db = [&](int x, int j) {
+      const int st = j % KV_ST;
+      const uint32_t q_lo = desc_lo_k128(smem_u32(sq + x * Q_BYTES));
+      const uint32_t k_lo = desc_lo_k128(smem_u32(skv + (size_t)st * (K2_BYTES + V2_BYTES)));
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+          umma_f16(tmem + S2_COL + (2 * x + (j & 1)) * BN2, desc_sw128(q_lo + (kb * TILE_BYTES >> 4) + 2 * k4),
+                   desc_sw128(k_lo + (kb * BN2 * 128 >> 4) + 2 * k4), idesc_qk, (kb | k4) ? 1u : 0u);
+      umma_commit(smem_u32(&bars->sd_full[x][j & 1]));
+    };
+    auto issue_pv_db = [&](int x, int j) {
+      const int st = j % KV_ST;
+      const uint32_t pa = tmem + S2_COL + (2 * x + (j & 1)) * BN2;
+      const uint32_t v_lo = desc_lo_mn128(smem_u32(skv + (size_t)st * (K2_BYTES + V2_BYTES) + K2_BYTES), BN2 * 128);
+#pragma unroll
+      for (int k = 0; k < BN2 / 16; ++k)
+        umma_f16_ts(tmem + O2_COL + x * HD, pa + 8 * k, desc_sw128(v_lo + (k * 16 * 128 >> 4)), idesc_pv,
+                    (j > 0 || k) ? 1u : 0u);
+      umma_commit(smem_u32(&bars->pv_done[x][j & 1]));
+    };
     int qk_a = 0, qk_b = 0, pv_a = 0, pv_b = 0, released = 0;
     long long t_last = clock64();
-    while (ok && (pv_a < n_tiles_a || pv_b < n_tiles_b)) {
+    while (ok && (DB && warp == 1 ? (qk_a < n_tiles_a || qk_b < n_tiles_b) : (pv_a < n_tiles_a || pv_b < n_tiles_b))) {
       bool progress = false;
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
         int& qk = x ? qk_b : qk_a;
         int& pv = x ? pv_b : pv_a;
         const int n = x ? n_tiles_b : n_tiles_a;
+        if constexpr (DB) {
+          // Two issuers, warp 1 for the scores and warp 10 for the P V products, each counting only
+          // its own: with one, a product that was ready waited behind the three other kinds (every
+          // issue call lasts as long as the tensor pipe is busy), and the softmax for its scores.
+          if (warp == 1 && qk < n && mbar_test(smem_u32(&bars->kv_full[qk % KV_ST]), (uint32_t)((qk / KV_ST) & 1)) &&
+              mbar_test(smem_u32(&bars->pv_done[x][qk & 1]), (uint32_t)(((qk >> 1) & 1) ^ 1))) {
+            tc_fence_after();
+            issue_qk_db(x, qk);
+            ++qk;
+            progress = true;
+          }
+          if (warp != 1 && pv < n && mbar_test(smem_u32(&bars->pd_full[x][pv & 1]), (uint32_t)((pv >> 1) & 1))) {
+            tc_fence_after();
+            issue_pv_db(x, pv);
+            ++pv;
+            progress = true;
+          }
+          continue;
+        }
         if (qk < n && mbar_test(smem_u32(&bars->kv_full[qk % KV_ST]), (uint32_t)((qk / KV_ST) & 1)) &&
             mbar_test(smem_u32(&bars->s_empty[x]), (uint32_t)((qk & 1) ^ 1))) {
           tc_fence_after();
@@ -571,15 +631,16 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
       }
       // a K/V stage goes back once both tiles' products over it have been issued
-      while (released < n_all && (released >= n_tiles_a || pv_a > released) && (released >= n_tiles_b || pv_b > released)) {
+      while (!(DB && warp == 1) && released < n_all && (released >= n_tiles_a || pv_a > released) &&
+             (released >= n_tiles_b || pv_b > released)) {
         umma_commit(smem_u32(&bars->kv_empty[released % KV_ST]));
         ++released;
       }
       if (progress) t_last = clock64();
       else if (clock64() - t_last > WAIT_CYCLES) ok = false;
     }
-    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 22, blockIdx.x);
-  } else if (warp >= 2) {
+    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, warp == 1 ? 22 : 24, blockIdx.x);
+  } else if (warp >= 2 && warp < 10) {
     // ------------------------------------------------------------------ softmax and epilogue
     const int x = (warp - 2) >> 2;                       // query tile of this group
     const int quarter = warp & 3;
@@ -598,8 +659,93 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     bool ok = true;
     const int nt = x ? n_tiles_b : n_tiles_a;
 
-    for (int j = 0; j < nt && ok; ++j) {
+    // the output so far is at the old scale: bring this warp's rows to the new one
+    auto rescale_output = [&](float alpha) {
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(o_addr + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+        tmem_st32(o_addr + c, v);
+      }
+      tmem_st_wait();
+    };
+    // keys past the last visible one share pages with stale rows: their values must be
+    // zeros, since 0 * NaN would poison the product (both groups write the same zeros)
+    auto zero_stale_values = [&](int j, int key0) -> bool {
       const int st = j % KV_ST;
+      if (!mbar_wait(smem_u32(&bars->kv_full[st]), (uint32_t)((j / KV_ST) & 1))) return false;
+      unsigned char* sv = skv + (size_t)st * (K2_BYTES + V2_BYTES) + K2_BYTES;
+      if (row < BN2 && key0 + row >= kend_all) {
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(sv + kb * BN2 * 128 + row * 128 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      return true;
+    };
+
+    if constexpr (DB) {
+      static_assert(!DB || BN2 == 64, "a row of scores is taken into 64 registers");
+      for (int j = 0; j < nt && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t sb_addr = lane_addr + S2_COL + (2 * x + b) * BN2;     // scores, then probabilities
+        if (!mbar_wait(smem_u32(&bars->sd_full[x][b]), (uint32_t)((j >> 1) & 1))) { ok = false; break; }
+        tc_fence_after();
+        const int key0 = j * BN2;
+        const bool need_mask = key0 + BN2 - 1 > ctx + tok0;
+        uint32_t v[64];
+        tmem_ld64(sb_addr, v);
+        tmem_ld_wait();
+        float mx = -INFINITY;
+        if (!need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            if (key0 + i > lim) v[i] = 0xff800000u;      // -inf: its probability is 0
+            mx = fmaxf(mx, __uint_as_float(v[i]));
+          }
+        }
+        mx *= sl2;
+        const bool grow = mx > m + 8.0f || (m == -INFINITY && mx > -INFINITY);
+        float alpha = 1.0f;
+        if (grow) {
+          alpha = fast_exp2(m - mx);
+          m = mx;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          if (!mbar_wait(smem_u32(&bars->pv_done[x][(j - 1) & 1]), (uint32_t)(((j - 1) >> 1) & 1))) { ok = false; break; }
+          tc_fence_after();
+          rescale_output(alpha);
+          l *= alpha;
+        }
+        const float m_use = m == -INFINITY ? 0.f : m;
+        float sum = 0.f;
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -m_use));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), sl2, -m_use));
+          sum += p0;
+          sum += p1;
+          w[i >> 1] = pack2(p0, p1);
+        }
+        tmem_st32(sb_addr, w);                           // over the first half of the tile's own scores
+        tmem_st_wait();
+        l += sum;
+        if (key0 + BN2 > kend_all && !zero_stale_values(j, key0)) { ok = false; break; }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bars->pd_full[x][b]));
+      }
+      if (ok && nt > 0) ok = mbar_wait(smem_u32(&bars->pv_done[x][(nt - 1) & 1]), (uint32_t)(((nt - 1) >> 1) & 1));
+    } else {
+    for (int j = 0; j < nt && ok; ++j) {
       if (!mbar_wait(smem_u32(&bars->s_full[x]), (uint32_t)(j & 1))) { ok = false; break; }
       tc_fence_after();
       const int key0 = j * BN2;
@@ -633,19 +779,9 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         m = mx;
       }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // the output so far is at the old scale: bring this warp's rows to the new one
         if (!mbar_wait(smem_u32(&bars->o_full[x]), (uint32_t)((j - 1) & 1))) { ok = false; break; }
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < HD; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(o_addr + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st32(o_addr + c, v);
-        }
-        tmem_st_wait();
+        rescale_output(alpha);
         l *= alpha;
       }
       const float m_use = m == -INFINITY ? 0.f : m;
@@ -680,24 +816,12 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tc_fence_before();
       mbar_arrive(smem_u32(&bars->s_empty[x]));          // the scores have been read twice: free for tile j + 1
       l += sum;
-      if (key0 + BN2 > kend_all) {
-        // keys past the last visible one share pages with stale rows: their values must be
-        // zeros, since 0 * NaN would poison the product (both groups write the same zeros)
-        if (!mbar_wait(smem_u32(&bars->kv_full[st]), (uint32_t)((j / KV_ST) & 1))) { ok = false; break; }
-        unsigned char* sv = skv + (size_t)st * (K2_BYTES + V2_BYTES) + K2_BYTES;
-        if (row < BN2 && key0 + row >= kend_all) {
-#pragma unroll
-          for (int kb = 0; kb < KB; ++kb)
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-              *reinterpret_cast<uint4*>(sv + kb * BN2 * 128 + row * 128 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
-        }
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (key0 + BN2 > kend_all && !zero_stale_values(j, key0)) { ok = false; break; }
       tc_fence_before();
       mbar_arrive(smem_u32(&bars->p_full[x]));
     }
     if (ok && nt > 0) ok = mbar_wait(smem_u32(&bars->o_full[x]), (uint32_t)((nt - 1) & 1));
+    }
     if (!ok) {
       if (lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 23, blockIdx.x);
     } else if (nt > 0) {
