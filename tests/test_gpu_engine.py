@@ -238,3 +238,59 @@ def test_running_one_step_ahead_changes_no_token(dirs):
     assert want[1][1] == "stop" and want[0][1] == "length" and want[2][1] == "length"
     assert st1["graph_replays"] > 0
     assert run(True)[0] == base
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_arrivals_aborts_and_a_tight_pool(dirs, seed):
+    """Requests of random lengths arrive while others decode, some are aborted midway, the pool is
+    too small for all of them (so some are preempted and recomputed) and prompts are cut into
+    portions: every request that finishes produces what it produces alone, greedy or sampled
+    from its own seed, and at the end no page is held."""
+    import random
+    from fastmlx_b200 import Engine, SamplingParams
+    rng = random.Random(seed)
+    cfg = tiny.TINY_B
+    n_req = 10
+    prompts = [tiny.rand_tokens(rng.randint(1, 90), cfg["vocab_size"], 500 + 17 * seed + i) for i in range(n_req)]
+    sps = [SamplingParams(max_tokens=rng.randint(3, 30), temperature=0.0 if i % 3 else 0.8, seed=77 + i)
+           for i in range(n_req)]
+    alone = Engine(dirs["B"], dtype="float32", block_size=16, max_cache_tokens=1024)
+    want = [alone.generate([p], sp)[0].output_token_ids for p, sp in zip(prompts, sps)]
+
+    eng = Engine(dirs["B"], dtype="float32", block_size=8, initial_cache_blocks=40, max_concurrent_requests=4,
+                 max_num_batched_tokens=48, prefill_chunk=rng.choice([5, 16, 32]))
+    arrive = sorted(rng.randint(0, 40) for _ in range(n_req))
+    abort_at = {i: arrive[i] + rng.randint(1, 12) for i in rng.sample(range(n_req), 3)}
+    ids, final, got = {}, {}, {}
+    step = 0
+    while step < 2000 and (len(ids) < n_req or eng.has_unfinished()):
+        for i in range(n_req):
+            if i not in ids and arrive[i] <= step:
+                ids[i] = eng.submit(prompts[i], sps[i])
+        for i, at in abort_at.items():
+            if at == step and i in ids and ids[i] not in final:
+                eng.abort(ids[i])
+        for out in eng.step():
+            got.setdefault(out.request_id, []).extend(out.new_token_ids)
+            if out.finished:
+                final[out.request_id] = out
+        step += 1
+    for out in eng.flush():
+        got.setdefault(out.request_id, []).extend(out.new_token_ids)
+        if out.finished:
+            final[out.request_id] = out
+    assert len(final) == n_req
+    finished_normally = 0
+    for i in range(n_req):
+        out = final[ids[i]]
+        assert out.err == ""
+        if out.finish_reason == "abort":
+            assert i in abort_at
+            assert out.output_token_ids == want[i][:len(out.output_token_ids)]
+        else:
+            finished_normally += 1
+            assert out.finish_reason == "length" and out.output_token_ids == want[i]
+            assert got[ids[i]] == want[i]                 # the increments add up to the whole
+    assert finished_normally >= n_req - 3
+    assert eng.stats()["pages_used"] == 0
+    eng.manager.check()
