@@ -88,6 +88,8 @@ class Engine:
         self._host_out = None
         self._side = None
         self._ahead = None                      # a step launched whose ids have not been read yet
+        self.defer_status_check = True          # see _finish
+        self._status_unchecked = False
         self.lookahead = bool(ec.lookahead) and self.rt.device.type == "cuda"
         self._requests: dict[str, Request] = {}
         self.counters = {"steps": 0, "prompt_tokens": 0, "generated_tokens": 0, "preemptions": 0, "h2d_bytes": 0,
@@ -128,6 +130,7 @@ class Engine:
             outs.extend(self._finish(prev))
             return outs
         if not self.scheduler.has_unfinished():
+            self._settle_status()
             return outs
         plan = self.scheduler.schedule()
         for req in plan.finished:
@@ -151,7 +154,19 @@ class Engine:
         if self._ahead is not None:
             prev, self._ahead = self._ahead, None
             outs.extend(self._finish(prev))
+        if not self.scheduler.has_unfinished():
+            self._settle_status()
         return outs
+
+    def _settle_status(self) -> None:
+        """Nothing is running any more: a status left by a portion whose request was aborted
+        before any of its tokens was read must not fall on the next request."""
+        if self._status_unchecked:
+            self._status_unchecked = False
+            try:
+                self.step_fn.check_status()
+            except StepError:
+                pass                                 # the request it belonged to is gone
 
     def _launch(self, plan, tokens_from, outs):
         """Put a planned step on the device.  -> (plan, sampled ids on the device, readiness
@@ -197,7 +212,14 @@ class Engine:
         try:
             tokens = self._read_back(sampled, ready) if sampled is not None else []
             if sampled is None:
-                self.step_fn.check_status()
+                # A portion of a prompt that asks for no token: nothing to wait for.  The kernels'
+                # status word keeps what it was given, and the next step that reads ids back reads
+                # it too (the request is still running then); waiting here would leave the device
+                # idle for every portion's launches and the host idle for every portion's run.
+                if self.defer_status_check and self.rt.device.type == "cuda":
+                    self._status_unchecked = True
+                else:
+                    self.step_fn.check_status()
         except (StepError, RuntimeError) as e:
             outs.extend(self.scheduler.step_failed(plan, str(e)))
             for req in plan.requests:
@@ -233,6 +255,7 @@ class Engine:
             self._host_out[n:n + 4].copy_(self.step_fn.status, non_blocking=True)
         self._side.synchronize()
         vals = self._host_out[:n + 4].tolist()
+        self._status_unchecked = False
         if vals[n]:
             torch.cuda.current_stream().synchronize()
             self.step_fn.check_status()          # raises with the code's meaning and clears the word

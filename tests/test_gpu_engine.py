@@ -294,3 +294,30 @@ def test_random_arrivals_aborts_and_a_tight_pool(dirs, seed):
     assert finished_normally >= n_req - 3
     assert eng.stats()["pages_used"] == 0
     eng.manager.check()
+
+
+def test_bad_token_in_an_early_portion_is_reported(dirs):
+    """A portion of a prompt that asks for no token is not waited for; the status it leaves is
+    read with the next step's ids, while the request still runs.  An aborted request's status
+    falls on nobody."""
+    from fastmlx_b200 import Engine, SamplingParams
+    cfg = tiny.TINY_A
+    sp = SamplingParams(max_tokens=2, temperature=0.0)
+    eng = Engine(dirs["A"], dtype="float32", block_size=16, max_cache_tokens=256, prefill_chunk=8,
+                 max_num_batched_tokens=8)
+    bad = tiny.rand_tokens(30, cfg["vocab_size"], 3)
+    bad[2] = 999999
+    out = eng.generate([bad], sp)[0]
+    assert out.finish_reason == "error" and "vocabulary" in out.err
+    good = tiny.rand_tokens(30, cfg["vocab_size"], 4)
+    ok = eng.generate([good], sp)[0]
+    assert ok.finish_reason == "length" and ok.completion_tokens == 2
+    rid = eng.submit(bad, sp)
+    eng.step()                                           # the first portion, with the bad token
+    eng.abort(rid)
+    while eng.has_unfinished():
+        eng.step()
+    eng.step()
+    ok2 = eng.generate([good], sp)[0]
+    assert ok2.finish_reason == "length" and ok2.output_token_ids == ok.output_token_ids
+    assert eng.stats()["pages_used"] == 0
