@@ -29,7 +29,7 @@
 //                      32-bit, probabilities go to shared memory in bfloat16, the per-tile outputs
 //                      are rescaled and summed in registers.
 // Every barrier wait is bounded by time; a wait that runs out leaves FMX_WAIT_EXPIRED in the
-// status word and the CTA frees its tensor memory and returns.  No cluster, no multicast.
+// status word and the CTA frees its tensor memory and returns.  No cluster: every CTA loads its own tiles.
 #include <cuda.h>
 #include <math.h>
 #include <type_traits>

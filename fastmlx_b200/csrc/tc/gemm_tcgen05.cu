@@ -18,7 +18,7 @@
 //                      Variants: plain; SiLU(gate) * up for a weight whose rows come in blocks
 //                      of BN/2 gate rows followed by their BN/2 up rows; residual add.
 //
-// No cluster, no multicast.  Every wait on a barrier is bounded by time: after about a
+// No cluster: every CTA loads its own tiles.  Every wait on a barrier is bounded by time: after about a
 // second it gives up, leaves FMX_WAIT_EXPIRED in the status word, and the CTA drains what it
 // has in flight, frees its tensor memory and returns.
 #include <cuda.h>
