@@ -162,7 +162,9 @@ def main(argv=None) -> int:
             impls.append((f"stream ctas={ctas} stages={stages}",
                           lambda w: k.gemm_stream(x, w, ctas=a.ctas or None, ring_bytes=a.ring * 1024 or None)))
         if a.dual:                      # N rows of gate and up in blocks of 128, SiLU-mul in the epilogue
-            impls = [(f"gemv gate/up {wd} features", (lambda wd: lambda w: k.gemv(x, w, block=128, wide=wd))(wd)) for wd in (8, 16, 32)]
+            impls = [(f"gemv gate/up {wd} features", (lambda wd: lambda w: k.gemv(x, w, block=128, wide=wd))(wd))
+                     for wd in (8, 16, 32) if a.M <= 16]
+            impls.append(("library product, then SiLU-mul", lambda w: k.silu_mul(torch.mm(x, w.t()), 128)))
             if a.M <= 8:
                 impls.append(("skinny_fused gate/up", lambda w: k.skinny_fused(x, w, block=128)))
         for name, fn in impls:
