@@ -378,7 +378,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // tile's, and K and V are read from shared memory once for 256 rows.
 // Head size 64: keys in tiles of 128; tensor memory holds S_A, S_B (one column per key), O_A, O_B
 // (one per head dimension) and P_A, P_B (the probabilities in bfloat16, two keys per column), 512
-// columns; shared memory Q_A, Q_B and three K/V stages of 32 KB.  A softmax thread reads its row
+// columns; shared memory Q_A, Q_B and four K/V stages of 32 KB.  A softmax thread reads its row
 // of scores twice, 64 columns at a time (once for the maximum, once for the exponentials); the
 // next Q K^T of its query tile starts when it has.
 // Head size 128: scores and outputs alone would fill tensor memory at 128 keys a tile, so keys come
@@ -402,7 +402,7 @@ namespace two {
 #endif
 constexpr bool DB = FMX_ATTN_DB;
 constexpr int BN2 = DB ? 64 : (HD == 64 ? 128 : 64);   // keys per tile
-constexpr int KV_ST = DB ? 4 : 3;
+constexpr int KV_ST = 4;
 constexpr int K2_BYTES = KB * BN2 * 128, V2_BYTES = K2_BYTES;      // KB blocks of [BN2 keys][64 dims]
 constexpr int THREADS2 = DB ? 352 : 320;        // producer, MMA issuer, 4 + 4 softmax warps; DB: a second issuer
 constexpr int GROUP_THREADS = 128;
