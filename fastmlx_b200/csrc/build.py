@@ -88,7 +88,9 @@ def build_dir() -> str:
     d = os.environ.get("FASTMLX_BUILD_DIR") or os.path.join(HERE, "_build")
     try:
         os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
+        # one probe file per thread: groups are built side by side, and two threads that shared a
+        # name took each other's file away and mistook that for a read-only tree
+        probe = os.path.join(d, f".w{os.getpid()}_{threading.get_ident()}")
         with open(probe, "w"):
             pass
         os.remove(probe)
