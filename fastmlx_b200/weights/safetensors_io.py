@@ -133,7 +133,8 @@ def write_file(path: str, tensors: dict[str, torch.Tensor], metadata: dict | Non
         f.write(blob)
         for name in order:
             t = tensors[name].detach().contiguous().cpu()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            if t.numel():
+                f.write(memoryview(t.view(torch.uint8).reshape(-1).numpy()))       # no second copy of the bytes
     os.replace(tmp, path)
 
 

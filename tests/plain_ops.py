@@ -141,3 +141,31 @@ def sample(logits, temperature=None, uniform=None, keep=None):
 
 def argmax(logits):
     return sample(logits)
+
+
+def paged_attention_by_rows(q, kv, rows, block_tables, nh, nkv, hd, scale, window=0):
+    """The same statement as `paged_attention`, one request at a time instead of one token at a
+    time, for contexts of thousands of keys.  rows: (keys before this step, tokens of this
+    step) per request; q [T, nh*hd] holds the steps' tokens in row order.  float64 on the CPU."""
+    page_size = kv.shape[3]
+    out = torch.zeros(q.shape[0], nh * hd, dtype=F64)
+    rep = nh // nkv
+    at = 0
+    for r, (c, ql) in enumerate(rows):
+        n = c + ql
+        js = torch.arange(n)
+        pages = block_tables[r][(js // page_size).long()].long()
+        assert (pages >= 0).all()
+        K = kv[pages, 0, :, (js % page_size).long(), :].to(F64)       # [n, nkv, hd]
+        V = kv[pages, 1, :, (js % page_size).long(), :].to(F64)
+        qi = torch.arange(c, n)
+        visible = js[None, :] <= qi[:, None]
+        if window > 0:
+            visible &= js[None, :] > (qi[:, None] - window)
+        qr = q[at:at + ql].reshape(ql, nh, hd).to(F64)
+        for h in range(nh):
+            s = (qr[:, h, :] @ K[:, h // rep, :].t()) * scale
+            s = s.masked_fill(~visible, float("-inf"))
+            out[at:at + ql, h * hd:(h + 1) * hd] = torch.softmax(s, dim=-1) @ V[:, h // rep, :]
+        at += ql
+    return out.to(q.dtype)

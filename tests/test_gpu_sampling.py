@@ -1,5 +1,5 @@
-"""Sampling filters and logits processors on the GPU against the plain statements and,
-when that checkout is present, tamnd/fastmlx's own fixtures."""
+"""Sampling filters and logits processors on the GPU against the plain statements and
+against the cases of tamnd/fastmlx's own fixtures (kept as data in tests/data/sampling_cases.json)."""
 import json
 import os
 
@@ -12,8 +12,8 @@ import plain_sampling as ps
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-REF = tiny.reference_dir()
-HAVE_REF = os.path.isdir(os.path.join(REF, "compute", "testdata"))
+with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "sampling_cases.json")) as _f:
+    CASES = json.load(_f)
 
 
 def k():
@@ -28,11 +28,8 @@ def _mask(logits, top_p=0.0, min_p=0.0, top_k=0, min_keep=1):
     return k().filter_mask(logits.to(DEV), f(top_p), f(min_p), i(top_k), i(min_keep)).cpu()
 
 
-@pytest.mark.skipif(not HAVE_REF, reason="the reference checkout is not present")
 def test_filters_match_the_reference_fixture():
-    with open(os.path.join(REF, "compute", "testdata", "sampler_filters.json")) as f:
-        fx = json.load(f)
-    for case in fx["cases"]:
+    for case in CASES["filters"]:
         lp = torch.tensor([ps.log_softmax(case["logits"])], dtype=torch.float32)
         p = case["params"]
         if case["op"] == "apply_top_p":
@@ -43,7 +40,7 @@ def test_filters_match_the_reference_fixture():
             got = _mask(lp, top_k=p["top_k"])
         else:
             continue
-        assert got[0].bool().tolist() == case["kept"], case["label"]
+        assert got[0].tolist() == case["kept"], case["label"]
 
 
 @pytest.mark.parametrize("V", [12, 131, 1000, 5000])
@@ -88,10 +85,8 @@ def test_large_vocabulary_top_k_and_top_p():
         assert p[~got[r].bool()].max() <= kept.min()
 
 
-@pytest.mark.skipif(not HAVE_REF, reason="the reference checkout is not present")
 def test_processors_match_the_reference_fixture():
-    with open(os.path.join(REF, "compute", "testdata", "logits_processors.json")) as f:
-        cases = json.load(f)
+    cases = CASES["processors"]
     from fastmlx_b200.engine.loading import make_runtime
     from fastmlx_b200.sampling import Sampler, SamplingParams
     sampler = Sampler(make_runtime("float32"))
@@ -105,7 +100,7 @@ def test_processors_match_the_reference_fixture():
                             presence_context_size=p.get("presence_context_size", 20),
                             frequency_context_size=p.get("frequency_context_size", 20))
         logits = torch.tensor([case["logits"]], dtype=torch.float32, device=DEV)
-        tok = sampler.sample(logits, [(sp, 0, 0, case["tokens"])])
+        tok = sampler.sample(logits, [(sp, 0, 0, case["history"])])
         assert logits[0].cpu().tolist() == pytest.approx(case["expected"], abs=1e-6), case["label"]
         assert int(tok[0]) == max(range(len(case["expected"])), key=lambda i: (case["expected"][i], -i)), case["label"]
 

@@ -1,5 +1,6 @@
-"""The plain sampling statements against tamnd/fastmlx's own fixtures (read in place when
-that checkout is present), and the engine's uniform numbers."""
+"""The plain sampling statements against the cases of tamnd/fastmlx's own fixtures (kept as
+data in tests/data/sampling_cases.json and, when that checkout is present, compared with the
+files they come from), and the engine's uniform numbers."""
 import json
 import os
 
@@ -15,20 +16,24 @@ needs_ref = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "compute", "t
                                reason="the reference checkout is not present")
 
 
-def filter_cases():
-    with open(os.path.join(REF, "compute", "testdata", "sampler_filters.json")) as f:
-        return json.load(f)
-
-
-def processor_cases():
-    with open(os.path.join(REF, "compute", "testdata", "logits_processors.json")) as f:
-        return json.load(f)
+with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "sampling_cases.json")) as _f:
+    CASES = json.load(_f)
 
 
 @needs_ref
+def test_the_kept_cases_are_the_reference_fixtures():
+    with open(os.path.join(REF, "compute", "testdata", "sampler_filters.json")) as f:
+        fx = [c for c in json.load(f)["cases"] if c["op"] in ("apply_top_p", "apply_min_p", "apply_top_k")]
+    assert [(c["label"], c["op"], c["params"], c["logits"], [int(x) for x in c["kept"]]) for c in fx] == \
+        [(c["label"], c["op"], c["params"], c["logits"], c["kept"]) for c in CASES["filters"]]
+    with open(os.path.join(REF, "compute", "testdata", "logits_processors.json")) as f:
+        pc = json.load(f)
+    assert [(c["label"], c["params"], c["tokens"], c["logits"], c["expected"]) for c in pc] == \
+        [(c["label"], c["params"], c["history"], c["logits"], c["expected"]) for c in CASES["processors"]]
+
+
 def test_plain_filters_match_the_reference_fixture():
-    fx = filter_cases()
-    for case in fx["cases"]:
+    for case in CASES["filters"]:
         lp = ps.log_softmax(case["logits"])
         p = case["params"]
         if case["op"] == "apply_top_p":
@@ -39,14 +44,13 @@ def test_plain_filters_match_the_reference_fixture():
             keep = ps.top_k_keep(lp, p["top_k"])
         else:
             continue
-        assert keep == case["kept"], case["label"]
+        assert [int(x) for x in keep] == case["kept"], case["label"]
 
 
-@needs_ref
 def test_plain_processors_match_the_reference_fixture():
-    for case in processor_cases():
+    for case in CASES["processors"]:
         p = case["params"]
-        got = ps.apply_processors(case["tokens"], case["logits"], p.get("logit_bias"), p.get("repetition_penalty"),
+        got = ps.apply_processors(case["history"], case["logits"], p.get("logit_bias"), p.get("repetition_penalty"),
                                   p.get("presence_penalty"), p.get("frequency_penalty"),
                                   p.get("repetition_context_size") or 20, p.get("presence_context_size") or 20,
                                   p.get("frequency_context_size") or 20)

@@ -61,3 +61,19 @@ def reference_dir() -> str:
     import os
     here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     return os.environ.get("FASTMLX_REFERENCE") or os.path.join(os.path.dirname(here), "reference")
+
+
+def check_greedy(cfg, W, prompt, got, round_to, slack):
+    """Every generated token is the plain model's best at its place, given the tokens before it
+    (one forward over prompt + generated: the model is causal), or falls short of the best
+    by less than `slack` of the largest logit (where two logits are that close, rounding
+    decides, and either choice is right)."""
+    import plain_llama
+    logits = plain_llama.forward(cfg, W, list(prompt) + list(got), round_to)[len(prompt) - 1: -1]
+    assert logits.shape[0] == len(got)
+    for i, tok in enumerate(got):
+        row = logits[i]
+        best = int(torch.argmax(row))
+        if best != tok:
+            gap = float(row[best] - row[tok]) / float(row.abs().max())
+            assert gap < slack, f"token {i}: engine chose {tok}, plain model {best}, gap {gap:.2e} (allowed {slack:.0e})"
