@@ -58,7 +58,9 @@ class CacheManager:
     def __init__(self, cache_needs, *, page_size: int, num_pages: int, max_requests: int,
                  dtype: torch.dtype = torch.bfloat16, device="cpu", allocate: bool = True):
         """`cache_needs`: per schedule entry (PagedKVSpec | None, StateSpec | None,
-        cache_from | None), as Model.cache_needs() returns it.  `num_pages` is per group."""
+        cache_from | None), as Model.cache_needs() returns it.  `num_pages` is per group: one
+        number for all, or one per group in the order in which the schedule first names them
+        (a group with a window needs far fewer than one that keeps every key)."""
         self.page_size, self.max_requests = int(page_size), int(max_requests)
         self.dtype, self.device = dtype, device
         self.groups: list[CacheGroup] = []
@@ -70,7 +72,8 @@ class CacheManager:
                 continue
             if kv not in by_spec:
                 by_spec[kv] = len(self.groups)
-                self.groups.append(CacheGroup(kv, [], PagePool(num_pages, page_size)))
+                n = num_pages if isinstance(num_pages, int) else list(num_pages)[len(self.groups)]
+                self.groups.append(CacheGroup(kv, [], PagePool(int(n), page_size)))
             g = by_spec[kv]
             entry_group.append((g, len(self.groups[g].entries)))
             self.groups[g].entries.append(pos)
@@ -118,11 +121,47 @@ class CacheManager:
         return min((g.pool.free_pages for g in self.groups), default=0)
 
     def pages_needed(self, req: RequestCache | None, n_new: int, length: int = 0) -> int:
-        """Most pages any group must take so that `n_new` more tokens fit."""
-        held = 0 if req is None else len(req.tables[0].pages) if req.tables else 0
+        """Most pages any group must take so that `n_new` more tokens fit.  (A block table has
+        an entry for every page of positions, given back or not, so a group with a window asks
+        for as many new pages as one without.)"""
         cur = length if req is None else req.length + req.reserved
         total = -(-(cur + n_new) // self.page_size)
-        return max(0, total - held)
+        if req is None or not req.tables:
+            return max(0, total)
+        return max(max(0, total - len(bt.pages)) for bt in req.tables)
+
+    def holds_alone(self, n_tokens: int, portion: int) -> int:
+        """0 if a request of `n_tokens` fed in portions of at most `portion` tokens fits the
+        pools when it runs alone; else the number of tokens the tightest group can hold.  A
+        group with a window holds the window and the running portion, not the whole request."""
+        for g in self.groups:
+            room = g.pool.num_pages * self.page_size
+            w = g.spec.window
+            need = n_tokens if w <= 0 else min(n_tokens, w + min(portion, n_tokens) + self.page_size)
+            if need > room:
+                return room
+        return 0
+
+    # ------------------------------------------------------------------ per-request state
+    @property
+    def has_state(self) -> bool:
+        return any(e.state is not None for e in self.entries)
+
+    def snapshot_state(self, slots=None):
+        """Copies of the state slots (all, or the given ones): what `restore_state` puts back
+        after a step that must not count (a failed one, or the warm-up run before a capture)."""
+        idx = None if slots is None else torch.as_tensor(list(slots), dtype=torch.long, device=self.device)
+        return idx, [None if e.state is None else (e.state.clone() if idx is None else e.state[idx].clone())
+                     for e in self.entries]
+
+    def restore_state(self, snapshot) -> None:
+        idx, saved = snapshot
+        for e, s in zip(self.entries, saved):
+            if s is not None:
+                if idx is None:
+                    e.state.copy_(s)
+                else:
+                    e.state[idx] = s
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request_id) -> RequestCache:

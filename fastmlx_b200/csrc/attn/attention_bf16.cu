@@ -18,6 +18,7 @@
 //
 // Keys out of sight (beyond a row's position, before its window, or in no page) are
 // zero-filled in shared memory and masked, never read from the cache.
+#include <mutex>
 #include <math.h>
 #include "common.cuh"
 
@@ -644,6 +645,22 @@ FMX_EXPORT long long fmx_attn_decode_scratch_floats(int rows, int nkv, int split
   return splits <= 1 ? 0 : (long long)rows * nkv * splits * 16 * (HD + 2);
 }
 
+// How many splits over the keys a decode step of `rows` rows takes on a device of `sms`
+// multiprocessors: as many as keep the whole grid resident at once (a second, partial round of
+// blocks costs more than it brings), with at least 128 keys to a split and at most 32 splits
+// (measured at batch 1 over 8192 keys: 17 to 32 splits 13.5 us, 48: 15.3, 64: 17.7; over 1024
+// keys: 2 splits 10.8 us, 8: 6.5).
+FMX_EXPORT int fmx_attn_decode_plan(int rows, int nkv, long long max_ctx, int sms) {
+  if (sms <= 0) sms = fmx_num_sms();
+  long long per_sm = (227 * 1024) / (long long)decode_smem();
+  per_sm = per_sm < 1 ? 1 : per_sm > 5 ? 5 : per_sm;
+  long long s = sms * per_sm / ((long long)rows * nkv > 0 ? (long long)rows * nkv : 1);
+  const long long by_keys = (max_ctx + 127) / 128;
+  if (s > by_keys) s = by_keys;
+  if (s > 32) s = 32;
+  return s < 1 ? 1 : (int)s;
+}
+
 FMX_EXPORT int fmx_attn_prefill(const void* q, long long q_stride, const void* kv, const int* block_tables,
                                 int bt_stride, const int* row_start, const int* row_ctx, void* out, int rows,
                                 int max_q_len, int nh, int nkv, int page_size, long long num_pages, float scale,
@@ -725,13 +742,22 @@ constexpr int NOALLOC_MAX_DEVICES = 64;
 // In host code the array's name stands for the symbol, not for a device address: a kernel
 // must be given what cudaGetSymbolAddress returns for the current device.
 float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_noalloc_mutex;          // two threads may make a device's first call at once
 
-int noalloc_setup(float** ptr) {
+int noalloc_setup(float** ptr, cudaStream_t stream) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fmx_fail("fmx_attn_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fmx_fail("fmx_attn_decode_noalloc: device %d is out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   if (g_noalloc_ptr[dev] == nullptr) {
+    // the set-up asks the runtime for an address and an attribute: not inside a stream capture
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing(stream, &cap);
+    if (e != cudaSuccess) return fmx_fail("fmx_attn_decode_noalloc: cudaStreamIsCapturing: %s", cudaGetErrorString(e));
+    if (cap != cudaStreamCaptureStatusNone)
+      return fmx_fail("fmx_attn_decode_noalloc: the first call on device %d does its set-up and must come before any "
+                      "stream capture; call it once on this device outside the capture", dev);
     float* p = nullptr;
     e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
     if (e != cudaSuccess || p == nullptr)
@@ -769,7 +795,7 @@ FMX_EXPORT int fmx_attn_decode_noalloc(const void* q, long long q_stride, const 
                     "built-in array holds %d; use fewer splits or fmx_attn_decode with a workspace of your own",
                     rows, nkv, splits, HD, need, FMX_ATTN_NOALLOC_MAX_FLOATS);
   float* scratch = nullptr;
-  if (noalloc_setup(&scratch) != 0) return 1;
+  if (noalloc_setup(&scratch, stream) != 0) return 1;
   float* part_o = scratch;
   float* part_ml = scratch + (long long)rows * nkv * splits * 16 * HD;
   dim3 grid(splits, nkv, rows);

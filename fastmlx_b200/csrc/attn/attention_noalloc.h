@@ -16,7 +16,12 @@
 //     with an error text; nothing is launched.
 //   * The first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and sets the kernels' shared-memory
-//     limit.  Make that first call outside any stream capture.
+//     limit.  Make that first call outside any stream capture: a first call on a capturing
+//     stream is refused with an error text.  The set-up is guarded by a lock, so two
+//     threads may race to be first.
+//   * Any number of splits fits that the array has room for.  (fmx_attn_decode stops at 64
+//     because there the last block of a row combines the splits through shared memory; this
+//     entry always combines in a second kernel, which walks the splits in a loop.)
 //   * The entry point calls no cudaMalloc, cudaFree or allocating library routine.
 //   * All calls share the one array and it keeps whatever the last call left in it.  The
 //     kernels write every partial before the combine step reads it, so nothing has to be

@@ -26,7 +26,11 @@ GROUPS = {
     "bf16": "bf16",
     "attn": "attn",
     "tc": "tc",
+    # the tensor-core product built for one test: a wait limit of 100,000 clocks and a producer that
+    # leaves out its last block, so that the path a wait takes when it runs out is executed
+    "tc_expiry": "tc",
 }
+EXTRA_FLAGS = {"tc_expiry": ["-DFMX_WAIT_CYCLES=100000LL", "-DFMX_SKIP_LAST_STAGE=1"]}
 HEAD_DIMS = tuple(range(16, 257, 16))
 
 
@@ -39,7 +43,7 @@ def _split(group: str) -> tuple[str, list[str]]:
         return "attn", [f"-DFMX_HD={hd}"]
     if group not in GROUPS:
         raise BuildError(f"unknown kernel group {group!r}")
-    return group, []
+    return group, list(EXTRA_FLAGS.get(group, ()))
 
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

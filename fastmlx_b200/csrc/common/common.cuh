@@ -81,6 +81,7 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 bool fmx_pdl_enabled();
+int fmx_num_sms();          // multiprocessors of the current device
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t fmx_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -281,7 +281,8 @@ FMX_EXPORT int fmx_silu_mul(const void* gu, void* out, int rows, int I, int blk,
   if (blk <= 0 || I % blk) return fmx_fail("fmx_silu_mul: %d is no multiple of the block size %d", I, blk);
   const long long n = (long long)rows * I;
   const int block = 256;
-  const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
+  const long long cap = (long long)fmx_num_sms() * 16;
+  const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
   if (dtype == FMX_F32)
     silu_mul_kernel<float><<<grid, block, 0, stream>>>((const float*)gu, (float*)out, rows, I, blk);
   else if (dtype == FMX_BF16) {

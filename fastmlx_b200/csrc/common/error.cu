@@ -20,17 +20,25 @@ int fmx_fail(const char* fmt, ...) {
   return 1;
 }
 
-// FASTMLX_PDL=0 turns programmatic dependent launch off (every kernel then waits for the one
-// before it to finish before it is scheduled).
-static int g_pdl = -1;
-bool fmx_pdl_enabled() {
-  if (g_pdl < 0) {
-    const char* e = getenv("FASTMLX_PDL");
-    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  return g_pdl == 1;
-}
+// Programmatic dependent launch is on; fmx_set_pdl(0) turns it off for this library (every
+// kernel then waits for the one before it to finish before it is scheduled), which is how
+// its effect is measured.
+static int g_pdl = 1;
+bool fmx_pdl_enabled() { return g_pdl == 1; }
 FMX_EXPORT void fmx_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
+// Multiprocessors of the current device, asked once per device.
+int fmx_num_sms() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 
 FMX_EXPORT const char* fmx_last_error() { return g_error; }
 

@@ -6,7 +6,13 @@
 #include "common.cuh"
 
 namespace fmx_tc {
-constexpr long long WAIT_CYCLES = 2000000000LL;        // about a second
+// How long a wait on a barrier may take before it gives up: about a second.  A build of the
+// same sources for a test sets a short limit (-DFMX_WAIT_CYCLES=...), so that a wait that nothing
+// will ever satisfy runs out while the test watches.
+#ifndef FMX_WAIT_CYCLES
+#define FMX_WAIT_CYCLES 2000000000LL
+#endif
+constexpr long long WAIT_CYCLES = FMX_WAIT_CYCLES;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

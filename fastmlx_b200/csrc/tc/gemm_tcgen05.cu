@@ -21,6 +21,11 @@
 // No cluster: every CTA loads its own tiles.  Every wait on a barrier is bounded by time: after about a
 // second it gives up, leaves FMX_WAIT_EXPIRED in the status word, and the CTA drains what it
 // has in flight, frees its tensor memory and returns.
+//
+// Compiled with -DFMX_SKIP_LAST_STAGE (and a short -DFMX_WAIT_CYCLES) the producer leaves out the
+// last k block of its CTA's last tile: the issuing thread and the epilogue warps then wait for
+// something that never comes, with no copy in flight, and the expiry path runs.  Only the test
+// library `tc_expiry` is built that way; the product library never is.
 #include <cuda.h>
 #include "common.cuh"
 #include "tcgen05.cuh"
@@ -38,6 +43,7 @@ template <int BN> struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = BN > 128 ? 512 : 256;   // two accumulators; a power of two >= 32
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+  static_assert((2 * STAGES + 5) * 8 + 4 <= 256, "the barriers outgrow their corner of shared memory");
 };
 
 __device__ __forceinline__ unsigned pack2(float lo, float hi) {
@@ -59,7 +65,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* empty_bar = bars + cfg::STAGES;        // [STAGES]
   uint64_t* acc_full = bars + 2 * cfg::STAGES;     // [2]
   uint64_t* acc_empty = acc_full + 2;              // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* drain_bar = acc_empty + 2;             // [1] a wait that expired: have the products issued so far finished?
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
@@ -75,6 +82,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(smem_u32(&acc_full[a]), 1);
       mbar_init(smem_u32(&acc_empty[a]), 128);
     }
+    mbar_init(smem_u32(drain_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -98,6 +106,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
       for (int kb = 0; kb < k_blocks; ++kb) {
+#ifdef FMX_SKIP_LAST_STAGE
+        if (kb == k_blocks - 1 && t + (int)gridDim.x >= n_tiles) break;      // the test build: never bring the last block
+#endif
         if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) { ok = false; break; }
         const uint32_t fb = smem_u32(&full_bar[stage]);
         unsigned char* sa = smem + (size_t)stage * cfg::STAGE_BYTES;
@@ -158,7 +169,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       phase ^= 1;
     }
-    if (!ok) fmx_set_status(status, FMX_WAIT_EXPIRED, 2, blockIdx.x);
+    if (!ok) {
+      fmx_set_status(status, FMX_WAIT_EXPIRED, 2, blockIdx.x);
+      // products issued before the wait ran out may still be running: the tensor memory they
+      // write is not freed under them.  A commit arrives when all of them are done.
+      umma_commit(smem_u32(drain_bar));
+      mbar_wait(smem_u32(drain_bar), 0);
+    }
   } else if (warp >= 2) {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;                  // the 32 lanes of tensor memory this warp may read
@@ -264,7 +281,7 @@ FMX_EXPORT int fmx_gemm_tcgen05(const void* A, long long lda, const void* W, lon
     return fmx_fail("fmx_gemm_tcgen05: rows must start on 16-byte boundaries (K=%d lda=%lld ldw=%lld)", K, lda, ldw);
   if (epilogue == EPI_SILU_MUL && N % bn) return fmx_fail("fmx_gemm_tcgen05: gate/up blocks need N a multiple of %d", bn);
   if (epilogue == EPI_RESIDUAL && residual == nullptr) return fmx_fail("fmx_gemm_tcgen05: the residual epilogue needs a residual");
-  if (sms <= 0) sms = 148;
+  if (sms <= 0) sms = fmx_num_sms();
 #define FMX_TC_CASE(BN_, EPI_) \
   if (bn == BN_ && epilogue == EPI_) return run<BN_, EPI_>(A, lda, W, ldw, C, ldc, residual, ldr, M, N, K, sms, status, stream)
   FMX_TC_CASE(256, EPI_PLAIN);

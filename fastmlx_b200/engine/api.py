@@ -75,7 +75,16 @@ class Engine:
         else:
             limit = self.model.max_positions or 8192
             pages = -(-min(limit, 8192) // ec.block_size) * ec.max_concurrent_requests
-        self.manager = CacheManager(needs, page_size=ec.block_size, num_pages=max(1, pages),
+        # a group with a window holds, per request, the window and the portion that runs: it
+        # gets that many pages, not the pool of a group that keeps every key
+        portion = ec.prefill_chunk or ec.max_num_batched_tokens
+        per_group = []
+        for g in probe.groups:
+            n = max(1, pages)
+            if g.spec.window > 0:
+                n = min(n, ec.max_concurrent_requests * (-(-(g.spec.window + portion) // ec.block_size) + 1))
+            per_group.append(n)
+        self.manager = CacheManager(needs, page_size=ec.block_size, num_pages=per_group or max(1, pages),
                                     max_requests=ec.max_concurrent_requests, dtype=self.rt.dtype,
                                     device=self.rt.device)
         self.step_fn = StepFunction(self.model, self.manager, self.rt, cuda_graphs=ec.cuda_graphs)

@@ -87,7 +87,8 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
 
     `pad_rows` / `pad_blocks` / `pad_want` fix the sizes (rows, block-table width, one
     wanted place per row) for a captured graph: padding rows bring one token at position
-    -1 that is stored nowhere and sees no key."""
+    -1 that is stored nowhere and sees no key, and their state slot is -1 (a mixer with
+    state of its own skips them as attention skips position -1)."""
     R = len(entries)
     q_lens = [len(e.tokens) for e in entries]
     T = sum(q_lens)
@@ -146,6 +147,7 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
         rstart[:Rp + 1] = np.arange(Rp + 1, dtype=np.int32)
         rctx[:R] = ctxs
         rslot[:R] = slots
+        rslot[R:Rp] = -1
         view("want")[:] = want
         ctx_np = np.asarray(ctxs, dtype=np.int64)
         for g in range(ngroups):
@@ -167,7 +169,7 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
     for r in range(R, Rp) if not one_each else ():   # padding rows: one token, no context, stored nowhere
         trow[off] = r
         pos[off] = -1
-        rstart[r], rctx[r], rslot[r] = off, 0, 0
+        rstart[r], rctx[r], rslot[r] = off, 0, -1
         off += 1
     if not one_each:
         rstart[Rp] = off

@@ -69,14 +69,14 @@ class Scheduler:
         req.arrival = self._arrivals
         self._arrivals += 1
         n = len(req.prompt_token_ids)
-        pool_tokens = min(g.pool.num_pages for g in self.manager.groups) * self.manager.page_size \
-            if self.manager.groups else 1 << 62
+        portion = self.cfg.prefill_chunk if self.cfg.prefill_chunk > 0 else self.cfg.max_num_batched_tokens
+        pool_tokens = self.manager.holds_alone(n, portion)
         err = ""
         if n == 0:
             err = "empty prompt"                       # compute/batch_generator.go:71,128-130
         elif self.max_positions and n >= self.max_positions:
             err = f"prompt of {n} tokens leaves no room under max_position_embeddings ({self.max_positions})"
-        elif n > pool_tokens:
+        elif pool_tokens:
             err = f"prompt of {n} tokens exceeds the cache pool of {pool_tokens} tokens"
         if err:
             req.status, req.error = RequestStatus.FINISHED_ERROR, err

@@ -47,12 +47,18 @@ class _DecodeGraph:
         n = probe.scratch["layout_ints"]
         self.static = StaticBuffers(n, rt.device)
         ctx = self._context(fn, entries)
-        # warm up outside the capture (library handles, lazily built kernels), then capture
+        # warm up outside the capture (library handles, lazily built kernels), then capture.  The
+        # warm-up runs the real step once and the first replay runs it again: writing the same
+        # keys and values twice changes nothing, but per-request state would advance twice, so
+        # it is put back as it was.
+        saved = manager.snapshot_state() if manager.has_state else None
         side = torch.cuda.Stream(device=rt.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             fn.model.forward(ctx)
         torch.cuda.current_stream().wait_stream(side)
+        if saved is not None:
+            manager.restore_state(saved)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         count = getattr(rt.k, "launch_count", lambda: 0)
@@ -99,22 +105,11 @@ class StepFunction:
         self.tokens_run = 0
         self.last_ctx: StepContext | None = None
         if self.cuda_graphs:
-            # the split decode attention's workspace must not grow once a graph holds its address
-            k = rt.k
-            need = 0
-            for g in manager.groups:
-                rows = 1
-                while rows <= max_graph_rows:
-                    s = k.decode_splits(rows, g.spec.num_kv_heads, 1 << 30, g.spec.head_dim)
-                    need = max(need, k.attn_decode_scratch_floats(rows, g.spec.num_kv_heads, s, g.spec.head_dim))
-                    rows *= 2
-            k.attention_scratch(rt.device, need)
-            if hasattr(k, "attention_tickets"):
-                k.attention_tickets(rt.device)
-            if hasattr(k, "skinny_workspace"):
-                k.skinny_workspace(rt.device)
-            if getattr(k, "stream_enabled", lambda: False)():
-                k.stream_workspace(rt.device)
+            # workspaces whose addresses the graphs will hold are made before any capture
+            for name in ("attention_scratch", "attention_tickets", "argmax_workspace"):
+                make = getattr(rt.k, name, None)
+                if make is not None:
+                    make(rt.device)
 
     def run(self, entries: list[StepEntry], reserved: bool = False, check: bool = True,
             tokens_from: torch.Tensor | None = None) -> torch.Tensor:
@@ -138,6 +133,11 @@ class StepFunction:
             if limit and e.request.length + len(e.tokens) > limit:
                 raise StepError(f"request {e.request.request_id!r} would pass max_position_embeddings ({limit})")
         taken = []
+        # With `check` the step's outcome is known before this returns, and a failed step leaves
+        # pages and per-request state as they were.  Without it the caller reads the status later
+        # and fails the step's requests, whose pages and slots are then given back whole.
+        saved = self.manager.snapshot_state([e.request.slot for e in entries]) \
+            if check and self.manager.has_state else None
         try:
             if not reserved:
                 for e in entries:
@@ -149,6 +149,8 @@ class StepFunction:
         except BaseException:
             for r in taken:
                 self.manager.rollback(r)
+            if saved is not None:
+                self.manager.restore_state(saved)
             raise
         for r in taken:
             self.manager.commit(r)

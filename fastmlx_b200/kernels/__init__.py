@@ -19,7 +19,6 @@ def launch_count() -> int:
     return _lib.launches
 
 F32, BF16 = 0, 1
-NUM_SMS = 148
 BAD_TOKEN, BAD_SLOT, BAD_PAGE, BAD_ROW = 1, 2, 3, 4
 
 
@@ -120,15 +119,25 @@ def gemm_simple(x, w, bias, out_dtype) -> torch.Tensor:
     return out
 
 
-import os as _os
-
-_USE_TC = _os.environ.get("FASTMLX_GEMM", "tcgen05") != "cublas"      # "cublas": library products for prefill
 _tc_status: dict = {}
+_props: dict = {}
 
 
 def _dev_index(device) -> int:
     device = torch.device(device)
     return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def num_sms(device=None) -> int:
+    """Multiprocessors of the device (148 on a B200; fewer under a partition), read once per
+    device.  Where no device is visible (host-side arithmetic in tests) a B200's count."""
+    if not torch.cuda.is_available():
+        return 148
+    i = _dev_index(device if device is not None else "cuda")
+    n = _props.get(i)
+    if n is None:
+        n = _props[i] = torch.cuda.get_device_properties(i).multi_processor_count
+    return n
 
 
 def set_status_word(device, status: torch.Tensor) -> None:
@@ -144,69 +153,35 @@ def _status_word(device):
     return st
 
 
-SKINNY_MAX_ROWS = 8          # beyond this the library product is faster
-
-
-SKINNY_WS_FLOATS = 1 << 20       # 4 MiB of split-K partials
-SKINNY_TICKETS = 1 << 14
-_skinny_ws: dict = {}
-
-
-def skinny_workspace(device):
-    """Partials and tickets of the split-K skinny product, one pair per device, made once (a
-    CUDA graph holds their addresses).  The tickets start at zero and every launch leaves
-    them at zero.  Launches sharing them run on one stream."""
-    ws = _skinny_ws.get(device)
-    if ws is None:
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("the skinny product's workspace must exist before a CUDA graph is captured")
-        ws = (torch.empty(SKINNY_WS_FLOATS, dtype=torch.float32, device=device),
-              torch.zeros(SKINNY_TICKETS, dtype=torch.int32, device=device))
-        _skinny_ws[device] = ws
-    return ws
-
-
-def skinny_splits(M: int, N: int, K: int) -> int:
-    """Split K over blocks until the grid fills the GPU about three times, keeping at least
-    512 of K per block and the partials inside the workspace."""
-    tiles = -(-N // 16)
-    s = max(1, min(round(4 * NUM_SMS / tiles), K // 512))
-    while s > 1 and (tiles * s * 128 * (1 if M <= 8 else 2) > SKINNY_WS_FLOATS or tiles > SKINNY_TICKETS):
-        s -= 1
-    return s
-
-
-def skinny_gemm(x, w, bias, out_dtype, splits=None) -> torch.Tensor:
-    """The decode-step product: at most 16 rows of x against a weight matrix streamed once."""
-    M, K = x.shape
-    N = w.shape[0]
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    if splits is None:
-        splits = skinny_splits(M, N, K)
-    ws, tickets = skinny_workspace(x.device) if splits > 1 else (None, None)
-    call("bf16", "fmx_skinny_gemm", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), out.data_ptr(),
-         out.stride(0), M, N, K, _dt(out), splits, _ptr(ws), ws.numel() if ws is not None else 0, _ptr(tickets),
-         tickets.numel() if tickets is not None else 0, _stream())
-    return out
-
-
+# Which kernel multiplies, by the rows M of x (one path per class, no switch):
+#   M <= 16                    whole-K weight-streaming kernel (`gemv`), except the vocabulary-sized head
+#   M >= 128, full rounds      tcgen05 kernel (`gemm_tcgen05`)
+#   everything else in bf16    the library (cuBLAS through torch.mm), as tamnd/fastmlx calls its library's matmul
+#   32-bit or mixed types      fixed-order FMA kernel (`gemm_simple`)
 GEMV_MAX_ROWS = 16
-# from this many output features on (the vocabulary) a decode step's product goes to the library
-LIBRARY_MIN_FEATURES = int(_os.environ.get("FASTMLX_LIBRARY_MIN_FEATURES", "65536"))
+LIBRARY_MIN_FEATURES = 65536     # from this many output features on (the vocabulary) the library's product streams best
+TC_MIN_ROWS = 128
+GATE_UP_BLOCK = 128              # gate/up rows of a fused weight alternate in blocks of this many
+EPI_PLAIN, EPI_SILU_MUL, EPI_RESIDUAL = 0, 1, 2
+
+
+def _bf16_operands(x, w) -> bool:
+    """bfloat16 operands laid out as the tensor-core kernels read them (16-byte rows)."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def can_gemv(x, w) -> bool:
     """May this product run on the whole-K kernel of decode steps?"""
-    return (_DECODE_GEMM == "gemv" and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and 0 < x.shape[0] <= GEMV_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
-            and w.stride(1) == 1 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+    return _bf16_operands(x, w) and x.shape[0] <= GEMV_MAX_ROWS
 
 
-def gemv_width(n_out: int, block: int = 0) -> int:
+def gemv_width(n_out: int, block: int = 0, device=None) -> int:
     """Output features per block: 32 once that still gives every SM a block, else 16 (measured:
     wider blocks re-read x less and keep more of W in flight per block, but too few of them
     leave SMs idle)."""
-    wide = 32 if n_out // 32 >= NUM_SMS else 16
+    wide = 32 if n_out // 32 >= num_sms(device) else 16
     while block and block % wide:
         wide //= 2
     return wide
@@ -223,48 +198,45 @@ def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     if wide is None:
-        wide = gemv_width(n_out, block)
+        wide = gemv_width(n_out, block, x.device)
     if warps is None:
         # fewer blocks than SMs over a long K: twice the warps keep enough bytes in flight
-        warps = 16 if wide < 32 and -(-n_out // wide) < NUM_SMS and K >= 4096 else 8
+        warps = 16 if wide < 32 and -(-n_out // wide) < num_sms(x.device) and K >= 4096 else 8
     call("bf16", "fmx_gemv", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), _ptr(residual),
          residual.stride(0) if residual is not None else 0, out.data_ptr(), out.stride(0), M, N, K, _dt(out), int(block),
          int(wide), int(warps), _stream())
     return out
 
 
-EPI_PLAIN, EPI_SILU_MUL, EPI_RESIDUAL = 0, 1, 2
-
-
-GATE_UP_BLOCK = 128          # gate/up rows of a fused weight alternate in blocks of this many
-TC_MIN_ROWS = 128            # from this many rows on, products run on the tcgen05 kernel
-
-
-def tc_enabled() -> bool:
-    return _USE_TC
-
-
-def tile_width(M: int, N: int) -> int:
+def tile_width(M: int, N: int, sms: int = 148) -> int:
     """The tile width (of 128, 192, 256) whose tiles fill the SMs' rounds best; wider wins ties."""
     best, best_eff = 256, -1.0
     for bn in (256, 192, 128):
         tiles = -(-M // 128) * -(-N // bn)
-        eff = tiles / (-(-tiles // NUM_SMS) * NUM_SMS) * (N / (-(-N // bn) * bn)) * (0.8 if bn == 128 else 1.0)
+        eff = tiles / (-(-tiles // sms) * sms) * (N / (-(-N // bn) * bn)) * (0.8 if bn == 128 else 1.0)
         if eff > best_eff + 1e-9:
             best, best_eff = bn, eff
     return best
 
 
-def tc_fills_the_gpu(M: int, N: int) -> bool:
+def tc_fills_the_gpu(M: int, N: int, sms: int = 148) -> bool:
     """The tensor-memory kernel gives each CTA whole tiles and walks K serially within a tile.
     With fewer tiles than about a round of the SMs (short prompts against the narrower matrices)
     most SMs idle behind that walk, and the library's product, which splits K, is two to three
     times faster (512 x 2048 x 8192: 41 us against 17); with full rounds the two are within a tenth."""
     tiles = -(-M // 128) * -(-N // 256)
-    rounds = -(-tiles // NUM_SMS)
+    rounds = -(-tiles // sms)
     # ... and the same when the last round of tiles is mostly empty (192 tiles: two rounds for the
     # work of 1.3; 2048 x 3072 x 2048 takes 28.9 us here against 19.8 in the library)
-    return tiles >= 0.8 * NUM_SMS and tiles >= 0.75 * rounds * NUM_SMS
+    return tiles >= 0.8 * sms and tiles >= 0.75 * rounds * sms
+
+
+def can_tc(x, w, bias=None, out_dtype=torch.bfloat16, epilogue: int = EPI_PLAIN) -> bool:
+    """May this product run on the tcgen05 kernel, and does it fill the GPU there?  One test for
+    `linear` and for the parts that ask for an epilogue."""
+    return (_bf16_operands(x, w) and bias is None and out_dtype == torch.bfloat16 and x.shape[0] >= TC_MIN_ROWS
+            and (epilogue != EPI_SILU_MUL or w.shape[0] % (2 * GATE_UP_BLOCK) == 0)
+            and tc_fills_the_gpu(x.shape[0], w.shape[0], num_sms(x.device)))
 
 
 def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn: int | None = None) -> torch.Tensor:
@@ -273,116 +245,13 @@ def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn
     result is silu(gate) * up, [M, N/2]; EPI_RESIDUAL: residual + product."""
     M, K = x.shape
     N = w.shape[0]
+    sms = num_sms(x.device)
     if bn is None:
-        bn = 2 * GATE_UP_BLOCK if epilogue == EPI_SILU_MUL else tile_width(M, N)
+        bn = 2 * GATE_UP_BLOCK if epilogue == EPI_SILU_MUL else tile_width(M, N, sms)
     out = torch.empty((M, N // 2 if epilogue == EPI_SILU_MUL else N), dtype=torch.bfloat16, device=x.device)
     call("tc", "fmx_gemm_tcgen05", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-         _ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, bn, epilogue, NUM_SMS,
-         _ptr(status), _stream())
-    return out
-
-
-STREAM_MAX_ROWS = 128
-STREAM_RING_BYTES = 110 * 1024    # a CTA's ring of stages: small enough for two CTAs on one SM
-_stream_ws: dict = {}
-
-
-def stream_plan(M: int, N: int, K: int, dual: bool, ctas: int | None = None, ring_bytes: int | None = None):
-    """-> (CTAs, stages, workspace floats, tickets) of the streaming product for these sizes."""
-    halves = 2 if dual else 1
-    nb = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
-    tiles = N // 256 if dual else -(-N // 128)
-    total = tiles * (-(-K // 64) if dual else -(-K // 128))       # a unit: 32 KB of W
-    stage_bytes = 32768 + (1 if dual else 2) * nb * 128
-    stages = max(2, min(12, (ring_bytes or STREAM_RING_BYTES) // stage_bytes))
-    ctas = max(1, min(ctas or NUM_SMS, total))
-    return ctas, stages, ctas * 2 * halves * M * 128, tiles
-
-
-def stream_workspace(device):
-    """Partial sums and tickets of the streaming product, one pair per device, made once at the
-    largest size a call can need (one CTA per SM, 128 rows, a gate/up pair: 39 MB) since a
-    CUDA graph holds their addresses.  The tickets start at zero and every launch leaves them
-    at zero.  Launches sharing them run on one stream."""
-    ws = _stream_ws.get(device)
-    if ws is None:
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("the streaming product's workspace must exist before a CUDA graph is captured")
-        ws = (torch.empty(NUM_SMS * 2 * 2 * STREAM_MAX_ROWS * 128, dtype=torch.float32, device=device),
-              torch.zeros(1 << 14, dtype=torch.int32, device=device))
-        _stream_ws[device] = ws
-    return ws
-
-
-_FUSE_ROPE = _os.environ.get("FASTMLX_FUSE_ROPE", "1") != "0"     # decode attention rotates and stores by itself
-
-# which kernel multiplies the few rows of a decode step: "gemv" (whole K per block), "skinny"
-# (16-row tiles, K split over blocks), "stream" (TMA ring + tcgen05)
-_DECODE_GEMM = _os.environ.get("FASTMLX_DECODE_GEMM", "gemv")
-
-
-def stream_enabled() -> bool:
-    return _DECODE_GEMM == "stream"
-
-
-def can_stream(x, w, bias=None, block: int = 0) -> bool:
-    """May this product run on the streaming tcgen05 kernel?"""
-    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and 0 < x.shape[0] <= STREAM_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
-            and x.stride(1) == 1 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-            and w.data_ptr() % 16 == 0 and w.shape[0] <= 128 << 14
-            and (block == 0 or (block == 128 and w.shape[0] % 256 == 0 and bias is None)))
-
-
-def gemm_stream(x, w, bias=None, out_dtype=torch.bfloat16, block: int = 0, ctas=None, ring_bytes=None, status=None):
-    """x[M <= 128, K] @ w[N, K]^T with W streamed once through shared memory by TMA and
-    multiplied on the tcgen05 tensor cores (W's rows on the lanes of tensor memory, tokens on
-    its columns).  block = 128: w's rows alternate in blocks of 128 gate rows and their up
-    rows, and the result is silu(gate) * up, [M, N/2]."""
-    M, K = x.shape
-    N = w.shape[0]
-    dual = block > 0
-    if dual and block != 128:
-        raise KernelError(f"the streaming product takes gate/up blocks of 128 rows, not {block}")
-    n_ctas, stages, floats, n_tickets = stream_plan(M, N, K, dual, ctas, ring_bytes)
-    ws, tickets = stream_workspace(x.device)
-    if floats > ws.numel() or n_tickets > tickets.numel():
-        raise KernelError(f"the streaming product's workspace does not hold {floats} floats and {n_tickets} tickets")
-    out = torch.empty((M, N // 2 if dual else N), dtype=out_dtype, device=x.device)
-    call("tc", "fmx_gemm_stream", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), out.data_ptr(),
-         out.stride(0), M, N, K, _dt(out), 1 if dual else 0, n_ctas, stages, ws.data_ptr(), ws.numel(),
-         tickets.data_ptr(), tickets.numel(), _ptr(status if status is not None else _status_word(x.device)), _stream())
-    return out
-
-
-def can_fuse_skinny(x, w, bias=None) -> bool:
-    """May this product run on the fused skinny kernel (norm prologue, residual / SiLU-mul epilogue)?"""
-    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and bias is None
-            and 0 < x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
-            and x.stride(1) == 1 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
-def skinny_fused(x, w, out_dtype=torch.bfloat16, norm=None, residual=None, block: int = 0, out=None, splits=None):
-    """x[M <= 8, K] @ w[N, K]^T with its neighbours folded in.  norm = (weight float32 [K], eps):
-    the rows of x are RMS-normalised on the fly.  residual [M, n_out] is added to the product
-    (out may be the residual itself).  block > 0: w's rows alternate in blocks of `block` gate
-    rows and their up rows, and the result is silu(gate) * up, [M, N/2]."""
-    M, K = x.shape
-    N = w.shape[0]
-    n_out = N // 2 if block else N
-    if out is None:
-        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-    tiles = N // 32 if block else -(-N // 16)
-    if splits is None:
-        splits = max(1, min(round(4 * NUM_SMS / tiles), K // 512))
-        while splits > 1 and (tiles * splits * (256 if block else 128) > SKINNY_WS_FLOATS or tiles > SKINNY_TICKETS):
-            splits -= 1
-    ws, tickets = skinny_workspace(x.device) if splits > 1 else (None, None)
-    nw, eps = norm if norm is not None else (None, 0.0)
-    call("bf16", "fmx_skinny_fused", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-         M, N, K, _dt(out), _ptr(nw), float(eps), _ptr(residual), residual.stride(0) if residual is not None else 0,
-         int(block), splits, _ptr(ws), ws.numel() if ws is not None else 0, _ptr(tickets),
-         tickets.numel() if tickets is not None else 0, _stream())
+         _ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, bn, epilogue, sms,
+         _ptr(status if status is not None else _status_word(x.device)), _stream())
     return out
 
 
@@ -391,36 +260,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype) -> torch.Tensor:
     _need_cuda(x, w, bias)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
     assert x.stride(1) == 1 and w.stride(1) == 1
-    if _DECODE_GEMM == "gemv" and w.shape[0] < LIBRARY_MIN_FEATURES and can_gemv(x, w) and out_dtype in (torch.bfloat16, torch.float32):
-        # From ~64k output features on (the vocabulary) the library's product streams best.
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[0] == 0:
+        return gemm_simple(x, w, bias, out_dtype)
+    if can_gemv(x, w) and (w.shape[0] < LIBRARY_MIN_FEATURES or bias is not None):
         return gemv(x, w, bias, out_dtype)
-    if _DECODE_GEMM == "stream" and x.shape[0] < TC_MIN_ROWS and w.shape[0] < LIBRARY_MIN_FEATURES and can_stream(x, w, bias) \
-            and out_dtype in (torch.bfloat16, torch.float32):
-        return gemm_stream(x, w, bias, out_dtype)
-    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_MAX_ROWS \
-            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32):
-        # From ~64k output features on (the vocabulary) the library's product streams best
-        # (77 us against 89 us for 128256 x 2048); below that this kernel, whose launch overlaps
-        # its predecessor's tail.
-        if w.shape[0] < LIBRARY_MIN_FEATURES or bias is not None:
-            return skinny_gemm(x, w, bias, out_dtype)
-        return torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else torch.mm(x, w.t(), out_dtype=out_dtype)
-    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] >= TC_MIN_ROWS and bias is None \
-            and out_dtype == torch.bfloat16 and _USE_TC and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 \
-            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 \
-            and tc_fills_the_gpu(x.shape[0], w.shape[0]):
-        return gemm_tcgen05(x, w, _status_word(x.device))
-    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0:
-        wt = w.t()
-        if bias is not None:
-            if out_dtype == torch.bfloat16:
-                return torch.addmm(bias.to(torch.bfloat16), x, wt)
-            return gemm_simple(x, w, bias, out_dtype)
+    if can_tc(x, w, bias, out_dtype):
+        return gemm_tcgen05(x, w)
+    wt = w.t()
+    if bias is not None:
         if out_dtype == torch.bfloat16:
-            return torch.mm(x, wt)
-        return torch.mm(x, wt, out_dtype=out_dtype)
-    return gemm_simple(x, w, bias, out_dtype)
+            return torch.addmm(bias.to(torch.bfloat16), x, wt)
+        return gemm_simple(x, w, bias, out_dtype)
+    return torch.mm(x, wt) if out_dtype == torch.bfloat16 else torch.mm(x, wt, out_dtype=out_dtype)
 
 
 # ----------------------------------------------------------------------------- positions and cache
@@ -450,18 +301,25 @@ def paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> t
 
 
 MAX_SPLITS = 64
+ATTN_SCRATCH_FLOATS = 8 << 20        # 32 MiB of split partials per device
 _scratch: dict = {}
 
 
-def attention_scratch(device, floats: int) -> torch.Tensor:
-    """The workspace of the split decode attention (partial outputs, maxima and sums), one
-    per device, grown on demand.  A CUDA graph must not grow it: size it before capture."""
-    buf = _scratch.get(device)
-    if buf is None or buf.numel() < floats:
+def attention_scratch(device, floats: int = 0) -> torch.Tensor:
+    """The workspace of the split decode attention (partial outputs, maxima and sums): one per
+    device, made once at a fixed size and never replaced, since captured graphs hold its
+    address.  The engine's own split counts keep rows * kv heads * splits within a round of
+    resident blocks, which needs at most 12 MB; a call that asks for more than the buffer
+    holds is refused."""
+    i = _dev_index(device)
+    buf = _scratch.get(i)
+    if buf is None:
         if torch.cuda.is_current_stream_capturing():
-            raise KernelError("the attention workspace must be sized before a CUDA graph is captured")
-        buf = torch.empty(max(floats, 1), dtype=torch.float32, device=device)
-        _scratch[device] = buf
+            raise KernelError("the attention workspace must exist before a CUDA graph is captured")
+        buf = _scratch[i] = torch.empty(ATTN_SCRATCH_FLOATS, dtype=torch.float32, device=device)
+    if floats > buf.numel():
+        raise KernelError(f"the split decode attention's workspace holds {buf.numel()} floats, {floats} asked for: "
+                          "use fewer splits")
     return buf
 
 
@@ -479,15 +337,11 @@ def attention_tickets(device) -> torch.Tensor:
     return t
 
 
-def decode_splits(rows: int, nkv: int, max_ctx: int, hd: int = 64) -> int:
-    """As many splits as keep the whole grid resident at once (a second, partial round of
-    blocks costs more than it brings), with at least 128 keys to a split and at most 32 splits
-    (measured at batch 1 over 8192 keys: 17 to 32 splits 13.5 us, 48: 15.3, 64: 17.7; over 1024
-    keys: 2 splits 10.8 us, 8: 6.5)."""
-    stages = 3 if hd <= 128 else 2
-    smem = stages * 2 * 64 * (hd + 8) * 2
-    resident = NUM_SMS * max(1, min(5, (227 * 1024) // smem))
-    return max(1, min(32, MAX_SPLITS, resident // max(1, rows * nkv), -(-max_ctx // 128)))
+def decode_splits(rows: int, nkv: int, max_ctx: int, hd: int = 64, device=None) -> int:
+    """Splits over the keys of a decode step, as the attention library of this head size plans
+    them from its own tile and shared-memory sizes (`fmx_attn_decode_plan`)."""
+    lib = load(f"attn_hd{hd}")
+    return int(lib.fmx_attn_decode_plan(int(rows), int(nkv), int(max_ctx), num_sms(device)))
 
 
 def attn_decode_scratch_floats(rows: int, nkv: int, splits: int, hd: int) -> int:
@@ -503,7 +357,7 @@ def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, spli
     R = ctx.R
     out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
     if splits is None:
-        splits = getattr(ctx, "n_splits", 0) or decode_splits(R, nkv, max(1, ctx.max_ctx_after), hd)
+        splits = getattr(ctx, "n_splits", 0) or decode_splits(R, nkv, max(1, ctx.max_ctx_after), hd, qkv.device)
     need = attn_decode_scratch_floats(R, nkv, splits, hd)
     scratch = attention_scratch(qkv.device, need) if need else None
     tickets = attention_tickets(qkv.device) if need and R * nkv <= ATTN_TICKETS else None
@@ -530,15 +384,7 @@ def paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> 
     return out
 
 
-# Which kernel attends for prompt portions: "auto" takes the tensor-memory kernel where it is
-# at least as fast as the mma.sync one (head size 128: 196 TFLOP/s both; at head size 64 the
-# softmax warps cannot keep up yet: 150 against 180), "tcgen05" and "mma" force one.
-_ATTN_CHOICE = _os.environ.get("FASTMLX_ATTN", "auto")
-TC_ATTN_MIN_TOKENS = 64
-
-
-def _use_tc_attention(hd: int) -> bool:
-    return _ATTN_CHOICE == "tcgen05" or (_ATTN_CHOICE == "auto" and hd in (64, 128))
+TC_ATTN_MIN_TOKENS = 64       # portions at least this long attend on the tensor-memory kernel
 
 
 def tc_attention_ok(nh: int, nkv: int, hd: int, page_size: int, window: int) -> bool:
@@ -564,7 +410,7 @@ def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale, variant:
 def decode_attention_fuses_rope(qkv, kv, ctx, nh, nkv, hd) -> bool:
     """Will `paged_attention` take this step on the split decode kernel, which can rotate q and
     k and store k and v itself?"""
-    return (_FUSE_ROPE and qkv.is_cuda and qkv.dtype == torch.bfloat16 and kv is not None and kv.dtype == qkv.dtype
+    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and kv is not None and kv.dtype == qkv.dtype
             and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0 and ctx.all_decode and nh // nkv <= 16)
 
 
@@ -581,7 +427,7 @@ def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window, rope=None) 
     if rope is not None:
         raise KernelError("only the split decode kernel rotates by itself: ask decode_attention_fuses_rope first")
     if qkv.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0:
-        if _use_tc_attention(hd) and ctx.max_q_len >= TC_ATTN_MIN_TOKENS and tc_attention_ok(nh, nkv, hd, kv.shape[3], window) \
+        if ctx.max_q_len >= TC_ATTN_MIN_TOKENS and tc_attention_ok(nh, nkv, hd, kv.shape[3], window) \
                 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
             return paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale)
         return paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
@@ -597,13 +443,13 @@ _argmax_ws: dict = {}
 def argmax_workspace(device):
     """Chunk results and tickets of the split greedy choice, one pair per device, made once;
     the tickets are zero between launches."""
-    ws = _argmax_ws.get(device)
+    ws = _argmax_ws.get(_dev_index(device))
     if ws is None:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("the greedy choice's workspace must exist before a CUDA graph is captured")
         ws = (torch.empty(ARGMAX_ROWS * ARGMAX_CHUNKS * 2, dtype=torch.int32, device=device),
               torch.zeros(ARGMAX_ROWS, dtype=torch.int32, device=device))
-        _argmax_ws[device] = ws
+        _argmax_ws[_dev_index(device)] = ws
     return ws
 
 
@@ -612,7 +458,7 @@ def argmax_chunks(rows: int, V: int) -> int:
     least ARGMAX_MIN_CHUNK logits; 1 = the one-block kernel."""
     if rows > ARGMAX_ROWS:
         return 1
-    return max(1, min(ARGMAX_CHUNKS, V // ARGMAX_MIN_CHUNK, -(-NUM_SMS // max(rows, 1))))
+    return max(1, min(ARGMAX_CHUNKS, V // ARGMAX_MIN_CHUNK, -(-num_sms() // max(rows, 1))))
 
 
 def sample(logits: torch.Tensor, temperature=None, uniform=None, keep=None) -> torch.Tensor:

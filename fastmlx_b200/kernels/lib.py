@@ -33,14 +33,10 @@ _SIGNATURES = {
         "fmx_logit_bias": [_P, _L, _I, _P, _P, _P, _I, _P],
     },
     "bf16": {
-        "fmx_skinny_fused": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P, _F, _P, _L, _I, _I, _P, _L, _P, _L, _P],
         "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],
-        "fmx_skinny_gemm": [_P, _L, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _P, _L, _P, _L, _P],
     },
     "tc": {
         "fmx_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
-        "fmx_gemm_stream": [_P, _L, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P, _L, _P, _P],
-        "fmx_mma_rate": [_I, _I, _I, _I, _I, _P, _P],
     },
     "attn": {
         "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
@@ -65,8 +61,11 @@ def load(group: str) -> ctypes.CDLL:
     if group.startswith("attn_hd"):
         lib.fmx_attn_decode_scratch_floats.argtypes = [_I, _I, _I]
         lib.fmx_attn_decode_scratch_floats.restype = c_longlong
+        lib.fmx_attn_decode_plan.argtypes = [_I, _I, _L, _I]
+        lib.fmx_attn_decode_plan.restype = c_int
     lib.fmx_last_error.restype = ctypes.c_char_p
-    for name, args in _SIGNATURES["attn" if group.startswith("attn_hd") else group].items():
+    family = "attn" if group.startswith("attn_hd") else "tc" if group == "tc_expiry" else group
+    for name, args in _SIGNATURES[family].items():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = c_int

@@ -3,8 +3,8 @@ launches), for tuning and for profiler captures on a small case.
 
     python -m fastmlx_b200.kernels.microbench --kernel attn_decode --batch 8 --ctx 8192
     python -m fastmlx_b200.kernels.microbench --kernel attn_prefill --batch 1 --qlen 2048
-    python -m fastmlx_b200.kernels.microbench --kernel skinny_gemm --M 8 --N 2048 --K 8192
-    python -m fastmlx_b200.kernels.microbench --kernel mma_rate
+    python -m fastmlx_b200.kernels.microbench --kernel gemv --M 8 --N 2048 --K 8192
+    python -m fastmlx_b200.kernels.microbench --kernel gemm --M 2048 --N 16384 --K 2048
 """
 from __future__ import annotations
 
@@ -57,7 +57,7 @@ def _attention_inputs(a, qlen):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "skinny_gemm", "gemm", "mma_rate"])
+    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "gemv", "gemm"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192, help="tokens already in the cache")
     ap.add_argument("--qlen", type=int, default=2048, help="tokens per row (attn_prefill)")
@@ -69,30 +69,12 @@ def main(argv=None) -> int:
     ap.add_argument("--M", type=int, default=8)
     ap.add_argument("--N", type=int, default=2048)
     ap.add_argument("--K", type=int, default=8192)
-    ap.add_argument("--ctas", type=int, default=0, help="CTAs of the streaming product (0: one per SM)")
-    ap.add_argument("--ring", type=int, default=0, help="KB of shared-memory ring of the streaming product (0: default)")
-    ap.add_argument("--dual", action="store_true", help="skinny_gemm: the gate/up product with SiLU-mul")
+    ap.add_argument("--dual", action="store_true", help="gemv: the gate/up product with SiLU-mul")
     ap.add_argument("--resident", action="store_true", help="one weight matrix, reused (it may stay in L2)")
     ap.add_argument("--only", default="", help="time only the implementations whose name starts so")
     ap.add_argument("--launches", type=int, default=10, help="kernel launches per graph")
     ap.add_argument("--replays", type=int, default=5)
     a = ap.parse_args(argv)
-    if a.kernel == "mma_rate":
-        # clocks per tcgen05.mma of 128 x N x 16 issued back to back by one thread
-        from .lib import call
-        out = torch.zeros(3, dtype=torch.int64, device="cuda")
-        iters = 2000
-        for n, tm, mn in [(64, 0, 0), (128, 0, 0), (256, 0, 0), (64, 0, 1), (128, 0, 1), (64, 1, 1), (128, 1, 1), (128, 1, 0),
-                          (256, 1, 0)]:
-            per = []
-            for fixed in (1, 0):
-                for _ in range(2):
-                    call("tc", "fmx_mma_rate", n, tm, mn, fixed, iters, out.data_ptr(), torch.cuda.current_stream().cuda_stream)
-                issued, done, expired = out.cpu().tolist()
-                per.append(f"{done / (4 * iters):.1f}" + (" (the wait ran out)" if expired else ""))
-            print(f"mma_rate N={n} A in {'tensor' if tm else 'shared'} memory, B {'MN' if mn else 'K'}-major: "
-                  f"{per[0]} clocks per product back to back, {per[1]} with descriptor arithmetic in between")
-        return 0
     if a.kernel == "attn_decode":
         qkv, kv, ctx, grp = _attention_inputs(a, 1)
         splits = a.splits or k.decode_splits(a.batch, a.nkv, a.ctx + 1, a.hd)
@@ -150,28 +132,20 @@ def main(argv=None) -> int:
             return f
         impls = [("cublas", lambda w: torch.mm(x, w.t()))]
         if a.M <= 16:
-            impls.append((f"skinny splits={a.splits or k.skinny_splits(a.M, a.N, a.K)}",
-                          lambda w: k.skinny_gemm(x, w, None, torch.bfloat16, splits=a.splits or None)))
             impls.append(("gemv 8 features", lambda w: k.gemv(x, w, wide=8, warps=8)))
             impls.append(("gemv 16 features", lambda w: k.gemv(x, w, wide=16, warps=8)))
             impls.append(("gemv 32 features", lambda w: k.gemv(x, w, wide=32, warps=8)))
             impls.append(("gemv 8 features, 16 warps", lambda w: k.gemv(x, w, wide=8, warps=16)))
             impls.append(("gemv 16 features, 16 warps", lambda w: k.gemv(x, w, wide=16, warps=16)))
-        if k.can_stream(x, ws[0]):
-            ctas, stages, _, _ = k.stream_plan(a.M, a.N, a.K, False, a.ctas or None, a.ring * 1024 or None)
-            impls.append((f"stream ctas={ctas} stages={stages}",
-                          lambda w: k.gemm_stream(x, w, ctas=a.ctas or None, ring_bytes=a.ring * 1024 or None)))
         if a.dual:                      # N rows of gate and up in blocks of 128, SiLU-mul in the epilogue
             impls = [(f"gemv gate/up {wd} features", (lambda wd: lambda w: k.gemv(x, w, block=128, wide=wd))(wd))
                      for wd in (8, 16, 32) if a.M <= 16]
             impls.append(("library product, then SiLU-mul", lambda w: k.silu_mul(torch.mm(x, w.t()), 128)))
-            if a.M <= 8:
-                impls.append(("skinny_fused gate/up", lambda w: k.skinny_fused(x, w, block=128)))
         for name, fn in impls:
             if not name.startswith(a.only):
                 continue
             us = _time_graph(rotating(fn), a.launches, a.replays)
-            print(f"skinny_gemm M={a.M} N={a.N} K={a.K} {name}: {us:.1f} us, {a.N * a.K * 2 / us / 1e3:.0f} GB/s of weights")
+            print(f"gemv M={a.M} N={a.N} K={a.K} {name}: {us:.1f} us, {a.N * a.K * 2 / us / 1e3:.0f} GB/s of weights")
         print("status", st.tolist())
     return 0
 

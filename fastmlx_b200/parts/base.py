@@ -120,11 +120,8 @@ class Mixer(Part):
     def forward_in_block(self, delta, residual, norm: "Norm", ctx, cache):
         """What a block calls: (delta, residual) in, (delta', residual') out, where the stream
         is residual + delta (either may be None).  The default normalises and calls `forward`;
-        a part that can fold the norm into its first kernel and the residual sum into its last
-        overrides this and returns (None, stream).  (The skinny product has both folds,
-        `kernels.skinny_fused`; for this architecture's sizes the norm fold costs more than the
-        small norm kernel it saves, since every block has to read whole rows, so the stock
-        parts keep the default.)"""
+        a part whose kernels fold the norm or the residual sum in overrides this and returns
+        (None, stream)."""
         x, residual = norm.forward(delta, residual)
         return self.forward(x, ctx, cache), residual
 

@@ -30,18 +30,13 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx):
         k, w = self.rt.k, self.gate_up.weight
-        if self.block and self.gate_up.bias is None and x.dtype == w.dtype == torch.bfloat16 \
-                and x.shape[0] >= getattr(k, "TC_MIN_ROWS", 1 << 30) and getattr(k, "tc_enabled", lambda: False)():
+        fused = self.block and self.gate_up.bias is None and hasattr(k, "can_tc")
+        if fused and k.can_tc(x, w, None, x.dtype, k.EPI_SILU_MUL):
+            # prompt portions: a 256-wide tile holds 128 gates and their ups, SiLU-mul in the epilogue
             act = k.gemm_tcgen05(x, w, ctx.status if ctx is not None else None, epilogue=k.EPI_SILU_MUL)
-        elif self.block and self.block % 16 == 0 and self.gate_up.bias is None and hasattr(k, "can_gemv") and k.can_gemv(x, w):
+        elif fused and self.block % 16 == 0 and k.can_gemv(x, w):
             # decode steps: a block owns some gate rows and their up rows, SiLU-mul in its epilogue
             act = k.gemv(x, w, block=self.block)
-        elif self.block and getattr(k, "stream_enabled", lambda: False)() and k.can_stream(x, w, self.gate_up.bias, self.block):
-            # few rows: W streamed once through the tensor cores, SiLU-mul in the epilogue
-            act = k.gemm_stream(x, w, block=self.block, status=ctx.status if ctx is not None else None)
-        elif self.block and hasattr(k, "skinny_fused") and k.can_fuse_skinny(x, w, self.gate_up.bias):
-            # decode steps: a block owns 16 gate rows and their 16 up rows, SiLU-mul in its epilogue
-            act = k.skinny_fused(x, w, block=self.block)
         else:
             act = k.silu_mul(self.gate_up.forward(x), self.block or None)
         return self.down.forward(act)

@@ -190,71 +190,6 @@ def test_gemm_tcgen05_epilogues(M, I, K):
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(16, 32), (64, 64), (131, 80), (3072, 2048), (2048, 8192), (50, 8), (320, 192), (17, 1000)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_skinny_gemm(M, N, K, out_dtype):
-    """The weight-streaming product of decode steps: every row count up to 16, widths that are
-    no multiple of the 32-wide k block or of the 16-row tile, with and without a bias."""
-    x, w = rnd(M, K, dtype=torch.bfloat16, seed=11), rnd(N, K, dtype=torch.bfloat16, seed=12, scale=0.05)
-    b = rnd(N, seed=13) if N % 2 else None
-    ref = plain_ops.linear(x, w, b, torch.float64)
-    got = k().skinny_gemm(x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None, out_dtype)
-    close(got, ref, out_dtype, "skinny gemm", scale=ref.abs().max().item() * 8 if out_dtype == torch.float32 else None)
-    # a row's result does not depend on how many rows share the step
-    alone = k().skinny_gemm(x[M - 1:].contiguous().to(DEV), w.to(DEV), b.to(DEV) if b is not None else None, out_dtype)
-    assert torch.equal(alone[0], got[M - 1])
-    # K split over blocks: the same values up to the order of the partial sums, twice in a row
-    # over the same workspace and tickets
-    for splits in (2, 3, 7, -2, -5, -8):                # negative: that many blocks as one cluster
-        for _ in range(2):
-            sp = k().skinny_gemm(x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None, out_dtype, splits=splits)
-            close(sp, ref, out_dtype, f"skinny gemm, {splits} splits",
-                  scale=ref.abs().max().item() * 8 if out_dtype == torch.float32 else None)
-    assert int(k().skinny_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
-
-
-@pytest.mark.parametrize("M", [1, 3, 8])
-@pytest.mark.parametrize("N,K", [(64, 64), (3072, 2048), (2048, 8192), (144, 200), (256, 72)])
-def test_skinny_fused_norm_and_residual(M, N, K):
-    """Norm folded into the product, residual folded into its epilogue (in place), against the
-    unfused chain with its roundings."""
-    x = rnd(M, K, dtype=torch.bfloat16, seed=41, scale=2.0)
-    w = rnd(N, K, dtype=torch.bfloat16, seed=42, scale=0.05)
-    nw = 1 + rnd(K, seed=43, scale=0.1)
-    res = rnd(M, N, dtype=torch.bfloat16, seed=44)
-    normed, _ = plain_ops.add_rmsnorm(x.clone(), None, nw, 1e-5)
-    ref = plain_ops.linear(normed, w, None, torch.float64)
-    for splits in (None, 1, 3):
-        got = k().skinny_fused(x.to(DEV), w.to(DEV), norm=(nw.to(DEV), 1e-5), splits=splits)
-        close(got, ref, torch.bfloat16, "norm prologue", extra=2.0 ** -8 * ref.abs().max().item())
-        got32 = k().skinny_fused(x.to(DEV), w.to(DEV), torch.float32, norm=(nw.to(DEV), 1e-5), splits=splits)
-        close(got32.bfloat16(), ref, torch.bfloat16, "norm prologue, float out", extra=2.0 ** -8 * ref.abs().max().item())
-        stream = res.clone().to(DEV)
-        out = k().skinny_fused(x.to(DEV), w.to(DEV), residual=stream, out=stream, splits=splits)
-        assert out.data_ptr() == stream.data_ptr()
-        want = plain_ops.linear(x, w, None, torch.bfloat16).double() + res.double()
-        close(stream, want, torch.bfloat16, "residual epilogue", extra=2.0 ** -8 * want.abs().max().item())
-    assert int(k().skinny_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
-
-
-@pytest.mark.parametrize("M", [1, 8])
-@pytest.mark.parametrize("I,K,blk", [(128, 64, 128), (8192, 2048, 128), (384, 200, 128), (64, 72, 32)])
-def test_skinny_fused_gate_up(M, I, K, blk):
-    x = rnd(M, K, dtype=torch.bfloat16, seed=51, scale=2.0)
-    wg, wu = rnd(I, K, dtype=torch.bfloat16, seed=52, scale=0.1), rnd(I, K, dtype=torch.bfloat16, seed=53, scale=0.1)
-    w = torch.stack([wg.view(-1, blk, K), wu.view(-1, blk, K)], dim=1).reshape(2 * I, K).contiguous()
-    nw = 1 + rnd(K, seed=54, scale=0.1)
-    normed, _ = plain_ops.add_rmsnorm(x.clone(), None, nw, 1e-6)
-    g = plain_ops.linear(normed, wg, None, torch.bfloat16)
-    u = plain_ops.linear(normed, wu, None, torch.bfloat16)
-    ref = plain_ops.silu_mul(torch.cat([g, u], dim=1))
-    for splits in (None, 1, 2):
-        got = k().skinny_fused(x.to(DEV), w.to(DEV), norm=(nw.to(DEV), 1e-6), block=blk, splits=splits)
-        assert got.shape == (M, I)
-        close(got, ref, torch.bfloat16, "gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
-
-
-@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(16, 32), (64, 64), (131, 80), (3072, 2048), (2048, 8192), (50, 8), (320, 192), (17, 1000)])
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemv(M, N, K, out_dtype):
     """The product with the whole of K in one block: every row count up to 16, widths that are
     no multiple of the 32-wide k block or of the 8-feature tile, bias, residual in place, both
@@ -294,55 +229,6 @@ def test_gemv_gate_up(M, I, K, blk):
         got = k().gemv(x.to(DEV), w.to(DEV), block=blk, wide=wide)
         assert got.shape == (M, I)
         close(got, ref, torch.bfloat16, "gemv gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
-
-
-@pytest.mark.parametrize("M", [1, 7, 8, 16, 17, 33, 64, 100, 128])
-@pytest.mark.parametrize("N,K", [(16, 32), (128, 64), (131, 80), (3072, 2048), (2048, 8192), (50, 8), (320, 192), (1000, 1000)])
-def test_gemm_stream(M, N, K):
-    """The streaming tcgen05 product: every column count, widths that are no multiple of the
-    64-wide k block or of the 128-row tile, with and without a bias, both output types; cut
-    over many, few and one CTA (whole tiles, tiles shared by two and by many CTAs), twice in a
-    row over the same workspace and tickets."""
-    x, w = rnd(M, K, dtype=torch.bfloat16, seed=11), rnd(N, K, dtype=torch.bfloat16, seed=12, scale=0.05)
-    b = rnd(N, seed=13) if N % 2 else None
-    ref = plain_ops.linear(x, w, b, torch.float64)
-    st = torch.zeros(4, dtype=torch.int32, device=DEV)
-    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV) if b is not None else None
-    first = None
-    for out_dtype in (torch.bfloat16, torch.float32):
-        scale = ref.abs().max().item() * 8 if out_dtype == torch.float32 else None
-        for ctas in (None, 1, 2, 3, 37):
-            for ring in (None, 40 * 1024):
-                for _ in range(2):
-                    got = k().gemm_stream(xd, wd, bd, out_dtype, ctas=ctas, ring_bytes=ring, status=st)
-                    close(got, ref, out_dtype, f"stream gemm, {ctas} CTAs", scale=scale)
-        if first is None:
-            first = got
-    # a row's result does not depend on how many rows share the step
-    alone = k().gemm_stream(xd[M - 1:].contiguous(), wd, bd, torch.float32, ctas=37, status=st)
-    assert torch.equal(alone[0], got[M - 1])
-    assert st.tolist()[0] == 0
-    assert int(k().stream_workspace(torch.device(DEV, torch.cuda.current_device()))[1].abs().sum()) == 0
-
-
-@pytest.mark.parametrize("M", [1, 8, 40])
-@pytest.mark.parametrize("I,K", [(128, 64), (8192, 2048), (384, 200), (1280, 72)])
-def test_gemm_stream_gate_up(M, I, K):
-    x = rnd(M, K, dtype=torch.bfloat16, seed=51, scale=2.0)
-    wg, wu = rnd(I, K, dtype=torch.bfloat16, seed=52, scale=0.1), rnd(I, K, dtype=torch.bfloat16, seed=53, scale=0.1)
-    w = torch.stack([wg.view(-1, 128, K), wu.view(-1, 128, K)], dim=1).reshape(2 * I, K).contiguous()
-    g = plain_ops.linear(x, wg, None, torch.bfloat16)
-    u = plain_ops.linear(x, wu, None, torch.bfloat16)
-    ref = plain_ops.silu_mul(torch.cat([g, u], dim=1))
-    st = torch.zeros(4, dtype=torch.int32, device=DEV)
-    for ctas in (None, 1, 5):
-        for _ in range(2):
-            got = k().gemm_stream(x.to(DEV), w.to(DEV), block=128, ctas=ctas, status=st)
-            assert got.shape == (M, I)
-            close(got, ref, torch.bfloat16, "streamed gate/up with SiLU-mul", extra=2.0 ** -7 * ref.abs().max().item())
-    assert st.tolist()[0] == 0
-    with pytest.raises(k().KernelError):
-        k().gemm_stream(x.to(DEV), w.to(DEV), block=64)
 
 
 @pytest.mark.parametrize("ta,tw,tc", [(torch.bfloat16, torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32, torch.float32),
@@ -751,3 +637,28 @@ def test_sampling_keep_mask():
     got = k().sample(logits.to(DEV), temps.to(DEV), u.to(DEV), keep.to(DEV)).cpu()
     assert ((got >= 100) & (got < 110)).all()
     assert got.tolist() == plain_ops.sample(logits, temps, u, keep).tolist()
+
+
+# ----------------------------------------------------------------------------- a wait that runs out
+def test_a_wait_that_runs_out_leaves_a_code_and_a_usable_stream():
+    """Every wait on a barrier in the tensor-core kernels is bounded.  The library `tc_expiry` is
+    the product kernel's source built with a limit of 100,000 clocks and a producer that never
+    brings its last block: the issuing thread and the epilogue warps wait for what never comes,
+    give up, leave code 5 in the status word, wait for the products already issued, free their
+    tensor memory and return.  Nothing faults and nothing is in flight; the next ordinary
+    product on the same stream is right."""
+    from fastmlx_b200.kernels.lib import call
+    M, N, K = 256, 512, 512
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1).to(DEV), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.1).to(DEV)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    st = status()
+    call("tc_expiry", "fmx_gemm_tcgen05", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+         None, 0, M, N, K, 256, 0, 0, st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()                               # returns: the kernel ended by itself
+    code, role, block = st.tolist()[:3]
+    assert code == 5 and role in (2, 3), (code, role, block)
+    st2 = status()
+    got = k().gemm_tcgen05(x, w, st2, bn=256)
+    torch.cuda.synchronize()
+    assert st2.tolist()[0] == 0
+    close(got, plain_ops.linear(x.cpu(), w.cpu(), None, torch.bfloat16), torch.bfloat16, "the product after an expired wait")

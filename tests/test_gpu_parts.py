@@ -448,3 +448,183 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):
             assert o.output_token_ids == seq[len(p):]
     finally:
         registry.unregister(["toy_routed"])
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state, captured in graphs
+def make_toy_on_device():
+    """The decaying sum again, with its decode step written as dense tensor operations over
+    the step's device arrays (no loop over rows on the host), so that a decode step of the
+    model may be captured in a CUDA graph.  Rows whose slot is -1 (the padding rows of a
+    captured step) match no slot and touch no state."""
+    from fastmlx_b200.parts import (Embedding, GQAAttention, Linear, LMHead, Mixer, Model, PreNormBlock, RMSNorm,
+                                    RotaryEmbedding, StateSpec, SwiGLU)
+
+    class DecayingSumOnDevice(Mixer):
+        supports_cuda_graph = True
+
+        def __init__(self, width, decay, name):
+            self.width, self.decay = width, decay
+            self.proj = Linear(width, [(name + ".proj", width)])
+
+        def children(self):
+            return (self.proj,)
+
+        def state_spec(self):
+            return StateSpec((self.width,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            u = self.proj.forward(x).float()
+            if ctx.all_decode:
+                state = cache.state                                         # [slots, width]
+                hit = (ctx.row_slot[:, None] == torch.arange(state.shape[0], device=u.device)[None, :]).float()   # [rows, slots]
+                s_new = self.decay * (hit @ state) + u                       # a padding row: 0 + u, written nowhere
+                state.mul_(1.0 - hit.sum(0)[:, None]).add_(hit.t() @ s_new)
+                return s_new.to(x.dtype)
+            out = torch.empty_like(u)
+            for r in range(ctx.R):
+                a, b, slot = ctx.h_row_start[r], ctx.h_row_start[r + 1], ctx.h_row_slot[r]
+                s = cache.state[slot]
+                for t in range(a, b):
+                    s = self.decay * s + u[t]
+                    out[t] = s
+                cache.state[slot] = s
+            return out.to(x.dtype)
+
+    ToyCfg, _ = make_toy()
+
+    def build(cfg):
+        d = cfg.width
+        blocks = [
+            PreNormBlock(DecayingSumOnDevice(d, cfg.decay, "l0.mix"), SwiGLU(d, 56, "l0.mlp"), RMSNorm(d, 1e-5, "l0.n1"),
+                         RMSNorm(d, 1e-5, "l0.n2")),
+            PreNormBlock(GQAAttention(d, 2, 1, 16, RotaryEmbedding(16, 100.0), "l1.attn"), SwiGLU(d, 56, "l1.mlp"),
+                         RMSNorm(d, 1e-5, "l1.n1"), RMSNorm(d, 1e-5, "l1.n2")),
+        ]
+        return Model(Embedding(cfg.vocab_size, d, "emb"), blocks, RMSNorm(d, 1e-5, "norm"),
+                     LMHead(cfg.vocab_size, d, "head"), vocab_size=cfg.vocab_size, max_positions=512)
+
+    return ToyCfg, build
+
+
+def test_a_mixer_with_state_runs_in_captured_decode_steps(tmp_path):
+    """Three live requests in a graph of four rows, one step ahead of the host: the padding row
+    must touch no request's state, and the run that warms a graph up before its capture must
+    not count as a step.  Token-equal to the plain statement."""
+    from fastmlx_b200 import Engine, SamplingParams, registry, write_random_model
+    ToyCfg, build = make_toy_on_device()
+    registry.register(["toy_decay_dev"], ToyCfg.from_dict, build, replace=True)
+    try:
+        config = {"model_type": "toy_decay_dev", "vocab_size": 77, "width": 40, "decay": 0.9}
+        d = write_random_model(str(tmp_path / "toydev"), config, seed=4)
+        W = tiny.load_plain_weights(d)
+        prompts = [tiny.rand_tokens(n, 77, 30 + n) for n in (19, 3, 27)]
+        eng = Engine(d, dtype="float32", block_size=8, max_cache_tokens=1024, max_concurrent_requests=4)
+        assert eng.model.graph_safe and eng.manager.has_state
+        outs = eng.generate(prompts, [SamplingParams(max_tokens=m, temperature=0.0) for m in (14, 9, 20)])
+        assert (4, 16) in eng.step_fn.graphs and eng.stats()["graph_replays"] > 10
+        for p, o in zip(prompts, outs):
+            seq = list(p)
+            for _ in range(len(o.output_token_ids)):
+                seq.append(int(torch.argmax(plain_toy(W, seq, 0.9)[-1])))
+            assert o.output_token_ids == seq[len(p):]
+        # a failed step leaves the state as it was: a token outside the vocabulary in the second step
+        from fastmlx_b200.engine.replay import Replayer
+        from fastmlx_b200.engine.step import StepError
+        rp = Replayer(d, "float32", 256, page_size=8)
+        toks = prompts[0]
+        rp.step({"step": 0, "entries": [{"id": "a", "tokens": toks[:10], "want": []}], "end": []})
+        before = rp.manager.entries[0].state.clone()
+        with pytest.raises(StepError):
+            rp.step({"step": 1, "entries": [{"id": "a", "tokens": [5, 99999, 7], "want": []}], "end": []})
+        assert torch.equal(rp.manager.entries[0].state, before) and rp.manager.requests["a"].length == 10
+        got = rp.step({"step": 2, "entries": [{"id": "a", "tokens": toks[10:], "want": [len(toks) - 11]}], "end": ["a"]})
+        ref = plain_toy(W, toks, 0.9)[-1]
+        assert (torch.from_numpy(got[0]).double() - ref).abs().max().item() / ref.abs().max().item() < 1e-5
+    finally:
+        registry.unregister(["toy_decay_dev"])
+
+
+# ----------------------------------------------------------------------------- a window through the engine's loop
+def make_windowed():
+    """Two attention layers, the first with a window of 9 keys: two cache groups with pools of
+    their own, the first of which gives pages back while a request runs."""
+    from fastmlx_b200.parts import Embedding, GQAAttention, LMHead, Model, PreNormBlock, RMSNorm, RotaryEmbedding, SwiGLU
+
+    @dataclass(frozen=True)
+    class WinCfg:
+        vocab_size: int
+        width: int
+        window: int
+        eos_token_id: int = -1
+
+        @staticmethod
+        def from_dict(d):
+            return WinCfg(int(d["vocab_size"]), int(d["width"]), int(d["window"]))
+
+    def build(cfg):
+        d = cfg.width
+        blocks = [PreNormBlock(GQAAttention(d, 4, 2, 16, RotaryEmbedding(16, 100.0), f"l{i}.attn", window=w),
+                               SwiGLU(d, 64, f"l{i}.mlp"), RMSNorm(d, 1e-5, f"l{i}.n1"), RMSNorm(d, 1e-5, f"l{i}.n2"))
+                  for i, w in enumerate((cfg.window, 0))]
+        return Model(Embedding(cfg.vocab_size, d, "emb"), blocks, RMSNorm(d, 1e-5, "norm"),
+                     LMHead(cfg.vocab_size, d, "head"), vocab_size=cfg.vocab_size, max_positions=512)
+
+    return WinCfg, build
+
+
+def plain_windowed(W, toks, window, round_to=None):
+    T = len(toks)
+    cfg = {"num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "attention_bias": False, "rope_traditional": False}
+    inv = pl.rope_inv_freq(16, 100.0, None)
+    h = pl.embedding(torch.tensor(toks), W["emb.weight"])
+    for i, w in enumerate((window, None)):
+        Wp = {k.replace(f"l{i}.attn.", "self_attn."): v for k, v in W.items() if k.startswith(f"l{i}.attn.")}
+        x = pl._rnd(pl.rms_norm(h, W[f"l{i}.n1.weight"], 1e-5), round_to)
+        h = h + pl.attention_block(x, Wp, "", cfg, torch.arange(T), inv, round_to, w)
+        y = pl._rnd(pl.rms_norm(h, W[f"l{i}.n2.weight"], 1e-5), round_to)
+        h = h + pl.swiglu(y, W[f"l{i}.mlp.gate_proj.weight"], W[f"l{i}.mlp.up_proj.weight"], W[f"l{i}.mlp.down_proj.weight"],
+                          round_to=round_to)
+    return pl.linear(pl._rnd(pl.rms_norm(h, W["norm.weight"], 1e-5), round_to), W["head.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_window_gives_pages_back_inside_the_engine_loop(tmp_path, dtype):
+    """Prompts in portions, then more than three windows of decode steps under graphs and one
+    step ahead, in a tight pool: the windowed group's pages go back at every commit, the graph's
+    block tables come from the mirror with -1 holes, and the step launched ahead builds its
+    tables after the earlier step's pages were returned.  Tokens against the plain model."""
+    from fastmlx_b200 import Engine, SamplingParams, registry, write_random_model
+    WinCfg, build = make_windowed()
+    registry.register(["toy_window"], WinCfg.from_dict, build, replace=True)
+    try:
+        config = {"model_type": "toy_window", "vocab_size": 83, "width": 48, "window": 9}
+        d = write_random_model(str(tmp_path / "win"), config, seed=6)
+        W = tiny.load_plain_weights(d)
+        prompts = [tiny.rand_tokens(n, 83, 50 + n) for n in (20, 35, 11)]
+        eng = Engine(d, dtype=dtype, block_size=8, initial_cache_blocks=40, max_concurrent_requests=4, prefill_chunk=7,
+                     max_num_batched_tokens=16)
+        groups = eng.manager.groups
+        assert [g.spec.window for g in groups] == [9, 0]
+        assert groups[0].pool.num_pages < groups[1].pool.num_pages            # the window's pool is its own size
+        ids = [eng.submit(p, SamplingParams(max_tokens=32, temperature=0.0)) for p in prompts]
+        final, most = {}, 0
+        while eng.has_unfinished():
+            for o in eng.step():
+                if o.finished:
+                    final[o.request_id] = o
+            eng.manager.check()
+            most = max(most, groups[0].pool.used_pages)
+        # per request the window holds at most 9 + 7 keys: which lie on three pages at most
+        assert most <= 3 * 3 and eng.stats()["pages_used"] == 0 and eng.stats()["graph_replays"] > 20
+        rt, slack = (torch.bfloat16, 2e-2) if dtype == "bfloat16" else (None, 1e-5)
+        for p, rid in zip(prompts, ids):
+            got = final[rid].output_token_ids
+            assert len(got) == 32
+            logits = plain_windowed(W, list(p) + got, 9, rt)[len(p) - 1: -1]
+            for i, tok in enumerate(got):
+                best = int(torch.argmax(logits[i]))
+                if best != tok:
+                    gap = float(logits[i][best] - logits[i][tok]) / float(logits[i].abs().max())
+                    assert gap < slack, (i, tok, best, gap)
+    finally:
+        registry.unregister(["toy_window"])
