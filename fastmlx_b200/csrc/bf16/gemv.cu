@@ -141,6 +141,22 @@ void launch(const void* x, long long ldx, const void* W, long long ldw, const fl
 }
 }  // namespace
 
+// Output features per block when the caller leaves the choice open: 32 once that still gives
+// every SM a block, else 16 (wider blocks re-read x less and keep more of W in flight per block,
+// but too few of them leave SMs idle); halved until it tiles the gate/up blocks.
+FMX_EXPORT int fmx_gemv_plan_width(int n_out, int blk, int sms) {
+  if (sms <= 0) sms = fmx_num_sms();
+  int wide = n_out / 32 >= sms ? 32 : 16;
+  while (blk > 0 && blk % wide) wide /= 2;
+  return wide;
+}
+// Warps per block: fewer blocks than SMs over a long K keep enough bytes in flight only with 16.
+FMX_EXPORT int fmx_gemv_plan_warps(int n_out, int K, int wide, int sms) {
+  if (sms <= 0) sms = fmx_num_sms();
+  return (wide < 32 && (n_out + wide - 1) / wide < sms && K >= 4096) ? 16 : 8;
+}
+
+
 // x [M <= 16, K] and W [N, K] bfloat16, rows 16-byte aligned; out [M, N] bfloat16 (out_dtype 1)
 // or float (0); bias float[N] or null; residual bfloat16 [M, n_out] or null (may be `out`).
 // blk > 0: W's rows alternate in blocks of blk gate rows and blk up rows, out is [M, N/2] =
@@ -157,6 +173,9 @@ FMX_EXPORT int fmx_gemv(const void* x, long long ldx, const void* W, long long l
     return fmx_fail("fmx_gemv: gate/up blocks of %d do not tile %d rows", blk, N);
   if (blk > 0 && out_dtype != FMX_BF16) return fmx_fail("fmx_gemv: the SiLU-mul epilogue writes bfloat16");
   const bool hi = M > 8;
+  const int n_out = blk > 0 ? N / 2 : N;
+  if (wide == 0) wide = fmx_gemv_plan_width(n_out, blk, 0);
+  if (warps == 0) warps = fmx_gemv_plan_warps(n_out, K, wide, 0);
   if (warps != 8 && warps != 16) return fmx_fail("fmx_gemv: 8 or 16 warps per block, not %d", warps);
   if (warps == 16 && wide == 32) return fmx_fail("fmx_gemv: 32 features per block go with 8 warps");
   if (wide != 8 && wide != 16 && wide != 32) return fmx_fail("fmx_gemv: 8, 16 or 32 features per block, not %d", wide);

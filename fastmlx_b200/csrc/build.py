@@ -26,6 +26,8 @@ GROUPS = {
     "bf16": "bf16",
     "attn": "attn",
     "tc": "tc",
+    # host code: the native step executor (no kernel of its own)
+    "host": "host",
     # the tensor-core product built for one test: a wait limit of 100,000 clocks and a producer that
     # leaves out its last block, so that the path a wait takes when it runs out is executed
     "tc_expiry": "tc",

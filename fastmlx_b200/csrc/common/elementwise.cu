@@ -298,3 +298,35 @@ FMX_EXPORT int fmx_silu_mul(const void* gu, void* out, int rows, int I, int blk,
   FMX_LAUNCH_CHECK();
   return 0;
 }
+
+// out[r, :] = vec for every row: the bias laid under a library product that adds to what it finds
+// (product and bias are then summed in 32-bit and rounded once).
+template <typename T>
+__global__ void fill_rows_kernel(const float* vec, T* out, long long rows, int cols, long long ldo) {
+  pdl_wait();
+  pdl_trigger();
+  const long long n = rows * cols;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / cols;
+    const int c = (int)(idx - r * cols);
+    out[r * ldo + c] = from_f<T>(vec[c]);
+  }
+}
+
+FMX_EXPORT int fmx_fill_rows(const float* vec, void* out, int rows, int cols, long long ldo, int dtype,
+                             cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  if (rows < 0 || cols < 0 || ldo < cols) return fmx_fail("fmx_fill_rows: bad sizes rows=%d cols=%d ld=%lld", rows, cols, ldo);
+  const long long n = (long long)rows * cols, cap = (long long)fmx_num_sms() * 16;
+  const int block = 256;
+  const int grid = (int)((n + block - 1) / block < cap ? (n + block - 1) / block : cap);
+  if (dtype == FMX_F32)
+    fmx_launch(fill_rows_kernel<float>, dim3(grid), dim3(block), 0, stream, vec, (float*)out, (long long)rows, cols, ldo);
+  else if (dtype == FMX_BF16)
+    fmx_launch(fill_rows_kernel<bf16>, dim3(grid), dim3(block), 0, stream, vec, (bf16*)out, (long long)rows, cols, ldo);
+  else
+    return fmx_fail("fmx_fill_rows: unknown dtype %d", dtype);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}

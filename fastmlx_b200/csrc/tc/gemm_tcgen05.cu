@@ -268,9 +268,39 @@ int run(const void* A, long long lda, const void* W, long long ldw, void* C, lon
 }
 }  // namespace
 
+// The tile width (of 128, 192, 256) whose tiles fill the SMs' rounds best; wider wins ties.
+FMX_EXPORT int fmx_gemm_tcgen05_plan_width(int M, int N, int sms) {
+  if (sms <= 0) sms = fmx_num_sms();
+  int best = 256;
+  double best_eff = -1.0;
+  const int widths[3] = {256, 192, 128};
+  for (int bn : widths) {
+    const long long tiles = (long long)((M + 127) / 128) * ((N + bn - 1) / bn);
+    const long long rounds = (tiles + sms - 1) / sms;
+    const double eff = (double)tiles / (double)(rounds * sms) * ((double)N / (double)(((N + bn - 1) / bn) * bn)) *
+                       (bn == 128 ? 0.8 : 1.0);
+    if (eff > best_eff + 1e-9) { best = bn; best_eff = eff; }
+  }
+  return best;
+}
+
+// Does this product fill the GPU here?  The kernel gives each CTA whole tiles and walks K serially
+// within a tile.  With fewer tiles than about a round of the SMs (short prompts against the
+// narrower matrices) most SMs idle behind that walk, and the library's product, which splits K, is
+// two to three times faster (512 x 2048 x 8192: 41 us against 17); with full rounds the two are
+// within a tenth.  The same holds when the last round of tiles is mostly empty (192 tiles: two
+// rounds for the work of 1.3; 2048 x 3072 x 2048 takes 28.9 us here against 19.8 in the library).
+FMX_EXPORT int fmx_gemm_tcgen05_plan_fills(int M, int N, int sms) {
+  if (sms <= 0) sms = fmx_num_sms();
+  const long long tiles = (long long)((M + 127) / 128) * ((N + 255) / 256);
+  const long long rounds = (tiles + sms - 1) / sms;
+  return (double)tiles >= 0.8 * sms && (double)tiles >= 0.75 * (double)(rounds * sms) ? 1 : 0;
+}
+
 // A [M, K], W [N, K] bfloat16 with K-contiguous rows whose starts are 16-byte aligned; C
 // bfloat16 [M, N] (EPI 0, 2) or [M, N/2] (EPI 1, W's rows in blocks of bn/2 gate rows then
-// bn/2 up rows).  bn is 128, 192 (plain only) or 256.  status: the engine's status word (a wait that expires
+// bn/2 up rows).  bn is 128, 192 (plain only) or 256, or 0 for the width that fills the SMs best
+// (256 with the SiLU-mul epilogue).  status: the engine's status word (a wait that expires
 // leaves FMX_WAIT_EXPIRED there).
 FMX_EXPORT int fmx_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
                                 const void* residual, long long ldr, int M, int N, int K, int bn, int epilogue,
@@ -279,6 +309,7 @@ FMX_EXPORT int fmx_gemm_tcgen05(const void* A, long long lda, const void* W, lon
   if (M < 0 || N < 0 || K <= 0) return fmx_fail("fmx_gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return fmx_fail("fmx_gemm_tcgen05: rows must start on 16-byte boundaries (K=%d lda=%lld ldw=%lld)", K, lda, ldw);
+  if (bn == 0) bn = epilogue == EPI_SILU_MUL ? 256 : fmx_gemm_tcgen05_plan_width(M, N, sms);
   if (epilogue == EPI_SILU_MUL && N % bn) return fmx_fail("fmx_gemm_tcgen05: gate/up blocks need N a multiple of %d", bn);
   if (epilogue == EPI_RESIDUAL && residual == nullptr) return fmx_fail("fmx_gemm_tcgen05: the residual epilogue needs a residual");
   if (sms <= 0) sms = fmx_num_sms();

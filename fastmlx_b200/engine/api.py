@@ -37,6 +37,7 @@ class EngineConfig:
     seed: int = 0
     cuda_graphs: bool = True
     lookahead: bool = True                    # run one decode step ahead of the host
+    native_executor: bool = True              # a step's host work in compiled code, where the model's parts allow it
     device: str = "cuda"
 
 
@@ -87,7 +88,8 @@ class Engine:
         self.manager = CacheManager(needs, page_size=ec.block_size, num_pages=per_group or max(1, pages),
                                     max_requests=ec.max_concurrent_requests, dtype=self.rt.dtype,
                                     device=self.rt.device)
-        self.step_fn = StepFunction(self.model, self.manager, self.rt, cuda_graphs=ec.cuda_graphs)
+        self.step_fn = StepFunction(self.model, self.manager, self.rt, cuda_graphs=ec.cuda_graphs,
+                                    native=ec.native_executor)
         self.scheduler = Scheduler(self.manager, SchedulerConfig(ec.max_concurrent_requests,
                                                                  ec.max_num_batched_tokens, ec.prefill_chunk),
                                    eos_token_ids=self.model.eos_token_ids, max_positions=self.model.max_positions)
@@ -288,4 +290,5 @@ class Engine:
         g = self.manager.groups
         return dict(self.counters, waiting=len(self.scheduler.waiting), running=len(self.scheduler.running),
                     pages_total=sum(x.pool.num_pages for x in g), pages_used=sum(x.pool.used_pages for x in g),
-                    model_steps=self.step_fn.steps, graph_replays=self.step_fn.graph_replays)
+                    model_steps=self.step_fn.steps, graph_replays=self.step_fn.graph_replays,
+                    native_executor=self.step_fn.native is not None)

@@ -36,13 +36,13 @@ def pool_pages(max_tokens: int, page_size: int) -> int:
 
 class Replayer:
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, device="cuda",
-                 kernels=None, max_live: int = MAX_LIVE):
+                 kernels=None, max_live: int = MAX_LIVE, native: bool = True):
         self.cfg, self.model, self.rt = load_model(model_dir, dtype, device, kernels)
         self.manager = CacheManager(self.model.cache_needs(), page_size=page_size,
                                     num_pages=pool_pages(max_tokens, page_size), max_requests=max_live,
                                     dtype=self.rt.dtype, device=self.rt.device)
         # replay feeds what the trace says: positions past max_position_embeddings are the trace's business
-        self.step_fn = StepFunction(self.model, self.manager, self.rt, position_limit=False)
+        self.step_fn = StepFunction(self.model, self.manager, self.rt, position_limit=False, native=native)
 
     def step(self, record: dict):
         """Run one trace record; -> float32 numpy [wanted, vocab] or None."""

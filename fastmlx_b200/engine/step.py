@@ -55,7 +55,7 @@ class _DecodeGraph:
         side = torch.cuda.Stream(device=rt.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            fn.model.forward(ctx)
+            fn.forward_context(ctx)
         torch.cuda.current_stream().wait_stream(side)
         if saved is not None:
             manager.restore_state(saved)
@@ -64,7 +64,7 @@ class _DecodeGraph:
         count = getattr(rt.k, "launch_count", lambda: 0)
         before = count()
         with torch.cuda.graph(self.graph):
-            self.logits = fn.model.forward(ctx)
+            self.logits = fn.forward_context(ctx)
         self.kernel_launches = count() - before        # launches of this package's kernels per replay
         self.ctx = ctx
 
@@ -87,9 +87,12 @@ class _DecodeGraph:
 
 class StepFunction:
     def __init__(self, model, manager: CacheManager, rt, cuda_graphs: bool = False, max_graph_rows: int = 256,
-                 position_limit: bool = True):
+                 position_limit: bool = True, native: bool = True):
         """position_limit: refuse a step that would take a request past the model's
-        max_position_embeddings (the serving policy); replay turns it off and runs what it is given."""
+        max_position_embeddings (the serving policy); replay turns it off and runs what it is given.
+        native: hand the step's host work (layout, choice of kernels, launches) to the compiled
+        executor where every part of the model can describe itself to it; else, and for models
+        with parts written in Python, `Model.forward` runs."""
         self.model, self.manager, self.rt = model, manager, rt
         self.position_limit = bool(position_limit)
         self.cuda_graphs = bool(cuda_graphs) and rt.device.type == "cuda" and bool(getattr(model, "graph_safe", False))
@@ -104,6 +107,10 @@ class StepFunction:
         self.steps = 0
         self.tokens_run = 0
         self.last_ctx: StepContext | None = None
+        self.native = None
+        if native and rt.device.type == "cuda" and getattr(rt.k, "__name__", "") == "fastmlx_b200.kernels":
+            from .native import build_program
+            self.native = build_program(model, manager, rt, self.status, max_graph_rows)
         if self.cuda_graphs:
             # workspaces whose addresses the graphs will hold are made before any capture
             for name in ("attention_scratch", "attention_tickets", "argmax_workspace"):
@@ -185,8 +192,16 @@ class StepFunction:
             if not picks:
                 return logits[:0], ctx
             return logits[torch.as_tensor(picks, device=logits.device)], ctx
+        if self.native is not None:
+            return self.native.step(entries)
         ctx = build_context(entries, self.manager, self.rt.device, self.status)
         return self.model.forward(ctx), ctx
+
+    def forward_context(self, ctx: StepContext) -> torch.Tensor:
+        """The model over a step that is laid out already (the captured decode steps)."""
+        if self.native is not None:
+            return self.native.forward_context(ctx)
+        return self.model.forward(ctx)
 
     def check_status(self) -> None:
         """Kernels never trap on a bad index: they skip the access and leave a code."""

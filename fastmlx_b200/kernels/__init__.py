@@ -177,16 +177,6 @@ def can_gemv(x, w) -> bool:
     return _bf16_operands(x, w) and x.shape[0] <= GEMV_MAX_ROWS
 
 
-def gemv_width(n_out: int, block: int = 0, device=None) -> int:
-    """Output features per block: 32 once that still gives every SM a block, else 16 (measured:
-    wider blocks re-read x less and keep more of W in flight per block, but too few of them
-    leave SMs idle)."""
-    wide = 32 if n_out // 32 >= num_sms(device) else 16
-    while block and block % wide:
-        wide //= 2
-    return wide
-
-
 def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 0, out=None, wide=None, warps=None):
     """x[M <= 16, K] @ w[N, K]^T, one block per `wide` (8, 16, 32) output features and the whole of K:
     nothing is summed across blocks.  residual [M, n_out] is added to the product (out may be
@@ -197,38 +187,24 @@ def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 
     n_out = N // 2 if block else N
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-    if wide is None:
-        wide = gemv_width(n_out, block, x.device)
-    if warps is None:
-        # fewer blocks than SMs over a long K: twice the warps keep enough bytes in flight
-        warps = 16 if wide < 32 and -(-n_out // wide) < num_sms(x.device) and K >= 4096 else 8
+    # wide / warps left open: the library plans them (`fmx_gemv_plan_width`, `fmx_gemv_plan_warps`)
     call("bf16", "fmx_gemv", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), _ptr(residual),
          residual.stride(0) if residual is not None else 0, out.data_ptr(), out.stride(0), M, N, K, _dt(out), int(block),
-         int(wide), int(warps), _stream())
+         int(wide or 0), int(warps or 0), _stream())
     return out
 
 
 def tile_width(M: int, N: int, sms: int = 148) -> int:
-    """The tile width (of 128, 192, 256) whose tiles fill the SMs' rounds best; wider wins ties."""
-    best, best_eff = 256, -1.0
-    for bn in (256, 192, 128):
-        tiles = -(-M // 128) * -(-N // bn)
-        eff = tiles / (-(-tiles // sms) * sms) * (N / (-(-N // bn) * bn)) * (0.8 if bn == 128 else 1.0)
-        if eff > best_eff + 1e-9:
-            best, best_eff = bn, eff
-    return best
+    """The tile width (of 128, 192, 256) whose tiles fill the SMs' rounds best, as the
+    tensor-core library plans it (`fmx_gemm_tcgen05_plan_width`)."""
+    return int(load("tc").fmx_gemm_tcgen05_plan_width(int(M), int(N), int(sms)))
 
 
 def tc_fills_the_gpu(M: int, N: int, sms: int = 148) -> bool:
-    """The tensor-memory kernel gives each CTA whole tiles and walks K serially within a tile.
-    With fewer tiles than about a round of the SMs (short prompts against the narrower matrices)
-    most SMs idle behind that walk, and the library's product, which splits K, is two to three
-    times faster (512 x 2048 x 8192: 41 us against 17); with full rounds the two are within a tenth."""
-    tiles = -(-M // 128) * -(-N // 256)
-    rounds = -(-tiles // sms)
-    # ... and the same when the last round of tiles is mostly empty (192 tiles: two rounds for the
-    # work of 1.3; 2048 x 3072 x 2048 takes 28.9 us here against 19.8 in the library)
-    return tiles >= 0.8 * sms and tiles >= 0.75 * rounds * sms
+    """Does a product of these sizes fill the GPU on the tensor-memory kernel (else the
+    library's product, which splits K, is the faster one)?  The library's own plan
+    (`fmx_gemm_tcgen05_plan_fills`)."""
+    return bool(load("tc").fmx_gemm_tcgen05_plan_fills(int(M), int(N), int(sms)))
 
 
 def can_tc(x, w, bias=None, out_dtype=torch.bfloat16, epilogue: int = EPI_PLAIN) -> bool:
@@ -246,11 +222,9 @@ def gemm_tcgen05(x, w, status=None, epilogue: int = EPI_PLAIN, residual=None, bn
     M, K = x.shape
     N = w.shape[0]
     sms = num_sms(x.device)
-    if bn is None:
-        bn = 2 * GATE_UP_BLOCK if epilogue == EPI_SILU_MUL else tile_width(M, N, sms)
     out = torch.empty((M, N // 2 if epilogue == EPI_SILU_MUL else N), dtype=torch.bfloat16, device=x.device)
     call("tc", "fmx_gemm_tcgen05", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-         _ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, bn, epilogue, sms,
+         _ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K, int(bn or 0), epilogue, sms,
          _ptr(status if status is not None else _status_word(x.device)), _stream())
     return out
 

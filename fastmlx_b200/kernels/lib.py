@@ -63,9 +63,15 @@ def load(group: str) -> ctypes.CDLL:
         lib.fmx_attn_decode_scratch_floats.restype = c_longlong
         lib.fmx_attn_decode_plan.argtypes = [_I, _I, _L, _I]
         lib.fmx_attn_decode_plan.restype = c_int
+    if group == "bf16":
+        lib.fmx_gemv_plan_width.argtypes = [_I, _I, _I]
+        lib.fmx_gemv_plan_warps.argtypes = [_I, _I, _I, _I]
+    if group in ("tc", "tc_expiry"):
+        lib.fmx_gemm_tcgen05_plan_width.argtypes = [_I, _I, _I]
+        lib.fmx_gemm_tcgen05_plan_fills.argtypes = [_I, _I, _I]
     lib.fmx_last_error.restype = ctypes.c_char_p
     family = "attn" if group.startswith("attn_hd") else "tc" if group == "tc_expiry" else group
-    for name, args in _SIGNATURES[family].items():
+    for name, args in _SIGNATURES.get(family, {}).items():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = c_int

@@ -62,3 +62,31 @@ class GQAAttention(Mixer):
         self.pos.apply_and_store(qkv, ctx, cache, self.nh, 0 if self.share_kv else self.nkv, self.hd)
         return self.rt.k.paged_attention(qkv, cache.kv, ctx, ctx.groups[cache.group],
                                          self.nh, self.nkv, self.hd, self.scale, self.window)
+
+    def emit(self, b, x, pos):
+        from ..engine.native import BF16, NotNative, OP_ATTENTION, _fn
+        from ..kernels import lib as klib
+        cache = b.manager.entries[pos]
+        if cache.kv is None:
+            raise NotNative("an attention layer without pages")
+        inv_freq, rot, trad = self.pos.native_args()
+        qkv = self.qkv.emit(b, x)
+        out = b.reg(self.nh * self.hd)
+        kv = cache.kv
+        num_pages, page_size = kv.shape[0], kv.shape[3]
+        fns = {}
+        tc_ok = 0
+        if b.act == BF16 and kv.dtype == self.rt.dtype and self.hd % 16 == 0 and self.hd <= 256:
+            lib = klib.load(f"attn_hd{self.hd}")
+            fns = dict(fn_attn_decode=_fn(lib, "fmx_attn_decode"), fn_attn_prefill=_fn(lib, "fmx_attn_prefill"),
+                       fn_attn_prefill_tc=_fn(lib, "fmx_attn_prefill_tc"), fn_attn_plan=_fn(lib, "fmx_attn_decode_plan"))
+            tc_ok = int(bool(lib.fmx_attn_prefill_tc_available())
+                        and self.rt.k.tc_attention_ok(self.nh, self.nkv, self.hd, page_size, self.window))
+        b.op(OP_ATTENTION, in0=qkv, out0=out, vec=b.ptr(inv_freq), nh=self.nh, nkv=self.nkv, hd=self.hd, window=self.window,
+             rot=int(rot), trad=int(bool(trad)), store=int(bool(cache.writable and not self.share_kv)),
+             share_kv=int(self.share_kv), group=cache.group, kv=b.ptr(kv), page_size=page_size, num_pages=num_pages,
+             scale=self.scale, tc_attention_ok=tc_ok, **fns)
+        b.release(qkv)
+        o = self.o.emit(b, out)
+        b.release(out)
+        return o

@@ -58,7 +58,11 @@ class Runtime:
 
 
 class Part:
-    """Base of all parts: a tree whose leaves declare tensors."""
+    """Base of all parts: a tree whose leaves declare tensors.
+
+    A part may also describe what it does to the native step executor (`emit`, writing
+    operations over numbered activation buffers to an `engine.native.ProgramBuilder`); a part
+    without it keeps its model on the Python path, where `forward` runs."""
 
     def children(self) -> Sequence["Part"]:
         return ()
@@ -117,6 +121,12 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
+    def emit(self, b, x: int, pos: int) -> int:
+        """Native program: register x[T, d] in, a new register [T, d_out] out; `pos` is the
+        schedule position whose cache this run uses."""
+        from ..engine.native import NotNative
+        raise NotNative(f"{type(self).__name__} runs in Python only")
+
     def forward_in_block(self, delta, residual, norm: "Norm", ctx, cache):
         """What a block calls: (delta, residual) in, (delta', residual') out, where the stream
         is residual + delta (either may be None).  The default normalises and calls `forward`;
@@ -132,6 +142,11 @@ class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
+    def emit(self, b, x: int) -> int:
+        """Native program: register x[T, d] in, a new register [T, d] out."""
+        from ..engine.native import NotNative
+        raise NotNative(f"{type(self).__name__} runs in Python only")
+
     def forward_in_block(self, delta, residual, norm: "Norm", ctx):
         """See Mixer.forward_in_block."""
         x, residual = norm.forward(delta, residual)
@@ -146,6 +161,12 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None):  # pragma: no cover
         raise NotImplementedError
 
+    def emit(self, b, x: int | None, stream: int | None) -> tuple[int, int]:
+        """Native program: (register x or None, stream register or None) -> (normed, stream);
+        x is given back to the builder once the stream holds its value."""
+        from ..engine.native import NotNative
+        raise NotNative(f"{type(self).__name__} runs in Python only")
+
 
 class PositionEncoding(Part):
     """Puts positions into the projected q and k of an attention mixer and stores k and v
@@ -158,6 +179,12 @@ class PositionEncoding(Part):
         """If a mixer's kernel may do this part's work itself: (frequencies or None, rotated
         width, traditional pairing, whether to store k and v); else None."""
         return None
+
+    def native_args(self):
+        """For the native executor's attention operation, which rotates and stores itself:
+        (inverse frequencies or None, rotated width, traditional pairing)."""
+        from ..engine.native import NotNative
+        raise NotNative(f"{type(self).__name__} runs in Python only")
 
 
 @dataclass(frozen=True)

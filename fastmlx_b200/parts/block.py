@@ -29,3 +29,13 @@ class PreNormBlock(Part):
     def forward(self, delta, residual, ctx, cache):
         delta, residual = self.mixer.forward_in_block(delta, residual, self.norm1, ctx, cache)
         return self.ffn.forward_in_block(delta, residual, self.norm2, ctx)
+
+    def emit(self, b, delta, stream, pos):
+        """Native program: (delta register, stream register or None) -> (delta', stream)."""
+        x, stream = self.norm1.emit(b, delta, stream)
+        y = self.mixer.emit(b, x, pos)
+        b.release(x)
+        x, stream = self.norm2.emit(b, y, stream)
+        z = self.ffn.emit(b, x)
+        b.release(x)
+        return z, stream

@@ -28,6 +28,13 @@ class Embedding(Part):
         return self.rt.k.embedding(ids, self.weight, ctx.status)
 
 
+    def emit(self, b) -> int:
+        from ..engine.native import OP_EMBED, _dt
+        out = b.reg(self.width)
+        b.op(OP_EMBED, out0=out, w=b.ptr(self.weight), w_dtype=_dt(self.weight.dtype), n=self.width, table_rows=self.vocab)
+        return out
+
+
 class LMHead(Part):
     """logits = x W^T in 32-bit, no bias, cap or scale; W is the embedding table when the
     model ties them (tamnd/fastmlx compute/models/llama.go:433-437).  Only the rows whose
@@ -58,3 +65,11 @@ class LMHead(Part):
         """Final norm, then logits."""
         x, _ = norm.forward(delta, residual)
         return self.forward(x)
+
+    def emit_after(self, b, delta, stream, norm) -> None:
+        """Native program: final norm, then the step's logits."""
+        from ..engine.native import F32, LOGITS, OP_LINEAR, _dt
+        x, _ = norm.emit(b, delta, stream)
+        w = self.tied.weight if self.tied is not None else self.weight
+        b.op(OP_LINEAR, in0=x, out0=LOGITS, w=b.ptr(w), w_dtype=_dt(w.dtype), ldw=w.stride(0), n=self.vocab, k=self.width,
+             out_dtype=F32)

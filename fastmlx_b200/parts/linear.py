@@ -52,3 +52,13 @@ class Linear(Part):
 
     def forward(self, x, out_dtype=None):
         return self.rt.k.linear(x, self.weight, self.bias, out_dtype or self.rt.dtype)
+
+    def emit(self, b, x: int, out_dtype=None, out: int | None = None) -> int:
+        """Native program: out = x . W^T (+ b) into a new register (or into `out`)."""
+        from ..engine.native import OP_LINEAR, _dt
+        dt = _dt(out_dtype or self.rt.dtype)
+        if out is None:
+            out = b.reg(self.out_features, dt)
+        b.op(OP_LINEAR, in0=x, out0=out, w=b.ptr(self.weight), bias=b.ptr(self.bias), w_dtype=_dt(self.weight.dtype),
+             ldw=self.weight.stride(0), n=self.out_features, k=self.in_features, out_dtype=dt)
+        return out

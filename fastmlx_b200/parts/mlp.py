@@ -40,3 +40,15 @@ class SwiGLU(FeedForward):
         else:
             act = k.silu_mul(self.gate_up.forward(x), self.block or None)
         return self.down.forward(act)
+
+    def emit(self, b, x):
+        from ..engine.native import OP_GATE_UP, _dt
+        act = b.reg(self.intermediate)
+        both = b.reg(2 * self.intermediate)              # gate and up side by side, where no kernel fuses SiLU-mul in
+        w = self.gate_up.weight
+        b.op(OP_GATE_UP, in0=x, out0=act, out1=both, w=b.ptr(w), bias=b.ptr(self.gate_up.bias), w_dtype=_dt(w.dtype),
+             ldw=w.stride(0), n=2 * self.intermediate, k=self.width, block=self.block, out_dtype=b.act)
+        b.release(both)
+        out = self.down.emit(b, act)
+        b.release(act)
+        return out

@@ -97,3 +97,22 @@ class Model(Part):
             if residual is not None:
                 residual = k.gather_rows(residual, ctx.logit_rows, ctx.status)
         return self.head.forward_after(delta, residual, self.final_norm)
+
+    def emit(self, b) -> None:
+        """The step as a program of the native executor (engine/native.py): what `forward` does,
+        said once.  Raises NotNative where a part has no `emit`."""
+        from ..engine.native import NotNative, OP_GATHER_ROWS
+        for part in (self.embed, self.final_norm, self.head, *self.layers):
+            if not hasattr(part, "emit") and not hasattr(part, "emit_after"):
+                raise NotNative(f"{type(part).__name__} runs in Python only")
+        delta, stream = self.embed.emit(b), None
+        for pos, run in enumerate(self.schedule):
+            delta, stream = self.layers[run.layer].emit(b, delta, stream, pos)
+        b.wanted = True                                   # from here on: the wanted rows only
+        picked = b.reg(b.cols(delta), b.dtype_of(delta))
+        b.op(OP_GATHER_ROWS, in0=delta, out0=picked)
+        picked_stream = None
+        if stream is not None and stream != delta:
+            picked_stream = b.reg(b.cols(stream), b.dtype_of(stream))
+            b.op(OP_GATHER_ROWS, in0=stream, out0=picked_stream)
+        self.head.emit_after(b, picked, picked_stream, self.final_norm)

@@ -30,6 +30,23 @@ class RMSNorm(Norm):
         return self.rt.k.add_rmsnorm(x, residual, self.weight, self.eps, stream_dtype=torch.float32,
                                      out_dtype=self.rt.dtype)
 
+    def emit(self, b, x, stream):
+        from ..engine.native import BF16, F32, OP_ADD_RMSNORM
+        out = b.reg(self.width)
+        args = dict(out0=out, vec=b.ptr(self.weight), n=self.width, eps=self.eps)
+        if stream is None and b.act == BF16:
+            # the stream's first value, widened into a 32-bit register of its own
+            stream = b.reg(self.width, F32)
+            b.op(OP_ADD_RMSNORM, in0=x, in1=stream, init=1, **args)
+            b.release(x)
+        elif stream is None:
+            b.op(OP_ADD_RMSNORM, in0=x, **args)          # x itself is the stream from here on
+            stream = x
+        else:
+            b.op(OP_ADD_RMSNORM, in0=-1 if x is None else x, in1=stream, **args)
+            b.release(x)
+        return out, stream
+
     def fold(self):
         """(weight, eps) for a kernel that normalises its input rows itself."""
         return (self.weight, self.eps)

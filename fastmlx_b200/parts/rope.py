@@ -62,6 +62,9 @@ class RotaryEmbedding(PositionEncoding):
         width, pairing, whether to store k and v)."""
         return (self.inv_freq, self.rotary_dim, self.traditional, bool(cache.kv is not None and cache.writable))
 
+    def native_args(self):
+        return (self.inv_freq, self.rotary_dim, self.traditional)
+
 
 class NoPositionEncoding(PositionEncoding):
     """Stores k and v unrotated (a mixer whose positions come from elsewhere)."""
@@ -76,3 +79,6 @@ class NoPositionEncoding(PositionEncoding):
 
     def fused_args(self, cache):
         return (None, 0, False, bool(cache.kv is not None and cache.writable))
+
+    def native_args(self):
+        return (None, 0, False)

@@ -49,9 +49,10 @@ def models(tmp_path_factory):
     return out
 
 
-def _run(model_dir, dtype, steps, max_tokens, page):
+def _run(model_dir, dtype, steps, max_tokens, page, native=True):
     from fastmlx_b200.engine.replay import Replayer
-    rp = Replayer(model_dir, dtype, max_tokens, page_size=page)
+    rp = Replayer(model_dir, dtype, max_tokens, page_size=page, native=native)
+    assert (rp.step_fn.native is not None) == native
     outs = []
     for st in steps:
         outs.append(rp.step(st))
@@ -78,12 +79,14 @@ def _compare(steps, outs, prompts, ref, tol):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
-def test_replay(models, name, dtype, cut):
+@pytest.mark.parametrize("native", [True, False], ids=["native", "python"])
+def test_replay(models, name, dtype, cut, native):
+    """native: the step's host work in the compiled executor; python: through `Model.forward`."""
     d, prompts, ref = models[name]
     case = CASES[name]
     steps = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions,
              "mixed": traces.mixed}[cut](prompts)
-    outs, rp = _run(d, dtype, steps, case["max_tokens"], case["page"])
+    outs, rp = _run(d, dtype, steps, case["max_tokens"], case["page"], native)
     _compare(steps, outs, prompts, ref[dtype], TOL[dtype])
     if cut == "mixed":
         total_pages = sum(-(-len(t) // case["page"]) for t in prompts.values())
