@@ -124,6 +124,16 @@ class Engine:
     def abort(self, request_id: str) -> None:
         self.scheduler.abort(request_id)
 
+    def reconfigure(self, *, max_num_batched_tokens: int | None = None, prefill_chunk: int | None = None) -> None:
+        """Change the scheduler's token budget or portion size between requests (the
+        reference's scheduler config, scheduler/scheduler.go:30-47, is fixed at start)."""
+        if self.has_unfinished():
+            raise RuntimeError("the scheduler is reconfigured only while no request is live")
+        if max_num_batched_tokens is not None:
+            self.scheduler.cfg.max_num_batched_tokens = self.engine_config.max_num_batched_tokens = int(max_num_batched_tokens)
+        if prefill_chunk is not None:
+            self.scheduler.cfg.prefill_chunk = self.engine_config.prefill_chunk = int(prefill_chunk)
+
     def has_unfinished(self) -> bool:
         return bool(self._pending_outputs) or self._ahead is not None or self.scheduler.has_unfinished()
 
