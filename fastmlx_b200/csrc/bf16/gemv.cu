@@ -31,10 +31,25 @@ template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { 
 
 // NT tiles of 8 features per block; HI: rows 8..15 of x exist; DUAL: the NT tiles are gate
 // tiles and each has an up tile `blk` rows further on.
-template <int NT, bool HI, bool DUAL, int U, int WARPS, typename TO>
+// What the greedy head leaves instead of logits: per row the best (value, index) as one 64-bit word that
+// atomicMax orders (the value's bits made monotonic above, the index inverted below, so that the lower
+// index wins a tie), a ticket that tells the last block, and the chosen ids.
+struct GreedyOut {
+  unsigned long long* best;      // [16], zero between launches
+  int* ticket;                   // [1], zero between launches
+  int* ids;                      // [M]
+};
+__device__ __forceinline__ unsigned long long greedy_key(float v, int n) {
+  unsigned u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);                  // monotonic in v; every real key is above 0
+  return ((unsigned long long)u << 32) | (unsigned)(0x7fffffff - n);
+}
+
+template <int NT, bool HI, bool DUAL, int U, int WARPS, typename TO, bool GREEDY = false>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long ldw, const float* __restrict__ bias,
-            const bf16* residual, long long ldr, TO* out, long long ldo, int M, int N, int K, int blk) {
+            const bf16* residual, long long ldr, TO* out, long long ldo, int M, int N, int K, int blk,
+            GreedyOut greedy = GreedyOut{nullptr, nullptr, nullptr}) {
   constexpr int TILES = DUAL ? 2 * NT : NT;
   constexpr int ROWS = HI ? 16 : 8;
   __shared__ float red[WARPS][TILES][ROWS][9];
@@ -115,6 +130,21 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
   for (int idx = threadIdx.x; idx < NT * ROWS * 8; idx += WARPS * 32) {
     const int f = idx & 7, rest = idx >> 3, i = rest % NT, tok = rest / NT;      // consecutive threads: consecutive features
     const int n = out0 + 8 * i + f;
+    if (GREEDY) {
+      // the row's 8 * NT logits of this block sit in consecutive lanes of whole warps: their best by a
+      // shuffle tree, then one atomicMax per row and block
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) v += red[w][i][tok][f];
+      unsigned long long key = (tok < M && n < n_out) ? greedy_key(v, n) : 0ull;
+#pragma unroll
+      for (int o = 4 * NT; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+        key = other > key ? other : key;
+      }
+      if ((idx & (8 * NT - 1)) == 0 && tok < M && key != 0ull) atomicMax(&greedy.best[tok], key);
+      continue;
+    }
     if (tok >= M || n >= n_out) continue;
     float v = 0.f;
 #pragma unroll
@@ -130,6 +160,24 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
     if (residual != nullptr) v = bf16r(v) + __bfloat162float(residual[(long long)tok * ldr + n]);
     store_out<TO>(out + (long long)tok * ldo + n, v);
   }
+  if (GREEDY) {
+    // The block that draws the last ticket turns the rows' best words into ids and leaves the words and
+    // the ticket at zero for the next launch.  Nobody waits for anybody.
+    __shared__ int drew_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      drew_last = atomicAdd(greedy.ticket, 1) == (int)gridDim.x - 1;
+      if (drew_last) __threadfence();
+    }
+    __syncthreads();
+    if (!drew_last) return;
+    if (threadIdx.x < M) {
+      const unsigned long long key = atomicExch(&greedy.best[threadIdx.x], 0ull);
+      greedy.ids[threadIdx.x] = key == 0ull ? 0 : 0x7fffffff - (int)(unsigned)(key & 0xffffffffull);
+    }
+    if (threadIdx.x == 0) *greedy.ticket = 0;
+  }
 }
 
 template <int NT, bool HI, bool DUAL, int U, int WARPS, typename TO>
@@ -137,9 +185,33 @@ void launch(const void* x, long long ldx, const void* W, long long ldw, const fl
             long long ldr, void* out, long long ldo, int M, int N, int K, int blk, cudaStream_t stream) {
   const int n_out = DUAL ? N / 2 : N;
   fmx_launch(gemv_kernel<NT, HI, DUAL, U, WARPS, TO>, dim3((n_out + 8 * NT - 1) / (8 * NT)), dim3(WARPS * 32), 0, stream,
-             (const bf16*)x, ldx, (const bf16*)W, ldw, bias, (const bf16*)residual, ldr, (TO*)out, ldo, M, N, K, blk);
+             (const bf16*)x, ldx, (const bf16*)W, ldw, bias, (const bf16*)residual, ldr, (TO*)out, ldo, M, N, K, blk,
+             GreedyOut{nullptr, nullptr, nullptr});
 }
 }  // namespace
+
+// The output head of a decode step with the greedy choice made in the same pass: ids[m] = the index of the
+// largest of x[m] . W[n]^T over n (the lowest index on ties), for at most 16 rows; no logits are written.
+// best: 16 64-bit words, ticket: one int, both zero before the first call (every call leaves them zero).
+// Calls that share them must not overlap on the GPU.
+FMX_EXPORT int fmx_gemv_argmax(const void* x, long long ldx, const void* W, long long ldw, int* ids, void* best, int* ticket,
+                               int M, int N, int K, cudaStream_t stream) {
+  if (M == 0) return 0;
+  if (M < 0 || M > 16 || N <= 0 || N > 0x7fffffff - 1 || K <= 0) return fmx_fail("fmx_gemv_argmax: takes 1..16 rows, got M=%d N=%d K=%d", M, N, K);
+  if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15))
+    return fmx_fail("fmx_gemv_argmax: rows must be 16-byte aligned (K=%d ldx=%lld ldw=%lld)", K, ldx, ldw);
+  if (ids == nullptr || best == nullptr || ticket == nullptr || ((uintptr_t)best & 7)) return fmx_fail("fmx_gemv_argmax: needs ids, best words and a ticket");
+  const GreedyOut g{(unsigned long long*)best, ticket, ids};
+  const dim3 grid((N + 31) / 32);
+  if (M > 8)
+    fmx_launch(gemv_kernel<4, true, false, 2, 8, float, true>, grid, dim3(256), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw,
+               (const float*)nullptr, (const bf16*)nullptr, 0LL, (float*)nullptr, 0LL, M, N, K, 0, g);
+  else
+    fmx_launch(gemv_kernel<4, false, false, 4, 8, float, true>, grid, dim3(256), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw,
+               (const float*)nullptr, (const bf16*)nullptr, 0LL, (float*)nullptr, 0LL, M, N, K, 0, g);
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
 
 // Output features per block when the caller leaves the choice open: 32 once that still gives
 // every SM a block, else 16 (wider blocks re-read x less and keep more of W in flight per block,

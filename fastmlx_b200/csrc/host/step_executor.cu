@@ -38,6 +38,7 @@ typedef int (*attn_prefill_fn)(const void*, long long, const void*, const int*, 
 typedef int (*attn_prefill_tc_fn)(const void*, long long, int, const void*, const int*, int, const int*, const int*,
                                   void*, int, int, int, int, int, long long, float, int, int*, cudaStream_t);
 typedef int (*attn_plan_fn)(int, int, long long, int);
+typedef int (*gemv_argmax_fn)(const void*, long long, const void*, long long, int*, void*, int*, int, int, int, cudaStream_t);
 
 constexpr int GEMV_MAX_ROWS = 16;            // as kernels/__init__.py names them
 constexpr int LIBRARY_MIN_FEATURES = 65536;
@@ -296,6 +297,13 @@ struct Run {
                                                   out_dtype, res_dtype, op.init, stream);
       }
       case FMX_OP_LINEAR: {
+        if (op.out0 == -2 && d.greedy_ids != nullptr) {
+          if (ex.k.gemv_argmax == nullptr || rows_of(op) > GEMV_MAX_ROWS)
+            return fmx_fail("the greedy head takes at most %d rows of bfloat16", GEMV_MAX_ROWS);
+          ++ex.launches;
+          return ((gemv_argmax_fn)ex.k.gemv_argmax)(reg(op.in0), op.k, op.w, op.ldw, d.greedy_ids, d.greedy_best, d.greedy_ticket,
+                                                    rows_of(op), op.n, op.k, stream);
+        }
         void* out = op.out0 == -2 ? (void*)d.logits : reg(op.out0);
         return linear(reg(op.in0), ex.regs[op.in0].dtype, op, out, op.out_dtype, rows_of(op));
       }

@@ -71,6 +71,7 @@ struct FmxKernelTable {
   void* gemv;
   void* gemm_tcgen05;
   void* gemm_tcgen05_plan_fills;
+  void* gemv_argmax;
 };
 
 // One laid-out step: device pointers into the packed buffer, and the step's workspaces.
@@ -94,6 +95,11 @@ struct FmxStepDesc {
   long long attn_scratch_floats;
   int* attn_tickets;
   int attn_tickets_n;
+  // not null: the head chooses greedily inside its product (at most 16 wanted rows, bfloat16 operands) and
+  // leaves ids here instead of logits; greedy_best / greedy_ticket are that kernel's words, zero between launches
+  int* greedy_ids;
+  void* greedy_best;
+  int* greedy_ticket;
 };
 
 // What the caller knows of a step before it is laid out: one entry per request.

@@ -193,12 +193,14 @@ class Engine:
         """Put a planned step on the device.  -> (plan, sampled ids on the device, readiness
         event) or None after reporting a failure."""
         try:
-            logits = self.step_fn.run(plan.entries, reserved=True, check=False, tokens_from=tokens_from)
             ahead = 1 if tokens_from is not None else 0
             rows = [(req.sampling, req.seed, len(req.output_token_ids) + ahead,
                      req.tail(req.sampling.history_needed) if not ahead else [])
                     for req, s in zip(plan.requests, plan.samples) if s]
-            sampled = self.sampler.sample(logits, rows) if rows else None
+            # every row takes its largest logit as it stands: the head chooses inside its product
+            greedy = bool(rows) and all(p.greedy and not p.logit_bias and not p.penalties_on for p, _, _, _ in rows)
+            out = self.step_fn.run(plan.entries, reserved=True, check=False, tokens_from=tokens_from, greedy=greedy)
+            sampled = (out if greedy else self.sampler.sample(out, rows)) if rows else None
         except (StepError, RuntimeError) as e:
             outs.extend(self.scheduler.step_failed(plan, str(e)))
             for req in plan.requests:

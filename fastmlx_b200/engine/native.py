@@ -50,7 +50,7 @@ class FmxOp(Structure):
 class FmxKernelTable(Structure):
     _fields_ = [(n, c_void_p) for n in ("gather_rows", "gather_rows_f32_to_bf16", "add_rmsnorm", "silu_mul", "gemm_simple",
                                         "rope_kv_write", "paged_attention_simple", "fill_rows", "gemv", "gemm_tcgen05",
-                                        "gemm_tcgen05_plan_fills")]
+                                        "gemm_tcgen05_plan_fills", "gemv_argmax")]
 
 
 class FmxStepDesc(Structure):
@@ -61,7 +61,8 @@ class FmxStepDesc(Structure):
                 ("block_tables", c_void_p * MAX_GROUPS), ("bt_stride", c_int * MAX_GROUPS),
                 ("slot_mapping", c_void_p * MAX_GROUPS), ("status", c_void_p), ("arena", c_void_p),
                 ("arena_bytes", c_longlong), ("logits", c_void_p), ("attn_scratch", c_void_p),
-                ("attn_scratch_floats", c_longlong), ("attn_tickets", c_void_p), ("attn_tickets_n", c_int)]
+                ("attn_scratch_floats", c_longlong), ("attn_tickets", c_void_p), ("attn_tickets_n", c_int),
+                ("greedy_ids", c_void_p), ("greedy_best", c_void_p), ("greedy_ticket", c_void_p)]
 
 
 class FmxBatchIn(Structure):
@@ -126,6 +127,7 @@ class ProgramBuilder:
         self.keep: list = []                       # tensors whose addresses the program holds
         self._free: dict[tuple[int, int], list[int]] = {}
         self.wanted = False                        # operations from here on run over the wanted rows only
+        self.greedy_head_ok = False                # the head may choose greedily inside its product
 
     def reg(self, cols: int, dtype=None) -> int:
         key = (int(cols), self.act if dtype is None else _dt(dtype) if not isinstance(dtype, int) else dtype)
@@ -222,6 +224,7 @@ class NativeProgram:
             setattr(table, name, _fn(common, "fmx_" + name))
         if rt.dtype == torch.bfloat16:
             setattr(table, "gemv", _fn(_klib.load("bf16"), "fmx_gemv"))
+            table.gemv_argmax = _fn(_klib.load("bf16"), "fmx_gemv_argmax")
             tc = _klib.load("tc")
             table.gemm_tcgen05 = _fn(tc, "fmx_gemm_tcgen05")
             table.gemm_tcgen05_plan_fills = _fn(tc, "fmx_gemm_tcgen05_plan_fills")
@@ -235,6 +238,8 @@ class NativeProgram:
         if not self.handle:
             raise _klib.KernelError(self.lib.fmx_last_error().decode(errors="replace"))
         self.vocab = model.vocab_size
+        self.greedy_ok = bool(b.greedy_head_ok and rt.dtype == torch.bfloat16)
+        self.greedy_ws = k.greedy_workspace(rt.device) if self.greedy_ok else None
         self.scratch = k.attention_scratch(rt.device)
         self.tickets = k.attention_tickets(rt.device)
         self.graph_rows = int(graph_rows)
@@ -264,19 +269,31 @@ class NativeProgram:
         if rc != 0:
             raise _klib.KernelError(self.lib.fmx_last_error().decode(errors="replace"))
 
-    def _finish_desc(self, d: FmxStepDesc, arena: torch.Tensor, n_want: int) -> torch.Tensor:
-        logits = torch.empty((n_want, self.vocab), dtype=torch.float32, device=self.rt.device)
+    def _finish_desc(self, d: FmxStepDesc, arena: torch.Tensor, n_want: int, greedy: bool = False):
+        """-> (the step's result tensor, whether the ids still have to be chosen from it)."""
+        fused = greedy and self.greedy_ok and 0 < n_want <= 16
+        if fused:
+            result = torch.empty(n_want, dtype=torch.int32, device=self.rt.device)
+            d.greedy_ids = result.data_ptr()
+            d.greedy_best, d.greedy_ticket = self.greedy_ws[0].data_ptr(), self.greedy_ws[1].data_ptr()
+        else:
+            result = torch.empty((n_want, self.vocab), dtype=torch.float32, device=self.rt.device)
+            d.logits = result.data_ptr()
         d.status = self.status.data_ptr()
         d.arena, d.arena_bytes = arena.data_ptr(), arena.numel()
-        d.logits = logits.data_ptr()
         d.attn_scratch, d.attn_scratch_floats = self.scratch.data_ptr(), self.scratch.numel()
         d.attn_tickets, d.attn_tickets_n = self.tickets.data_ptr(), self.tickets.numel()
-        return logits
+        return result, greedy and not fused
+
+    def _result(self, result, choose: bool):
+        return self.rt.k.argmax(result) if choose and result.shape[0] else \
+            (torch.empty(0, dtype=torch.int32, device=self.rt.device) if choose else result)
 
     # ------------------------------------------------------------------ a step the Python side has laid out
-    def forward_context(self, ctx) -> torch.Tensor:
+    def forward_context(self, ctx, greedy: bool = False) -> torch.Tensor:
         """Run the program over a `StepContext` (the captured decode steps are laid out by
-        `build_context` into their graph's fixed buffers)."""
+        `build_context` into their graph's fixed buffers).  `greedy`: -> the wanted rows' greedy
+        choices (int32) instead of their logits."""
         d = FmxStepDesc()
         n_want = int(ctx.logit_rows.numel()) if ctx.logit_rows is not None else 0
         d.T, d.R, d.n_want = ctx.T, ctx.R, n_want
@@ -296,10 +313,10 @@ class NativeProgram:
             raise _klib.KernelError(f"a captured step holds at most {self.graph_rows} tokens")
         else:
             arena = self._big_arena(ctx.T)
-        logits = self._finish_desc(d, arena, n_want)
+        result, choose = self._finish_desc(d, arena, n_want, greedy)
         self._check(self.lib.fmx_exec_forward(self.handle, ctypes.byref(d), torch.cuda.current_stream().cuda_stream))
         self._count()
-        return logits
+        return self._result(result, choose)
 
     def _big_arena(self, T: int) -> torch.Tensor:
         if T > self.arena_tokens:
@@ -310,7 +327,7 @@ class NativeProgram:
         return self.arena
 
     # ------------------------------------------------------------------ a step from its entries
-    def step(self, entries) -> tuple[torch.Tensor, StepInfo]:
+    def step(self, entries, greedy: bool = False) -> tuple[torch.Tensor, StepInfo]:
         """Lay the entries out, copy the description to the device and run the program: one
         call into compiled code.  Pages for the new tokens must have been reserved."""
         R = len(entries)
@@ -352,10 +369,10 @@ class NativeProgram:
         self._check(self.lib.fmx_exec_layout(ctypes.byref(inp), host.data_ptr(), self.buffers.dev.data_ptr(),
                                              self.buffers.ints, ctypes.byref(d), stream))
         self.buffers.mark()
-        logits = self._finish_desc(d, self._big_arena(d.T), len(want))
+        result, choose = self._finish_desc(d, self._big_arena(d.T), len(want), greedy)
         self._check(self.lib.fmx_exec_forward(self.handle, ctypes.byref(d), stream))
         self._count()
-        return logits, StepInfo(d.T, int(ints) * 4)
+        return self._result(result, choose), StepInfo(d.T, int(ints) * 4)
 
 
 def build_program(model, manager, rt, status, graph_rows: int = 256):

@@ -40,8 +40,8 @@ def _pow2_at_least(n: int, floor: int = 1) -> int:
 class _DecodeGraph:
     """One captured decode step for `rows` rows and block tables `width` pages wide."""
 
-    def __init__(self, fn: "StepFunction", rows: int, width: int, entries):
-        self.rows, self.width = rows, width
+    def __init__(self, fn: "StepFunction", rows: int, width: int, entries, greedy: bool = False):
+        self.rows, self.width, self.greedy = rows, width, greedy
         rt, manager = fn.rt, fn.manager
         probe = build_context(entries, manager, None, fn.status, pad_rows=rows, pad_blocks=width, pad_want=True)
         n = probe.scratch["layout_ints"]
@@ -55,7 +55,7 @@ class _DecodeGraph:
         side = torch.cuda.Stream(device=rt.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            fn.forward_context(ctx)
+            fn.forward_context(ctx, greedy)
         torch.cuda.current_stream().wait_stream(side)
         if saved is not None:
             manager.restore_state(saved)
@@ -64,7 +64,7 @@ class _DecodeGraph:
         count = getattr(rt.k, "launch_count", lambda: 0)
         before = count()
         with torch.cuda.graph(self.graph):
-            self.logits = fn.forward_context(ctx)
+            self.logits = fn.forward_context(ctx, greedy)
         self.kernel_launches = count() - before        # launches of this package's kernels per replay
         self.ctx = ctx
 
@@ -119,9 +119,11 @@ class StepFunction:
                     make(rt.device)
 
     def run(self, entries: list[StepEntry], reserved: bool = False, check: bool = True,
-            tokens_from: torch.Tensor | None = None) -> torch.Tensor:
+            tokens_from: torch.Tensor | None = None, greedy: bool = False) -> torch.Tensor:
         """-> float32 logits [sum(len(e.want)), vocab] on the device, in the order of the
-        entries and of their `want`.  `reserved`: the caller (the scheduler) has taken the
+        entries and of their `want`; with `greedy`, the index of each wanted place's largest logit
+        instead (int32 [sum(len(e.want))], the lowest index on ties), which a decode step's head
+        chooses inside its product without writing logits.  `reserved`: the caller (the scheduler) has taken the
         pages already and commits or rolls back itself.  `check=False` leaves the read of
         the kernels' status word to the caller, who reads results from the device anyway.
         The tensor may be a view of a graph's output: use it before the next step.
@@ -150,7 +152,7 @@ class StepFunction:
                 for e in entries:
                     self.manager.reserve(e.request, len(e.tokens))
                     taken.append(e.request)
-            logits, ctx = self._forward(entries, tokens_from)
+            logits, ctx = self._forward(entries, tokens_from, greedy)
             if check:
                 self.check_status()
         except BaseException:
@@ -170,7 +172,7 @@ class StepFunction:
     def graphable(self, entries) -> bool:
         return self.cuda_graphs and len(entries) <= self.max_graph_rows and all(len(e.tokens) == 1 for e in entries)
 
-    def _forward(self, entries, tokens_from=None):
+    def _forward(self, entries, tokens_from=None, greedy: bool = False):
         if tokens_from is not None and not self.graphable(entries):
             raise StepError("ids can be fed from the device only into a captured decode step")
         if self.cuda_graphs and len(entries) <= self.max_graph_rows and all(len(e.tokens) == 1 for e in entries):
@@ -178,11 +180,15 @@ class StepFunction:
             rows = _pow2_at_least(len(entries))
             blocks = max(-(-(e.request.length + 1) // ps) for e in entries)
             width = _pow2_at_least(blocks, 16)
-            key = (rows, width)
+            key = (rows, width, True) if greedy else (rows, width)
             g = self.graphs.get(key)
             if g is None:
-                g = self.graphs[key] = _DecodeGraph(self, rows, width, entries)
+                g = self.graphs[key] = _DecodeGraph(self, rows, width, entries, greedy)
             logits, ctx = g.run(self, entries, tokens_from)
+            if greedy:
+                # the ids lie in the graph's own output, which its next replay overwrites, and an engine
+                # that runs a step ahead reads them on another stream after that replay is launched
+                logits = logits.clone()
             self.graph_replays += 1
             self.graph_kernel_launches += g.kernel_launches
             # one wanted place per row in the graph; give back what was asked for
@@ -193,15 +199,20 @@ class StepFunction:
                 return logits[:0], ctx
             return logits[torch.as_tensor(picks, device=logits.device)], ctx
         if self.native is not None:
-            return self.native.step(entries)
+            return self.native.step(entries, greedy)
         ctx = build_context(entries, self.manager, self.rt.device, self.status)
-        return self.model.forward(ctx), ctx
+        return self.forward_context(ctx, greedy), ctx
 
-    def forward_context(self, ctx: StepContext) -> torch.Tensor:
+    def forward_context(self, ctx: StepContext, greedy: bool = False) -> torch.Tensor:
         """The model over a step that is laid out already (the captured decode steps)."""
         if self.native is not None:
-            return self.native.forward_context(ctx)
-        return self.model.forward(ctx)
+            return self.native.forward_context(ctx, greedy)
+        if not greedy:
+            return self.model.forward(ctx)
+        try:
+            return self.model.forward(ctx, greedy=True)
+        except TypeError:                     # a model class of its own whose forward knows no greedy head
+            return self.rt.k.argmax(self.model.forward(ctx))
 
     def check_status(self) -> None:
         """Kernels never trap on a bad index: they skip the access and leave a code."""

@@ -194,6 +194,39 @@ def gemv(x, w, bias=None, out_dtype=torch.bfloat16, residual=None, block: int = 
     return out
 
 
+_greedy_ws: dict = {}
+
+
+def greedy_workspace(device):
+    """The greedy head's 16 best-so-far words and its ticket, one pair per device, made once
+    (captured graphs hold their addresses); zero between launches."""
+    ws = _greedy_ws.get(_dev_index(device))
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the greedy head's workspace must exist before a CUDA graph is captured")
+        ws = _greedy_ws[_dev_index(device)] = (torch.zeros(16, dtype=torch.int64, device=device),
+                                               torch.zeros(1, dtype=torch.int32, device=device))
+    return ws
+
+
+def can_greedy_head(x, w) -> bool:
+    """May the output head choose greedily in the same pass (no logits written)?"""
+    return _bf16_operands(x, w) and x.shape[0] <= GEMV_MAX_ROWS
+
+
+def greedy_head(x, w) -> torch.Tensor:
+    """argmax over n of x[m] . w[n]^T for at most 16 rows, the lowest index on ties: the head of
+    a decode step whose rows all choose greedily.  The weight streams once; every block keeps the
+    best of its 32 logits per row, and the rows' bests meet in one 64-bit atomicMax each.
+    -> int32 [M]."""
+    M, K = x.shape
+    ids = torch.empty(M, dtype=torch.int32, device=x.device)
+    best, ticket = greedy_workspace(x.device)
+    call("bf16", "fmx_gemv_argmax", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), ids.data_ptr(), best.data_ptr(),
+         ticket.data_ptr(), M, w.shape[0], K, _stream())
+    return ids
+
+
 def tile_width(M: int, N: int, sms: int = 148) -> int:
     """The tile width (of 128, 192, 256) whose tiles fill the SMs' rounds best, as the
     tensor-core library plans it (`fmx_gemm_tcgen05_plan_width`)."""

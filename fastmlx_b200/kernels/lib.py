@@ -34,6 +34,7 @@ _SIGNATURES = {
     },
     "bf16": {
         "fmx_gemv": [_P, _L, _P, _L, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],
+        "fmx_gemv_argmax": [_P, _L, _P, _L, _P, _P, _P, _I, _I, _I, _P],
     },
     "tc": {
         "fmx_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],

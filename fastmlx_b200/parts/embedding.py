@@ -61,10 +61,17 @@ class LMHead(Part):
         w = self.tied.weight if self.tied is not None else self.weight
         return self.rt.k.linear(x, w, None, torch.float32)
 
-    def forward_after(self, delta, residual, norm):
-        """Final norm, then logits."""
+    def forward_after(self, delta, residual, norm, greedy: bool = False):
+        """Final norm, then logits; `greedy`: the index of each row's largest logit instead
+        (int32), chosen inside the head's product where its kernel can (no logits written)."""
         x, _ = norm.forward(delta, residual)
-        return self.forward(x)
+        if not greedy:
+            return self.forward(x)
+        k = self.rt.k
+        w = self.tied.weight if self.tied is not None else self.weight
+        if hasattr(k, "can_greedy_head") and k.can_greedy_head(x, w):
+            return k.greedy_head(x, w)
+        return k.argmax(self.forward(x))
 
     def emit_after(self, b, delta, stream, norm) -> None:
         """Native program: final norm, then the step's logits."""
@@ -73,3 +80,6 @@ class LMHead(Part):
         w = self.tied.weight if self.tied is not None else self.weight
         b.op(OP_LINEAR, in0=x, out0=LOGITS, w=b.ptr(w), w_dtype=_dt(w.dtype), ldw=w.stride(0), n=self.vocab, k=self.width,
              out_dtype=F32)
+        # the greedy choice inside the product takes bfloat16 operands in 16-byte rows
+        b.greedy_head_ok = bool(w.dtype == torch.bfloat16 and b.act == _dt(torch.bfloat16) and self.width % 8 == 0
+                                and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0)

@@ -84,8 +84,9 @@ class Model(Part):
         return self
 
     # ---- one step over a flat batch
-    def forward(self, ctx) -> torch.Tensor:
-        """Logits [len(ctx.logit_rows), vocab] in 32-bit for the batch that `ctx` describes."""
+    def forward(self, ctx, greedy: bool = False) -> torch.Tensor:
+        """Logits [len(ctx.logit_rows), vocab] in 32-bit for the batch that `ctx` describes;
+        `greedy`: each wanted row's greedy choice instead, int32 [len(ctx.logit_rows)]."""
         delta = self.embed.forward(ctx.tokens, ctx)
         residual = None
         for pos, run in enumerate(self.schedule):
@@ -96,7 +97,7 @@ class Model(Part):
                 delta = k.gather_rows(delta, ctx.logit_rows, ctx.status)
             if residual is not None:
                 residual = k.gather_rows(residual, ctx.logit_rows, ctx.status)
-        return self.head.forward_after(delta, residual, self.final_norm)
+        return self.head.forward_after(delta, residual, self.final_norm, greedy)
 
     def emit(self, b) -> None:
         """The step as a program of the native executor (engine/native.py): what `forward` does,

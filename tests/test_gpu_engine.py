@@ -421,8 +421,8 @@ def test_graphs_across_block_table_widths_and_batch_sizes(tmp_path, dtype):
 
     got, eng = run(True)
     keys = set(eng.step_fn.graphs)
-    assert {w for _, w in keys} >= {16, 32, 64}, keys
-    assert {r for r, _ in keys} >= {8, 4, 2, 1}, keys
+    assert {k[1] for k in keys} >= {16, 32, 64}, keys
+    assert {k[0] for k in keys} >= {8, 4, 2, 1}, keys
     for (n, m), p, toks in zip(lens_new, prompts, got):
         assert len(toks) == m
         tiny.check_greedy(cfg, W, p, toks, torch.bfloat16 if dtype == "bfloat16" else None,
@@ -443,7 +443,7 @@ def test_many_live_requests(dirs, dtype, live):
     eng = Engine(dirs["B"], dtype=dtype, block_size=16, max_cache_tokens=live * 128, max_concurrent_requests=live,
                  max_num_batched_tokens=4096)
     outs = eng.generate(prompts, SamplingParams(max_tokens=6, temperature=0.0))
-    assert max(r for r, _ in eng.step_fn.graphs) == live
+    assert max(k[0] for k in eng.step_fn.graphs) == live
     for p, o in zip(prompts, outs):
         assert o.finish_reason == "length" and len(o.output_token_ids) == 6
         tiny.check_greedy(cfg, W, p, o.output_token_ids, torch.bfloat16 if dtype == "bfloat16" else None,

@@ -662,3 +662,31 @@ def test_a_wait_that_runs_out_leaves_a_code_and_a_usable_stream():
     torch.cuda.synchronize()
     assert st2.tolist()[0] == 0
     close(got, plain_ops.linear(x.cpu(), w.cpu(), None, torch.bfloat16), torch.bfloat16, "the product after an expired wait")
+
+
+# ----------------------------------------------------------------------------- the greedy head
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("V,K", [(256, 64), (320, 192), (131, 80), (128256, 2048), (50001, 136)])
+def test_greedy_head_chooses_the_largest_logit(M, V, K):
+    """The head's product with the greedy choice inside against the logits' argmax; twice in a row
+    (its words go back to zero by themselves), and with ties, where the lowest index wins."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=M).to(DEV)
+    w = rnd(V, K, dtype=torch.bfloat16, seed=V, scale=0.05).to(DEV)
+    w[V - 1] = w[3]                                          # rows 3 and V-1 give equal logits everywhere
+    if V > 40:
+        x[0] = (w[3].float() * 40).to(torch.bfloat16)        # ... and row 0's largest logit is that pair's
+    logits = k().gemv(x, w, out_dtype=torch.float32) if V < 65536 else None
+    ref = plain_ops.linear(x.cpu(), w.cpu(), None, torch.float64)
+    for _ in range(2):
+        ids = k().greedy_head(x, w).cpu()
+        for r in range(M):
+            got = int(ids[r])
+            assert 0 <= got < V
+            best = float(ref[r].max())
+            assert float(ref[r, got]) >= best - 1e-3 * max(1.0, abs(best)), (r, got, int(ref[r].argmax()))
+        if logits is not None:                               # the same sums: the same choice, the first index on ties
+            assert ids.tolist() == k().argmax(logits).cpu().tolist()
+        if V > 40:
+            assert int(ids[0]) == 3
+    best_words, ticket = k().greedy_workspace(DEV)
+    assert int(ticket) == 0 and int(best_words.abs().sum()) == 0

@@ -521,7 +521,7 @@ def test_a_mixer_with_state_runs_in_captured_decode_steps(tmp_path):
         eng = Engine(d, dtype="float32", block_size=8, max_cache_tokens=1024, max_concurrent_requests=4)
         assert eng.model.graph_safe and eng.manager.has_state
         outs = eng.generate(prompts, [SamplingParams(max_tokens=m, temperature=0.0) for m in (14, 9, 20)])
-        assert (4, 16) in eng.step_fn.graphs and eng.stats()["graph_replays"] > 10
+        assert any(k[:2] == (4, 16) for k in eng.step_fn.graphs) and eng.stats()["graph_replays"] > 10
         for p, o in zip(prompts, outs):
             seq = list(p)
             for _ in range(len(o.output_token_ids)):
