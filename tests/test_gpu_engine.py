@@ -267,6 +267,11 @@ def test_random_arrivals_aborts_and_a_tight_pool(dirs, seed):
             finished_normally += 1
             assert out.finish_reason == "length" and out.output_token_ids == want[i]
             assert got[ids[i]] == want[i]                 # the increments add up to the whole
+    # and what "alone" produced is the plain model's choice, token by token (the greedy requests)
+    W = tiny.load_plain_weights(dirs["B"])
+    for i in range(n_req):
+        if sps[i].temperature == 0.0:
+            tiny.check_greedy(cfg, W, prompts[i], want[i], None, 1e-5)
     assert finished_normally >= n_req - 3
     assert eng.stats()["pages_used"] == 0
     eng.manager.check()
