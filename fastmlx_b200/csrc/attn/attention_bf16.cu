@@ -40,6 +40,10 @@ constexpr int THREADS = 128;
 constexpr int PREFILL_STAGES = HD <= 128 ? 3 : 2;
 constexpr int DECODE_STAGES = HD <= 128 ? 3 : 2;
 constexpr float LOG2E = 1.4426950408889634f;
+// Block-table entries a decode block keeps in shared memory.  From head size 128 on (two blocks of four warps
+// per SM: little to hide the table read behind) it takes a tenth off the kernel; at head size 64 (four blocks
+// per SM) it cost 3 to 5 %, so there the tiles' copies keep reading the table itself.
+constexpr int BT_CACHE = HD < 128 ? 0 : 1024;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -358,8 +362,8 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   const int t = row_start[r];
   const int pos = positions[t];                      // -1 for a padding row: no keys at all
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
-                page_shift_of(page_size)};
+  Cache c{kv, block_tables + (long long)r * bt_stride, bt_stride, nkv, page_size, num_pages,
+          page_shift_of(page_size)};
 
   const int lo_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int n_keys = max(0, pos + 1 - lo_key);
@@ -369,6 +373,14 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   const int kend = min(pos + 1, kbeg + per);
   const int kstart = kbeg & ~3;
   const int n_tiles = kend > kbeg ? (kend - kstart + BN - 1) / BN : 0;
+  // The pages of this block's keys, once, into shared memory: a tile's copies then start from an address that
+  // is at hand instead of behind a read of the block table from L2 (which stood in front of every tile's
+  // copies: the profile's long-scoreboard stalls).  Ranges beyond the cache keep reading the table itself.
+  // The first tiles go out with addresses read from the table itself; the cache is filled behind them and
+  // used from the loop's first pass on (whose barrier makes it visible).
+  __shared__ int bt_cache[BT_CACHE > 0 ? BT_CACHE : 1];
+  const int bt_blk0 = kstart / page_size;
+  const bool bt_cached = BT_CACHE > 0 && n_tiles > 0 && (kend - 1) / page_size - bt_blk0 + 1 <= BT_CACHE;
 
   auto stage_k = [&](int s) { return smem + (size_t)s * 2 * TILE; };
   auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
@@ -479,6 +491,11 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   for (int s = 0; s < DECODE_STAGES - 1; ++s) {
     if (s >= fetched && s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
     cp_async_commit();
+  }
+  if (bt_cached) {
+    const int nblk = (kend - 1) / page_size - bt_blk0 + 1;
+    for (int i = threadIdx.x; i < nblk; i += THREADS) bt_cache[i] = bt_blk0 + i < bt_stride ? c.bt[bt_blk0 + i] : -1;
+    c.bt = bt_cache - bt_blk0;
   }
   for (int it = 0; it < n_tiles; ++it) {
     cp_async_wait<DECODE_STAGES - 2>();
