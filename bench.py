@@ -383,6 +383,8 @@ def main() -> int:
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill (for profiling)")
     ap.add_argument("--no-cuda-graphs", action="store_true", help="run decode steps eagerly (for profiling)")
     ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--only-steps", type=int, default=0,
+                    help="for a profiler's launch list: fill the batch, run this many decode steps and stop (no timing, no JSON line)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -409,6 +411,15 @@ def main() -> int:
     full_layers = SHAPES[args.shape][1]["num_hidden_layers"]
     vocab = cfg["vocab_size"]
     nums = model_numbers(engine, cfg)
+
+    if args.only_steps > 0:
+        ids = fill(engine, args.batch, args.context - args.only_steps - warmup - 4, vocab, seed=1000 * args.batch)
+        for _ in range(warmup + args.only_steps):
+            engine.step()
+        drain(engine, ids)
+        torch.cuda.synchronize()
+        print(f"ran {args.only_steps} decode steps of batch {args.batch} at context {args.context} after {warmup} warm-up steps")
+        return 0
 
     # ---- a 2,048-token prompt, whole
     prefill = {} if args.no_prefill else prefill_numbers(engine, cfg, nums, pk)
