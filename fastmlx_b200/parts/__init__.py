@@ -1,6 +1,6 @@
 from .attention import GQAAttention
 from .base import (FeedForward, Mixer, Norm, PagedKVSpec, Part, PositionEncoding, Run, Runtime,
-                   StateSpec, WeightSpec)
+                   StateSpec, StreamEncoding, WeightSpec)
 from .block import PreNormBlock
 from .embedding import Embedding, LMHead
 from .linear import Linear
@@ -10,5 +10,5 @@ from .norm import RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding, inverse_frequencies
 
 __all__ = ["GQAAttention", "FeedForward", "Mixer", "Norm", "PagedKVSpec", "Part", "PositionEncoding",
-           "Run", "Runtime", "StateSpec", "WeightSpec", "PreNormBlock", "Embedding", "LMHead", "Linear",
+           "Run", "Runtime", "StateSpec", "StreamEncoding", "WeightSpec", "PreNormBlock", "Embedding", "LMHead", "Linear",
            "SwiGLU", "Model", "RMSNorm", "NoPositionEncoding", "RotaryEmbedding", "inverse_frequencies"]

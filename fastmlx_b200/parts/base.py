@@ -187,6 +187,16 @@ class PositionEncoding(Part):
         raise NotNative(f"{type(self).__name__} runs in Python only")
 
 
+class StreamEncoding(Part):
+    """Puts positions into the embedding stream itself (learned absolute positions, a sinusoid
+    added to the token embeddings): forward(h[T, d], ctx) -> h', applied once, after the
+    embedding and before the first layer.  `ctx.positions` holds every token's position.  A
+    model whose mixers use it passes them a `NoPositionEncoding`, which only stores k and v."""
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
 @dataclass(frozen=True)
 class Run:
     """One entry of a model's schedule: run `layer`; `cache_from` names an earlier

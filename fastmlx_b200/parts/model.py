@@ -22,8 +22,11 @@ class Model(Part):
 
     def __init__(self, embed: Embedding, layers: Sequence[Part], final_norm: Norm, head: LMHead,
                  schedule: Sequence[Run] | None = None, drop: Sequence[str] = (), vocab_size: int | None = None,
-                 max_positions: int = 0, eos_token_ids: Sequence[int] = ()):
+                 max_positions: int = 0, eos_token_ids: Sequence[int] = (), stream_encoding: Part | None = None):
+        """`stream_encoding`: an optional `StreamEncoding` that puts positions into the embedding
+        stream (architectures whose positions are not applied to q and k)."""
         self.embed, self.layers, self.final_norm, self.head = embed, list(layers), final_norm, head
+        self.stream_encoding = stream_encoding
         self.schedule = list(schedule) if schedule is not None else [Run(i) for i in range(len(self.layers))]
         for pos, run in enumerate(self.schedule):
             if not 0 <= run.layer < len(self.layers):
@@ -37,7 +40,8 @@ class Model(Part):
         self.eos_token_ids = tuple(eos_token_ids)
 
     def children(self):
-        return (self.embed, *self.layers, self.final_norm, self.head)
+        extra = (self.stream_encoding,) if self.stream_encoding is not None else ()
+        return (self.embed, *extra, *self.layers, self.final_norm, self.head)
 
     # ---- what the cache manager must provide, by schedule position
     def cache_needs(self):
@@ -52,7 +56,8 @@ class Model(Part):
     @property
     def graph_safe(self) -> bool:
         """May a decode step of this model be captured in a CUDA graph?"""
-        return all(getattr(layer, "supports_cuda_graph", False) for layer in self.layers)
+        return all(getattr(layer, "supports_cuda_graph", False) for layer in self.layers) and \
+            bool(getattr(self.stream_encoding, "supports_cuda_graph", True))
 
     # ---- weights
     def check_weights(self, tensors: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
@@ -88,6 +93,8 @@ class Model(Part):
         """Logits [len(ctx.logit_rows), vocab] in 32-bit for the batch that `ctx` describes;
         `greedy`: each wanted row's greedy choice instead, int32 [len(ctx.logit_rows)]."""
         delta = self.embed.forward(ctx.tokens, ctx)
+        if self.stream_encoding is not None:
+            delta = self.stream_encoding.forward(delta, ctx)
         residual = None
         for pos, run in enumerate(self.schedule):
             delta, residual = self.layers[run.layer].forward(delta, residual, ctx, ctx.caches[pos])
@@ -106,7 +113,12 @@ class Model(Part):
         for part in (self.embed, self.final_norm, self.head, *self.layers):
             if not hasattr(part, "emit") and not hasattr(part, "emit_after"):
                 raise NotNative(f"{type(part).__name__} runs in Python only")
-        delta, stream = self.embed.emit(b), None
+        if self.stream_encoding is not None:
+            if not hasattr(self.stream_encoding, "emit"):
+                raise NotNative(f"{type(self.stream_encoding).__name__} runs in Python only")
+            delta, stream = self.stream_encoding.emit(b, self.embed.emit(b)), None
+        else:
+            delta, stream = self.embed.emit(b), None
         for pos, run in enumerate(self.schedule):
             delta, stream = self.layers[run.layer].emit(b, delta, stream, pos)
         b.wanted = True                                   # from here on: the wanted rows only

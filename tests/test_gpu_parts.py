@@ -628,3 +628,96 @@ def test_a_window_gives_pages_back_inside_the_engine_loop(tmp_path, dtype):
                     assert gap < slack, (i, tok, best, gap)
     finally:
         registry.unregister(["toy_window"])
+
+
+# ----------------------------------------------------------------------------- positions in the embedding stream
+def make_learned_positions():
+    """Learned absolute positions added to the token embeddings (no rotation of q and k): a
+    `StreamEncoding` defined here, with a table of its own in the checkpoint."""
+    from fastmlx_b200.parts import (Embedding, GQAAttention, LMHead, Model, NoPositionEncoding, PreNormBlock, RMSNorm,
+                                    StreamEncoding, SwiGLU, WeightSpec)
+    from fastmlx_b200.parts.base import to_compute
+
+    class LearnedPositions(StreamEncoding):
+        def __init__(self, max_positions, width, name):
+            self.max_positions, self.width, self.name = max_positions, width, name
+
+        def own_weight_specs(self):
+            return [WeightSpec(self.name + ".weight", (self.max_positions, self.width), "embedding")]
+
+        def bind_own(self, tensors, rt):
+            self.table = to_compute(tensors[self.name + ".weight"], rt)
+
+        def forward(self, h, ctx):
+            pos = ctx.positions.long().clamp(min=0)              # a padding row's position is -1: any row will do
+            return (h.float() + self.table[pos].float()).to(h.dtype)
+
+    @dataclass(frozen=True)
+    class PosCfg:
+        vocab_size: int
+        width: int
+        max_positions: int
+        eos_token_id: int = -1
+
+        @staticmethod
+        def from_dict(d):
+            return PosCfg(int(d["vocab_size"]), int(d["width"]), int(d["max_positions"]))
+
+    def build(cfg):
+        d = cfg.width
+        blocks = [PreNormBlock(GQAAttention(d, 4, 2, 16, NoPositionEncoding(), f"l{i}.attn"), SwiGLU(d, 64, f"l{i}.mlp"),
+                               RMSNorm(d, 1e-5, f"l{i}.n1"), RMSNorm(d, 1e-5, f"l{i}.n2")) for i in range(2)]
+        return Model(Embedding(cfg.vocab_size, d, "emb"), blocks, RMSNorm(d, 1e-5, "norm"), LMHead(cfg.vocab_size, d, "head"),
+                     vocab_size=cfg.vocab_size, max_positions=cfg.max_positions,
+                     stream_encoding=LearnedPositions(cfg.max_positions, d, "pos"))
+
+    return PosCfg, build
+
+
+def plain_learned_positions(W, toks):
+    T = len(toks)
+    h = pl.embedding(torch.tensor(toks), W["emb.weight"]) + W["pos.weight"].double()[:T]
+    for i in range(2):
+        x = pl.rms_norm(h, W[f"l{i}.n1.weight"], 1e-5)
+        q = pl.linear(x, W[f"l{i}.attn.q_proj.weight"]).view(T, 4, 16)
+        k = pl.linear(x, W[f"l{i}.attn.k_proj.weight"]).view(T, 2, 16)
+        v = pl.linear(x, W[f"l{i}.attn.v_proj.weight"]).view(T, 2, 16)
+        h = h + pl.linear(pl.attention(q, k, v, 0.25).reshape(T, 64), W[f"l{i}.attn.o_proj.weight"])
+        h = h + pl.swiglu(pl.rms_norm(h, W[f"l{i}.n2.weight"], 1e-5), W[f"l{i}.mlp.gate_proj.weight"],
+                          W[f"l{i}.mlp.up_proj.weight"], W[f"l{i}.mlp.down_proj.weight"])
+    return pl.linear(pl.rms_norm(h, W["norm.weight"], 1e-5), W["head.weight"])
+
+
+def test_positions_in_the_embedding_stream(tmp_path):
+    """An encoding that is added to the embedding stream instead of applied to q and k: a part of
+    its own kind (`StreamEncoding`), registered from here, replayed under every cut and generated
+    from under graphs."""
+    from fastmlx_b200 import Engine, SamplingParams, registry, write_random_model
+    from fastmlx_b200.engine.replay import Replayer
+    PosCfg, build = make_learned_positions()
+    registry.register(["toy_learned_pos"], PosCfg.from_dict, build, replace=True)
+    try:
+        config = {"model_type": "toy_learned_pos", "vocab_size": 71, "width": 64, "max_positions": 128}
+        d = write_random_model(str(tmp_path / "pos"), config, seed=8)
+        W = tiny.load_plain_weights(d)
+        assert W["pos.weight"].shape == (128, 64)
+        prompts = {f"r{i}": tiny.rand_tokens(n, 71, 60 + i) for i, n in enumerate([23, 40, 5, 33])}
+        ref = {r: plain_learned_positions(W, t) for r, t in prompts.items()}
+        rp = Replayer(d, "float32", 256, page_size=8)
+        assert rp.step_fn.native is None                     # a part defined here: the Python path
+        for cut in (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
+            steps = cut(prompts)
+            rows = traces.collect(steps, [rp.step(s) for s in steps])
+            for r, t in prompts.items():
+                got = torch.tensor([rows[r][i].tolist() for i in range(len(t))], dtype=torch.float64)
+                assert (got - ref[r]).abs().max().item() / ref[r].abs().max().item() < 1e-5, (cut.__name__, r)
+        eng = Engine(d, dtype="float32", block_size=8, max_cache_tokens=512, max_concurrent_requests=4)
+        outs = eng.generate([prompts["r0"], prompts["r2"], prompts["r3"]], SamplingParams(max_tokens=6, temperature=0.0))
+        assert eng.stats()["graph_replays"] > 0
+        for p, o in zip([prompts["r0"], prompts["r2"], prompts["r3"]], outs):
+            seq = list(p)
+            for _ in range(6):
+                seq.append(int(torch.argmax(plain_learned_positions(W, seq)[-1])))
+            assert o.output_token_ids == seq[len(p):]
+    finally:
+        registry.unregister(["toy_learned_pos"])
