@@ -155,3 +155,83 @@ def test_the_native_layout_is_the_python_layout():
             assert d.bt_stride[g] == bt.shape[1]
             assert torch.equal(arr(d.block_tables[g], bt.numel()).view(bt.shape), bt)
             assert torch.equal(arr(d.slot_mapping[g], d.T, torch.int64), ctx.groups[g].slot_mapping.cpu())
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4])
+def test_the_native_layout_is_the_python_layout_on_random_steps(seed):
+    """Random live requests in two cache groups (one with a window, so its tables have -1 holes),
+    random mixes of portions and single tokens, random padding: `fmx_exec_layout` and
+    `build_context` describe every step alike."""
+    import ctypes
+    import random
+    from fastmlx_b200.cache import CacheManager
+    from fastmlx_b200.engine import native as nat
+    from fastmlx_b200.engine.batch import StepEntry, build_context
+    from fastmlx_b200.parts import PagedKVSpec
+    rng = random.Random(seed)
+    ps = rng.choice([4, 8, 16])
+    needs = [(PagedKVSpec(2, 16, 0), None, None), (PagedKVSpec(1, 32, 3 * ps + 1), None, None)]
+    m = CacheManager(needs, page_size=ps, num_pages=400, max_requests=12, dtype=torch.float32, device="cuda")
+    lib = nat.host_library()
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    live = {}
+    for step in range(30):
+        while len(live) < 8 and rng.random() < 0.6:
+            rid = f"r{step}-{len(live)}-{rng.random()}"
+            live[rid] = m.add_request(rid)
+        if not live:
+            continue
+        chosen = rng.sample(sorted(live), rng.randint(1, len(live)))
+        entries = []
+        for rid in chosen:
+            q = 1 if rng.random() < 0.5 else rng.randint(2, 3 * ps + 5)
+            toks = [rng.randrange(1000) for _ in range(q)]
+            entries.append(StepEntry(live[rid], toks, sorted(rng.sample(range(q), rng.randint(0, min(q, 3))))))
+            m.reserve(live[rid], q)
+        pad_rows = rng.choice([0, 0, 8, 16])
+        pad_blocks = rng.choice([0, 0, 16, 64])
+        if pad_rows and any(len(e.tokens) != 1 for e in entries):
+            pad_rows = 0                                    # the Python layout pads one-token steps only
+        ctx = build_context(entries, m, "cuda", status, pad_rows=pad_rows, pad_blocks=pad_blocks)
+        R = len(entries)
+        want, off = [], 0
+        for e in entries:
+            want += [off + w for w in e.want]
+            off += len(e.tokens)
+        flat = np.array([len(e.tokens) for e in entries] + [e.request.length for e in entries] + [e.request.slot for e in entries]
+                        + want + [t for e in entries for t in e.tokens], dtype=np.int32)
+        inp = nat.FmxBatchIn()
+        base = flat.ctypes.data
+        inp.R, inp.n_want = R, len(want)
+        inp.q_lens, inp.ctx_lens, inp.slots = base, base + 4 * R, base + 8 * R
+        inp.want, inp.tokens = base + 12 * R, base + 12 * R + 4 * len(want)
+        inp.pad_rows, inp.pad_blocks, inp.page_size, inp.n_groups = pad_rows, pad_blocks, ps, 2
+        for g, mir in enumerate(m.table_mirror):
+            inp.mirror[g], inp.mirror_cols[g] = mir.ctypes.data, mir.shape[1]
+        ints = lib.fmx_exec_layout_ints(ctypes.byref(inp))
+        host = torch.zeros(ints, dtype=torch.int32).pin_memory()
+        dev = torch.zeros(ints, dtype=torch.int32, device="cuda")
+        d = nat.FmxStepDesc()
+        assert lib.fmx_exec_layout(ctypes.byref(inp), host.data_ptr(), dev.data_ptr(), ints, ctypes.byref(d),
+                                   torch.cuda.current_stream().cuda_stream) == 0
+        torch.cuda.synchronize()
+
+        def arr(ptr, n, dtype=torch.int32):
+            o = (ptr - dev.data_ptr()) // 4
+            return dev[o: o + n * (2 if dtype == torch.int64 else 1)].view(dtype).cpu()
+        assert (d.T, d.R, d.max_q_len, d.max_ctx_after, d.all_decode) == (ctx.T, ctx.R, ctx.max_q_len, ctx.max_ctx_after, int(ctx.all_decode))
+        for name, n in (("tokens", d.T), ("positions", d.T), ("token_row", d.T), ("row_start", d.R + 1), ("row_ctx", d.R),
+                        ("row_slot", d.R)):
+            assert torch.equal(arr(getattr(d, name), n), getattr(ctx, name).cpu()), (step, name)
+        if want:
+            assert torch.equal(arr(d.want, len(want)), ctx.logit_rows.cpu())
+        for g in range(2):
+            bt = ctx.groups[g].block_tables.cpu()
+            assert torch.equal(arr(d.block_tables[g], bt.numel()).view(bt.shape), bt), (step, g)
+            assert torch.equal(arr(d.slot_mapping[g], d.T, torch.int64), ctx.groups[g].slot_mapping.cpu()), (step, g)
+        for e in entries:
+            m.commit(e.request)
+        m.check()
+        for rid in [r for r in sorted(live) if rng.random() < 0.15]:
+            m.free(rid)
+            del live[rid]
