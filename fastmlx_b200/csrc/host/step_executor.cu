@@ -435,8 +435,12 @@ FMX_EXPORT int fmx_exec_layout(const FmxBatchIn* in, int* host, int* dev, long l
     }
     for (; t < L.Tp; ++t) sm[t] = -1;
   }
-  cudaError_t e = cudaMemcpyAsync(dev, host, (size_t)L.total * sizeof(int), cudaMemcpyHostToDevice, stream);
-  if (e != cudaSuccess) return fmx_fail("copying the step's description to the device: %s", cudaGetErrorString(e));
+  if (dev == nullptr) {
+    dev = host;                                          // no device: the description's pointers then point into `host`
+  } else {
+    cudaError_t e = cudaMemcpyAsync(dev, host, (size_t)L.total * sizeof(int), cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fmx_fail("copying the step's description to the device: %s", cudaGetErrorString(e));
+  }
   desc->T = L.Tp;
   desc->R = L.Rp;
   desc->n_want = in->n_want;

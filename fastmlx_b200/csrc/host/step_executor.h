@@ -127,6 +127,7 @@ long long fmx_exec_arena_bytes(void* exec, int T);
 long long fmx_exec_layout_ints(const FmxBatchIn* in);
 // Lay the step out into `host` (>= fmx_exec_layout_ints ints, pinned), copy it to `dev` on the stream and fill the
 // pointers of `desc` (T, R, n_want, the sizes and every array); workspaces, arena, logits and status are the caller's.
+// dev == null: nothing is copied and the pointers of `desc` point into `host` (how the layout is tested without a GPU).
 int fmx_exec_layout(const FmxBatchIn* in, int* host, int* dev, long long capacity_ints, FmxStepDesc* desc,
                     cudaStream_t stream);
 // Run the program over a laid-out step.  -> 0, or non-zero after leaving a text for fmx_last_error().
