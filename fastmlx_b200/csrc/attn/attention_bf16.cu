@@ -39,10 +39,18 @@ constexpr int TILE = BN * ROW;           // elements of one K (or V) tile
 constexpr int THREADS = 128;
 constexpr int PREFILL_STAGES = HD <= 128 ? 3 : 2;
 constexpr int DECODE_STAGES = HD <= 128 ? 3 : 2;
+// A deeper ring for grids that leave room for it: with few blocks on an SM two tiles in flight per block do not
+// cover the latency of HBM (batch 1 at head size 64: a tile per microsecond and block, whatever the bandwidth).
+// As many stages as still let two blocks share an SM, at most 8; head sizes whose ring of DECODE_STAGES already
+// takes half an SM have no deeper one.
+constexpr int MO_ROW = HD + 4;           // floats in a row of a warp's partial output: heads 2t and 2t + 2 on other banks
+constexpr int DEEP_FIT = (int)((226 * 1024 / 2) / (2 * 64 * (HD + 8) * 2));
+constexpr int DEEP_STAGES = DEEP_FIT > 8 ? 8 : DEEP_FIT > DECODE_STAGES ? DEEP_FIT : DECODE_STAGES;
 constexpr float LOG2E = 1.4426950408889634f;
 // Block-table entries a decode block keeps in shared memory.  From head size 128 on (two blocks of four warps
-// per SM: little to hide the table read behind) it takes a tenth off the kernel; at head size 64 (four blocks
-// per SM) it cost 3 to 5 %, so there the tiles' copies keep reading the table itself.
+// per SM: little to hide the table read behind) it takes a tenth off the kernel; at head size 64 it cost 3 to 5 %
+// with four blocks per SM and, with the few blocks of batch 1, won 7 % over 131,072 keys and lost 8 % over 8,192,
+// so there the tiles' copies keep reading the table itself.
 constexpr int BT_CACHE = HD < 128 ? 0 : 1024;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -101,6 +109,31 @@ __device__ __forceinline__ void load_tiles(bf16* kdst, bf16* vdst, const Cache& 
   const long long plane = (long long)c.nkv * c.page_size * HD;          // k plane -> v plane
   const long long page_stride = 2 * plane;
   const bf16* base = c.kv + (long long)g * c.page_size * HD;
+  if (c.page_shift >= 0 && k0 >= kbeg && k0 + BN <= kend) {
+    // A tile inside the range (all but the first and last of a block): no key needs a test, and what does not
+    // depend on the tile (the thread's chunk, its place in the shared tile) folds into the copies' offsets.
+    const unsigned kbase = (unsigned)__cvta_generic_to_shared(kdst), vbase = (unsigned)__cvta_generic_to_shared(vdst);
+#pragma unroll
+    for (int it = 0; it < ((BN / 4) * CHUNKS + THREADS - 1) / THREADS; ++it) {
+      const int item = threadIdx.x + it * THREADS;
+      if (((BN / 4) * CHUNKS) % THREADS != 0 && item >= (BN / 4) * CHUNKS) break;
+      const int rg = item / CHUNKS, ch = item - rg * CHUNKS;
+      const int key0 = k0 + 4 * rg;
+      const int blk = key0 >> c.page_shift;
+      const int page = blk < c.bt_len ? c.bt[blk] : -1;
+      const bool have = page >= 0 && page < c.num_pages;
+      if (!have) fmx_set_status(status, FMX_BAD_PAGE, page, where);
+      const bf16* src = have ? base + page * page_stride + (long long)(key0 & (c.page_size - 1)) * HD + ch * 8 : c.kv;
+      const int n = have ? 16 : 0;                     // 0: zeros, and nothing is read (the offsets stay inside page 0)
+      const unsigned off = (unsigned)(((4 * rg) * ROW + ch * 8) * 2);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(kbase + off + i * ROW * 2), "l"(src + i * HD), "r"(n));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vbase + off + i * ROW * 2), "l"(src + i * HD + plane), "r"(n));
+      }
+    }
+    return;
+  }
   if (c.page_shift >= 0) {
     for (int item = threadIdx.x; item < (BN / 4) * CHUNKS; item += THREADS) {
       const int rg = item / CHUNKS, ch = item - rg * CHUNKS;
@@ -231,6 +264,94 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
   }
 }
 
+// ---- decode: keys on the rows ----
+// A decode row brings the few query heads of one kv head (4 with Llama's grouping).  With the heads on the 16 rows
+// of the MMA three quarters of every product were padding; here the keys are the rows and up to 8 heads the
+// columns: S^T = K . Q^T, O^T += V^T . P^T.  Per 16 keys that is HD/16 products for the scores and HD/16 for the
+// output (half of what the other orientation took), four scores per thread instead of eight, and an accumulator of
+// half the size.  The probabilities leave the score product as its C fragment (keys g, g+8; heads 2t, 2t+1) and
+// enter the output product as a B fragment (keys 2t, 2t+1, 2t+8, 2t+9; head g): one movmatrix each way.
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+  unsigned d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+
+// s[nh] (16 keys x 8 heads) = K rows [key_row0, +16) of a shared tile . Q^T; q[nh][k]: the B fragments of head
+// group nh at k-step k.  Two accumulators take alternate k-steps so that the products do not form one chain.
+template <int NH>
+__device__ __forceinline__ void qk_keys(float (&s)[NH][4], const unsigned (&q)[NH][KSTEPS][2], const bf16* ks, int key_row0) {
+  const int lane = threadIdx.x & 31, mi = lane >> 3, ri = lane & 7;
+  // matrices: (keys 0-7, hd 16k), (keys 8-15, hd 16k), (keys 0-7, hd 16k+8), (keys 8-15, hd 16k+8)
+  const bf16* p = ks + (key_row0 + (mi & 1) * 8 + ri) * ROW + (mi >> 1) * 8;
+  float s2[NH][4];
+#pragma unroll
+  for (int h = 0; h < NH; ++h)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[h][e] = s2[h][e] = 0.f;
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+    unsigned a[4];
+    ldmatrix_x4(a[0], a[1], a[2], a[3], p + 16 * k);
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+      if (k & 1) mma_bf16(s2[h], a, q[h][k][0], q[h][k][1]);
+      else mma_bf16(s[h], a, q[h][k][0], q[h][k][1]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < NH; ++h)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[h][e] += s2[h][e];
+}
+
+// One step of the online softmax for the heads (2t, 2t+1) of each group that a thread holds, over the 16 keys
+// key0 + {g, g+8}; keys outside [kfirst, klast] are masked when MASK.  m, l, alpha are per head and the same in the
+// eight lanes that share t (l is each lane's share until the end).  Leaves the probabilities as B fragments.
+template <int NH, bool MASK>
+__device__ __forceinline__ void softmax_keys(float (&s)[NH][4], float (&m)[NH][2], float (&l)[NH][2], float (&alpha)[NH][2],
+                                             unsigned (&pb)[NH][2], float sl2, int key0, int kfirst, int klast) {
+  const int g = (threadIdx.x & 31) >> 2;
+  const bool ok0 = !MASK || (key0 + g >= kfirst && key0 + g <= klast);
+  const bool ok1 = !MASK || (key0 + g + 8 >= kfirst && key0 + g + 8 <= klast);
+#pragma unroll
+  for (int h = 0; h < NH; ++h) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float v0 = ok0 ? s[h][j] * sl2 : -INFINITY, v1 = ok1 ? s[h][2 + j] * sl2 : -INFINITY;
+      float mx = fmaxf(v0, v1);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m[h][j], mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      alpha[h][j] = fast_exp2(m[h][j] - m_use);
+      m[h][j] = m_new;
+      const float p0 = fast_exp2(v0 - m_use), p1 = fast_exp2(v1 - m_use);
+      s[h][j] = p0;
+      s[h][2 + j] = p1;
+      l[h][j] = l[h][j] * alpha[h][j] + p0 + p1;
+    }
+    pb[h][0] = movmatrix_trans(pack_bf16(s[h][0], s[h][1]));
+    pb[h][1] = movmatrix_trans(pack_bf16(s[h][2], s[h][3]));
+  }
+}
+
+// o[nh][n] (hd 16n + {g, g+8} x heads 2t, 2t+1) += V^T of the key rows [key_row0, +16) . P^T
+template <int NH>
+__device__ __forceinline__ void pv_keys(float (&o)[NH][HD / 16][4], const unsigned (&pb)[NH][2], const bf16* vs, int key_row0) {
+  const int lane = threadIdx.x & 31, mi = lane >> 3, ri = lane & 7;
+  // matrices (transposed on the way): (keys 0-7, hd 16n), (keys 0-7, hd 16n+8), (keys 8-15, hd 16n), (keys 8-15, hd 16n+8)
+  const bf16* p = vs + (key_row0 + (mi >> 1) * 8 + ri) * ROW + (mi & 1) * 8;
+#pragma unroll
+  for (int n = 0; n < HD / 16; ++n) {
+    unsigned a[4];
+    ldmatrix_x4_trans(a[0], a[1], a[2], a[3], p + 16 * n);
+#pragma unroll
+    for (int h = 0; h < NH; ++h) mma_bf16(o[h][n], a, pb[h][0], pb[h][1]);
+  }
+}
+
 // ------------------------------------------------------------------------------------ prefill
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kv,
@@ -349,6 +470,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
 // ------------------------------------------------------------------------------------ decode
 // part_o: [R, nkv, splits, 16, HD] float; part_ml: [R, nkv, splits, 16, 2] float (max in the
 // scaled log2 domain, sum).  With one split the output is written directly.
+template <int STAGES, int NH>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int* block_tables, int bt_stride,
                    const int* row_start, const int* positions, bf16* out, float* part_o, float* part_ml, int nh, int nkv,
@@ -378,9 +500,10 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   // copies: the profile's long-scoreboard stalls).  Ranges beyond the cache keep reading the table itself.
   // The first tiles go out with addresses read from the table itself; the cache is filled behind them and
   // used from the loop's first pass on (whose barrier makes it visible).
-  __shared__ int bt_cache[BT_CACHE > 0 ? BT_CACHE : 1];
+  constexpr int BTC = BT_CACHE;
+  __shared__ int bt_cache[BTC > 0 ? BTC : 1];
   const int bt_blk0 = kstart / page_size;
-  const bool bt_cached = BT_CACHE > 0 && n_tiles > 0 && (kend - 1) / page_size - bt_blk0 + 1 <= BT_CACHE;
+  const bool bt_cached = BTC > 0 && n_tiles > 0 && (kend - 1) / page_size - bt_blk0 + 1 <= BTC;
 
   auto stage_k = [&](int s) { return smem + (size_t)s * 2 * TILE; };
   auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
@@ -388,7 +511,7 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   // fetched while the kernel ahead (which writes the new key and the queries) is still running.
   int fetched = 0;
 #pragma unroll
-  for (int s = 0; s < DECODE_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (fetched == s && s < n_tiles && min(kend, kstart + (s + 1) * BN) <= pos) {
       load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
       fetched = s + 1;
@@ -397,7 +520,7 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   // The last stage of the ring is free until the first pass of the loop below: with rotation in
   // this kernel it holds the rotated queries and the row's sines and cosines meanwhile.  Those
   // depend on the position alone, so they too are ready before the kernel ahead has finished.
-  bf16* q_rot = stage_k(DECODE_STAGES - 1);            // [16][HD]
+  bf16* q_rot = stage_k(STAGES - 1);            // [16][HD]
   float* rope_sin = reinterpret_cast<float*>(q_rot + 16 * HD);
   float* rope_cos = rope_sin + HD / 2;
   static_assert(16 * HD * 2 + HD * 4 <= TILE * 2, "the rotated queries must fit one K tile");
@@ -465,30 +588,35 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
     qbase = q_rot;
   }
 
-  unsigned qf[KSTEPS][4];
+  // the queries as B fragments: head 8 h + gq, k = 16 k + 2 tq (+8)
+  unsigned qf[NH][KSTEPS][2];
 #pragma unroll
-  for (int k = 0; k < KSTEPS; ++k)
+  for (int h = 0; h < NH; ++h) {
+    const int head = 8 * h + gq;
+    const bool ok = head < rep;
+    const bf16* qp = qbase + (long long)(ok ? head : 0) * qhead_stride + 2 * tq;
 #pragma unroll
-    for (int x = 0; x < 2; ++x) {
-      const int hrow = gq + 8 * x;
-      const bool ok = hrow < rep;
-      const bf16* qp = qbase + (long long)(ok ? hrow : 0) * qhead_stride + 16 * k + 2 * tq;
-      qf[k][x] = ok ? *reinterpret_cast<const unsigned*>(qp) : 0u;
-      qf[k][x + 2] = ok ? *reinterpret_cast<const unsigned*>(qp + 8) : 0u;
+    for (int k = 0; k < KSTEPS; ++k) {
+      qf[h][k][0] = ok ? *reinterpret_cast<const unsigned*>(qp + 16 * k) : 0u;
+      qf[h][k][1] = ok ? *reinterpret_cast<const unsigned*>(qp + 16 * k + 8) : 0u;
     }
-  const int lim[2] = {kend - 1, kend - 1};
-  const int lo[2] = {kbeg, kbeg};
+  }
   const float sl2 = scale * LOG2E;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  float o[NT_O][4];
+  float m[NH][2], l[NH][2];
+  float o[NH][HD / 16][4];
 #pragma unroll
-  for (int n = 0; n < NT_O; ++n)
+  for (int h = 0; h < NH; ++h) {
+    m[h][0] = m[h][1] = -INFINITY;
+    l[h][0] = l[h][1] = 0.f;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    for (int n = 0; n < HD / 16; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[h][n][e] = 0.f;
+  }
 
   // the groups of the pipeline: tile s is in group s, whether it went out before the wait or not
 #pragma unroll
-  for (int s = 0; s < DECODE_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s >= fetched && s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
     cp_async_commit();
   }
@@ -498,56 +626,58 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
     c.bt = bt_cache - bt_blk0;
   }
   for (int it = 0; it < n_tiles; ++it) {
-    cp_async_wait<DECODE_STAGES - 2>();
+    cp_async_wait<STAGES - 2>();
     __syncthreads();
-    const int nx = it + DECODE_STAGES - 1;
+    const int nx = it + STAGES - 1;
     if (nx < n_tiles)
-      load_tiles(stage_k(nx % DECODE_STAGES), stage_v(nx % DECODE_STAGES), c, g, kstart + nx * BN, kbeg, kend, status, r);
+      load_tiles(stage_k(nx % STAGES), stage_v(nx % STAGES), c, g, kstart + nx * BN, kbeg, kend, status, r);
     cp_async_commit();
-    const bf16* ks = stage_k(it % DECODE_STAGES);
-    const bf16* vs = stage_v(it % DECODE_STAGES);
-    float s[2][4];
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-    qk_tile<2>(s, qf, ks, warp * 16);
-    float alpha[2];
+    const bf16* ks = stage_k(it % STAGES);
+    const bf16* vs = stage_v(it % STAGES);
+    float s[NH][4], alpha[NH][2];
+    unsigned pb[NH][2];
+    qk_keys<NH>(s, qf, ks, warp * 16);
     const int wk0 = kstart + it * BN + warp * 16;
     if (wk0 >= kbeg && wk0 + 15 < kend)
-      softmax_step<2, false>(s, m, l, alpha, sl2, wk0, lim, lo);
+      softmax_keys<NH, false>(s, m, l, alpha, pb, sl2, wk0, kbeg, kend - 1);
     else
-      softmax_step<2, true>(s, m, l, alpha, sl2, wk0, lim, lo);
+      softmax_keys<NH, true>(s, m, l, alpha, pb, sl2, wk0, kbeg, kend - 1);
 #pragma unroll
-    for (int n = 0; n < NT_O; ++n) {
-      o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
-      o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
-    }
-    pv_tile<1>(o, s, vs, warp * 16);
+    for (int h = 0; h < NH; ++h)
+#pragma unroll
+      for (int n = 0; n < HD / 16; ++n) {
+        o[h][n][0] *= alpha[h][0]; o[h][n][1] *= alpha[h][1];
+        o[h][n][2] *= alpha[h][0]; o[h][n][3] *= alpha[h][1];
+      }
+    pv_keys<NH>(o, pb, vs, warp * 16);
   }
   cp_async_wait<0>();
   __syncthreads();                                   // the tiles are done with; reuse the memory
   pdl_trigger();                                     // the block's loads are done: room for the next kernel's
 
-  // merge the four warps: each leaves (m, l, o) of its 16 rows
-  float* mo = reinterpret_cast<float*>(smem_raw);    // [4][16][HD]
-  float* mml = mo + 4 * 16 * HD;                     // [4][16][2]
+  // merge the four warps: each leaves (m, l, o) of its up to 16 heads
+  float* mo = reinterpret_cast<float*>(smem_raw);    // [4][16][MO_ROW]
+  float* mml = mo + 4 * 16 * MO_ROW;                 // [4][16][2]
 #pragma unroll
-  for (int x = 0; x < 2; ++x) {
-    l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
-    l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
-    const int row = gq + 8 * x;
-    float* dst = mo + ((size_t)warp * 16 + row) * HD + 2 * tq;
+  for (int h = 0; h < NH; ++h)
 #pragma unroll
-    for (int n = 0; n < NT_O; ++n) {
-      dst[8 * n] = o[n][2 * x];
-      dst[8 * n + 1] = o[n][2 * x + 1];
+    for (int j = 0; j < 2; ++j) {
+      float lj = l[h][j];                            // the lanes that share tq hold the shares of this head's sum
+      lj += __shfl_xor_sync(0xffffffffu, lj, 4);
+      lj += __shfl_xor_sync(0xffffffffu, lj, 8);
+      lj += __shfl_xor_sync(0xffffffffu, lj, 16);
+      const int row = 8 * h + 2 * tq + j;
+      float* dst = mo + ((size_t)warp * 16 + row) * MO_ROW + gq;
+#pragma unroll
+      for (int n = 0; n < HD / 16; ++n) {
+        dst[16 * n] = o[h][n][j];
+        dst[16 * n + 8] = o[h][n][2 + j];
+      }
+      if (gq == 0) {
+        mml[(warp * 16 + row) * 2] = m[h][j];
+        mml[(warp * 16 + row) * 2 + 1] = lj;
+      }
     }
-    if (tq == 0) {
-      mml[(warp * 16 + row) * 2] = m[x];
-      mml[(warp * 16 + row) * 2 + 1] = l[x];
-    }
-  }
   __syncthreads();
   for (int idx = threadIdx.x; idx < rep * HD; idx += THREADS) {
     const int row = idx / HD, d = idx - row * HD;
@@ -560,7 +690,7 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
     for (int w = 0; w < 4; ++w) {
       const float f = exp2f(mml[(w * 16 + row) * 2] - Mu);
       L += f * mml[(w * 16 + row) * 2 + 1];
-      acc += f * mo[((size_t)w * 16 + row) * HD + d];
+      acc += f * mo[((size_t)w * 16 + row) * MO_ROW + d];
     }
     if (splits == 1) {
       out[((long long)t * nh + g * rep + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
@@ -647,11 +777,37 @@ __global__ void attn_combine_kernel(const float* part_o, const float* part_ml, c
 }
 
 constexpr size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * TILE * sizeof(bf16); }
-constexpr size_t decode_smem() {
-  const size_t pipe = (size_t)DECODE_STAGES * 2 * TILE * sizeof(bf16);
-  const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+constexpr size_t decode_smem(int stages = DECODE_STAGES) {
+  const size_t pipe = (size_t)stages * 2 * TILE * sizeof(bf16);
+  const size_t merge = (size_t)(4 * 16 * MO_ROW + 4 * 16 * 2) * sizeof(float);
   return pipe > merge ? pipe : merge;
 }
+// The deeper ring, where the head size has one and the whole grid is resident with it.
+bool decode_deep(dim3 grid) {
+  if (DEEP_STAGES <= DECODE_STAGES) return false;
+  const long long per_sm = (226 * 1024) / (long long)decode_smem(DEEP_STAGES);
+  return (long long)grid.x * grid.y * grid.z <= per_sm * fmx_num_sms();
+}
+template <int STAGES, int NH> cudaError_t configure_decode_one() {
+  return cudaFuncSetAttribute(attn_decode_kernel<STAGES, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)decode_smem(STAGES));
+}
+cudaError_t configure_decode() {
+  cudaError_t e = configure_decode_one<DECODE_STAGES, 1>();
+  if (e == cudaSuccess) e = configure_decode_one<DECODE_STAGES, 2>();
+  if (e == cudaSuccess && DEEP_STAGES > DECODE_STAGES) e = configure_decode_one<DEEP_STAGES, 1>();
+  if (e == cudaSuccess && DEEP_STAGES > DECODE_STAGES) e = configure_decode_one<DEEP_STAGES, 2>();
+  return e;
+}
+// The instantiation for a grid and a number of query heads per kv head: LAUNCH(stages, head groups of 8).
+#define FMX_DECODE_DISPATCH(grid, rep, LAUNCH)            \
+  do {                                                    \
+    if (decode_deep(grid)) {                              \
+      if ((rep) <= 8) { LAUNCH(DEEP_STAGES, 1); } else { LAUNCH(DEEP_STAGES, 2); }      \
+    } else {                                              \
+      if ((rep) <= 8) { LAUNCH(DECODE_STAGES, 1); } else { LAUNCH(DECODE_STAGES, 2); }  \
+    }                                                     \
+  } while (0)
 }  // namespace
 
 FMX_EXPORT int fmx_attn_head_dim() { return HD; }
@@ -726,18 +882,20 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
     return fmx_fail("fmx_attn_decode: scratch of %lld floats given, %lld needed", scratch_floats, need);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)decode_smem());
-    if (e != cudaSuccess) return fmx_fail("fmx_attn_decode: shared memory of %zu bytes refused: %s", decode_smem(),
-                                          cudaGetErrorString(e));
+    cudaError_t e = configure_decode();
+    if (e != cudaSuccess) return fmx_fail("fmx_attn_decode: shared memory of %zu bytes refused: %s",
+                                          decode_smem(DEEP_STAGES), cudaGetErrorString(e));
     configured = true;
   }
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (long long)rows * nkv * splits * 16 * HD : nullptr;
   dim3 grid(splits, nkv, rows);
-  fmx_launch(attn_decode_kernel, grid, dim3(THREADS), decode_smem(), stream,
-      (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
-      part_ml, nh, nkv, page_size, num_pages, scale, window, status, tickets, inv_freq, rot, interleaved, rope_mode);
+#define FMX_DECODE_LAUNCH(ST, NHG)                                                                                    \
+  fmx_launch(attn_decode_kernel<ST, NHG>, grid, dim3(THREADS), decode_smem(ST), stream, (const bf16*)q, q_stride,       \
+             (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o, part_ml, nh, nkv,      \
+             page_size, num_pages, scale, window, status, tickets, inv_freq, rot, interleaved, rope_mode)
+  FMX_DECODE_DISPATCH(grid, nh / nkv, FMX_DECODE_LAUNCH);
+#undef FMX_DECODE_LAUNCH
   FMX_LAUNCH_CHECK();
   if (splits > 1 && tickets == nullptr) {
     fmx_launch(attn_combine_kernel, dim3(nh, rows), dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)part_o,
@@ -779,9 +937,9 @@ int noalloc_setup(float** ptr, cudaStream_t stream) {
     e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
     if (e != cudaSuccess || p == nullptr)
       return fmx_fail("fmx_attn_decode_noalloc: cudaGetSymbolAddress on device %d: %s", dev, cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem());
+    e = configure_decode();
     if (e != cudaSuccess)
-      return fmx_fail("fmx_attn_decode_noalloc: shared memory of %zu bytes refused: %s", decode_smem(),
+      return fmx_fail("fmx_attn_decode_noalloc: shared memory of %zu bytes refused: %s", decode_smem(DEEP_STAGES),
                       cudaGetErrorString(e));
     g_noalloc_ptr[dev] = p;
   }
@@ -816,9 +974,12 @@ FMX_EXPORT int fmx_attn_decode_noalloc(const void* q, long long q_stride, const 
   float* part_o = scratch;
   float* part_ml = scratch + (long long)rows * nkv * splits * 16 * HD;
   dim3 grid(splits, nkv, rows);
-  attn_decode_kernel<<<grid, THREADS, decode_smem(), stream>>>(
-      (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,
-      part_ml, nh, nkv, page_size, num_pages, scale, window, status, (int*)nullptr, (const float*)nullptr, 0, 0, 0);
+#define FMX_DECODE_LAUNCH(ST, NHG)                                                                                    \
+  attn_decode_kernel<ST, NHG><<<grid, THREADS, decode_smem(ST), stream>>>(                                              \
+      (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,     \
+      part_ml, nh, nkv, page_size, num_pages, scale, window, status, (int*)nullptr, (const float*)nullptr, 0, 0, 0)
+  FMX_DECODE_DISPATCH(grid, nh / nkv, FMX_DECODE_LAUNCH);
+#undef FMX_DECODE_LAUNCH
   FMX_LAUNCH_CHECK();
   if (splits > 1) {
     attn_combine_kernel<<<dim3(nh, rows), HD < 128 ? 64 : 128, 0, stream>>>(part_o, part_ml, row_start, (bf16*)out, nh,
