@@ -39,20 +39,13 @@ constexpr int TILE = BN * ROW;           // elements of one K (or V) tile
 constexpr int THREADS = 128;
 constexpr int PREFILL_STAGES = HD <= 128 ? 3 : 2;
 constexpr int DECODE_STAGES = HD <= 128 ? 3 : 2;
-// A deeper ring for grids that leave room for it: with few blocks on an SM two tiles in flight per block do not
-// cover the latency of HBM (batch 1 at head size 64: a tile per microsecond and block, whatever the bandwidth).
-// As many stages as still let two blocks share an SM, at most 8; head sizes whose ring of DECODE_STAGES already
-// takes half an SM have no deeper one.
 constexpr int MO_ROW = HD + 4;           // floats in a row of a warp's partial output: heads 2t and 2t + 2 on other banks
-constexpr int DEEP_FIT = (int)((226 * 1024 / 2) / (2 * 64 * (HD + 8) * 2));
-constexpr int DEEP_STAGES = DEEP_FIT > 8 ? 8 : DEEP_FIT > DECODE_STAGES ? DEEP_FIT : DECODE_STAGES;
+// Groups of 16 keys in a warp's decode tile.  Grids of few blocks (batch 1 to 4 with 8 kv heads) are bound by the
+// chain of one pass of the loop, not by bandwidth: there a pass takes 32 keys per warp where two blocks of that
+// ring still share an SM (head sizes up to 64).  Measured at head size 64, batch 1 over 131,072 keys: 16 keys a
+// pass 56.8 us, 32 keys 51.5; batch 8 over 8,192: 28.5 and 28.9.
+constexpr int FEW_KG = (2 * 3 * 2 * 4 * 32 * (HD + 8) * 2 <= 226 * 1024) ? 2 : 1;
 constexpr float LOG2E = 1.4426950408889634f;
-// Block-table entries a decode block keeps in shared memory.  From head size 128 on (two blocks of four warps
-// per SM: little to hide the table read behind) it takes a tenth off the kernel; at head size 64 it cost 3 to 5 %
-// with four blocks per SM and, with the few blocks of batch 1, won 7 % over 131,072 keys and lost 8 % over 8,192,
-// so there the tiles' copies keep reading the table itself.
-constexpr int BT_CACHE = HD < 128 ? 0 : 1024;
-
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   const int n = valid ? 16 : 0;
@@ -305,21 +298,34 @@ __device__ __forceinline__ void qk_keys(float (&s)[NH][4], const unsigned (&q)[N
     for (int e = 0; e < 4; ++e) s[h][e] += s2[h][e];
 }
 
-// One step of the online softmax for the heads (2t, 2t+1) of each group that a thread holds, over the 16 keys
-// key0 + {g, g+8}; keys outside [kfirst, klast] are masked when MASK.  m, l, alpha are per head and the same in the
-// eight lanes that share t (l is each lane's share until the end).  Leaves the probabilities as B fragments.
-template <int NH, bool MASK>
-__device__ __forceinline__ void softmax_keys(float (&s)[NH][4], float (&m)[NH][2], float (&l)[NH][2], float (&alpha)[NH][2],
-                                             unsigned (&pb)[NH][2], float sl2, int key0, int kfirst, int klast) {
+// One step of the online softmax for the heads (2t, 2t+1) of each head group that a thread holds, over the 16 KG keys
+// key0 + 16 kg + {g, g+8}; keys outside [kfirst, klast] are masked when MASK.  m, l, alpha are per head and the same
+// in the eight lanes that share t (l is each lane's share until the end).  Leaves the probabilities as B fragments.
+template <int NH, int KG, bool MASK>
+__device__ __forceinline__ void softmax_keys(float (&s)[KG][NH][4], float (&m)[NH][2], float (&l)[NH][2], float (&alpha)[NH][2],
+                                             unsigned (&pb)[KG][NH][2], float sl2, int key0, int kfirst, int klast) {
   const int g = (threadIdx.x & 31) >> 2;
-  const bool ok0 = !MASK || (key0 + g >= kfirst && key0 + g <= klast);
-  const bool ok1 = !MASK || (key0 + g + 8 >= kfirst && key0 + g + 8 <= klast);
+  bool ok[KG][2];
+#pragma unroll
+  for (int kg = 0; kg < KG; ++kg)
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const int key = key0 + 16 * kg + g + 8 * x;
+      ok[kg][x] = !MASK || (key >= kfirst && key <= klast);
+    }
 #pragma unroll
   for (int h = 0; h < NH; ++h) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      const float v0 = ok0 ? s[h][j] * sl2 : -INFINITY, v1 = ok1 ? s[h][2 + j] * sl2 : -INFINITY;
-      float mx = fmaxf(v0, v1);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int kg = 0; kg < KG; ++kg)
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const float v = ok[kg][x] ? s[kg][h][2 * x + j] * sl2 : -INFINITY;
+          s[kg][h][2 * x + j] = v;
+          mx = fmaxf(mx, v);
+        }
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
@@ -327,13 +333,22 @@ __device__ __forceinline__ void softmax_keys(float (&s)[NH][4], float (&m)[NH][2
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       alpha[h][j] = fast_exp2(m[h][j] - m_use);
       m[h][j] = m_new;
-      const float p0 = fast_exp2(v0 - m_use), p1 = fast_exp2(v1 - m_use);
-      s[h][j] = p0;
-      s[h][2 + j] = p1;
-      l[h][j] = l[h][j] * alpha[h][j] + p0 + p1;
+      float sum = 0.f;
+#pragma unroll
+      for (int kg = 0; kg < KG; ++kg)
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const float pr = fast_exp2(s[kg][h][2 * x + j] - m_use);
+          s[kg][h][2 * x + j] = pr;
+          sum += pr;
+        }
+      l[h][j] = l[h][j] * alpha[h][j] + sum;
     }
-    pb[h][0] = movmatrix_trans(pack_bf16(s[h][0], s[h][1]));
-    pb[h][1] = movmatrix_trans(pack_bf16(s[h][2], s[h][3]));
+#pragma unroll
+    for (int kg = 0; kg < KG; ++kg) {
+      pb[kg][h][0] = movmatrix_trans(pack_bf16(s[kg][h][0], s[kg][h][1]));
+      pb[kg][h][1] = movmatrix_trans(pack_bf16(s[kg][h][2], s[kg][h][3]));
+    }
   }
 }
 
@@ -349,6 +364,87 @@ __device__ __forceinline__ void pv_keys(float (&o)[NH][HD / 16][4], const unsign
     ldmatrix_x4_trans(a[0], a[1], a[2], a[3], p + 16 * n);
 #pragma unroll
     for (int h = 0; h < NH; ++h) mma_bf16(o[h][n], a, pb[h][0], pb[h][1]);
+  }
+}
+
+// ---- decode: a stream of tiles per warp ----
+// Each warp of a decode block walks a quarter of the block's keys by itself: its own ring of tiles of 16 KG keys in
+// shared memory, filled by its own lanes' copies and waited for with cp.async.wait_group and a warp barrier.  No
+// block barrier stands in the loop, so a warp never waits for a slower one, and the block-table entries of the next
+// tile can be read a pass ahead into registers (a block barrier would have made the warp wait for them at once).
+template <int KG> struct WarpTile {
+  static constexpr int TK = 16 * KG;                        // keys per tile
+  static constexpr int ELEMS = TK * ROW;                    // elements of a K (or V) tile
+  static constexpr int ITEMS = (TK / 4) * CHUNKS;           // (four keys, one 16-byte chunk)
+  static constexpr int PER_LANE = (ITEMS + 31) / 32;
+};
+
+template <int KG>
+__device__ __forceinline__ void warp_fetch_pages(int (&pg)[WarpTile<KG>::PER_LANE], const Cache& c, int k0) {
+  using W = WarpTile<KG>;
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int i = 0; i < W::PER_LANE; ++i) {
+    const int item = lane + 32 * i;
+    const int blk = (k0 + 4 * (item / CHUNKS)) >> c.page_shift;
+    pg[i] = (item < W::ITEMS && blk < c.bt_len) ? c.bt[blk] : -1;
+  }
+}
+
+// A tile that lies inside the warp's range, pages of a power of two: the entries come in registers.
+template <int KG>
+__device__ __forceinline__ void warp_tile_inside(bf16* kdst, bf16* vdst, const Cache& c, int g, int k0,
+                                                 const int (&pg)[WarpTile<KG>::PER_LANE], int* status, int where) {
+  using W = WarpTile<KG>;
+  const int lane = threadIdx.x & 31;
+  const long long plane = (long long)c.nkv * c.page_size * HD;
+  const bf16* base = c.kv + (long long)g * c.page_size * HD;
+  const unsigned kbase = (unsigned)__cvta_generic_to_shared(kdst), vbase = (unsigned)__cvta_generic_to_shared(vdst);
+#pragma unroll
+  for (int i = 0; i < W::PER_LANE; ++i) {
+    const int item = lane + 32 * i;
+    if (W::ITEMS % 32 != 0 && item >= W::ITEMS) break;
+    const int rg = item / CHUNKS, ch = item - rg * CHUNKS;
+    const int key0 = k0 + 4 * rg;
+    const int page = pg[i];
+    const bool have = page >= 0 && page < c.num_pages;
+    if (!have) fmx_set_status(status, FMX_BAD_PAGE, page, where);
+    const bf16* src = have ? base + page * 2 * plane + (long long)(key0 & (c.page_size - 1)) * HD + ch * 8 : c.kv;
+    const int n = have ? 16 : 0;                       // 0: zeros, and nothing is read (the offsets stay inside page 0)
+    const unsigned off = (unsigned)(((4 * rg) * ROW + ch * 8) * 2);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(kbase + off + j * ROW * 2), "l"(src + j * HD), "r"(n));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vbase + off + j * ROW * 2), "l"(src + j * HD + plane), "r"(n));
+    }
+  }
+}
+
+// Any tile, any page size: keys outside [kbeg, kend) or without a page become zeros.
+template <int KG>
+__device__ __forceinline__ void warp_tile_any(bf16* kdst, bf16* vdst, const Cache& c, int g, int k0, int kbeg, int kend,
+                                              int* status, int where) {
+  using W = WarpTile<KG>;
+  const int lane = threadIdx.x & 31;
+  const long long plane = (long long)c.nkv * c.page_size * HD;
+  const bf16* base = c.kv + (long long)g * c.page_size * HD;
+  for (int idx = lane; idx < W::TK * CHUNKS; idx += 32) {
+    const int rr = idx / CHUNKS, ch = idx - rr * CHUNKS;
+    const int key = k0 + rr;
+    bool valid = key >= kbeg && key < kend;
+    const bf16* src = c.kv;
+    if (valid) {
+      const int blk = c.page_shift >= 0 ? key >> c.page_shift : key / c.page_size;
+      const int page = blk < c.bt_len ? c.bt[blk] : -1;
+      if (page < 0 || page >= c.num_pages) {
+        fmx_set_status(status, FMX_BAD_PAGE, page, where);
+        valid = false;
+      } else {
+        src = base + page * 2 * plane + (long long)(key - blk * c.page_size) * HD + ch * 8;
+      }
+    }
+    cp_async16(kdst + rr * ROW + ch * 8, src, valid);
+    cp_async16(vdst + rr * ROW + ch * 8, valid ? src + plane : c.kv, valid);
   }
 }
 
@@ -470,7 +566,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
 // ------------------------------------------------------------------------------------ decode
 // part_o: [R, nkv, splits, 16, HD] float; part_ml: [R, nkv, splits, 16, 2] float (max in the
 // scaled log2 domain, sum).  With one split the output is written directly.
-template <int STAGES, int NH>
+template <int STAGES, int NH, int KG>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int* block_tables, int bt_stride,
                    const int* row_start, const int* positions, bf16* out, float* part_o, float* part_ml, int nh, int nkv,
@@ -489,41 +585,58 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
 
   const int lo_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int n_keys = max(0, pos + 1 - lo_key);
+  using W = WarpTile<KG>;
   int per = (n_keys + splits - 1) / splits;
-  per = (per + BN - 1) / BN * BN;
+  per = (per + 4 * W::TK - 1) / (4 * W::TK) * (4 * W::TK);
   const int kbeg = lo_key + split * per;
   const int kend = min(pos + 1, kbeg + per);
-  const int kstart = kbeg & ~3;
-  const int n_tiles = kend > kbeg ? (kend - kstart + BN - 1) / BN : 0;
-  // The pages of this block's keys, once, into shared memory: a tile's copies then start from an address that
-  // is at hand instead of behind a read of the block table from L2 (which stood in front of every tile's
-  // copies: the profile's long-scoreboard stalls).  Ranges beyond the cache keep reading the table itself.
-  // The first tiles go out with addresses read from the table itself; the cache is filled behind them and
-  // used from the loop's first pass on (whose barrier makes it visible).
-  constexpr int BTC = BT_CACHE;
-  __shared__ int bt_cache[BTC > 0 ? BTC : 1];
-  const int bt_blk0 = kstart / page_size;
-  const bool bt_cached = BTC > 0 && n_tiles > 0 && (kend - 1) / page_size - bt_blk0 + 1 <= BTC;
+  // This warp's keys [rbeg, rend) and its tiles of 16 KG keys, which start on a multiple of four keys.  With the
+  // small tile the block's tiles go round the warps, which then walk through the same pages side by side (batch 8
+  // over 8,192 keys at head size 64: 27.8 us against 28.8); with the large tile of the grids of few blocks each warp
+  // has a quarter of the keys to itself (batch 1 over 131,072 keys: 51.2 us against 58.2).
+  constexpr bool QUARTERS = KG > 1;
+  const int rbeg = QUARTERS ? kbeg + warp * (per / 4) : kbeg;
+  const int rend = QUARTERS ? min(kend, rbeg + per / 4) : kend;
+  const int rstart = rbeg & ~3;
+  const int r_tiles = rend > rbeg ? (rend - rstart + W::TK - 1) / W::TK : 0;
+  const int n_tiles = QUARTERS ? r_tiles : (r_tiles > warp ? (r_tiles - warp + 3) / 4 : 0);
+  auto tile_key = [&](int tile) { return rstart + (QUARTERS ? tile : 4 * tile + warp) * W::TK; };
+  const bool pow2 = c.page_shift >= 0;
 
-  auto stage_k = [&](int s) { return smem + (size_t)s * 2 * TILE; };
-  auto stage_v = [&](int s) { return smem + (size_t)s * 2 * TILE + TILE; };
+  bf16* ring = smem + (size_t)warp * STAGES * 2 * W::ELEMS;
+  auto stage_k = [&](int s) { return ring + (size_t)s * 2 * W::ELEMS; };
+  auto stage_v = [&](int s) { return ring + (size_t)s * 2 * W::ELEMS + W::ELEMS; };
+  int pg[W::PER_LANE];
+  // Tile `tile` into its stage; pages of a power of two and a tile inside the range take the short path, with the
+  // table entries that `pg` holds when the caller read them ahead.
+  auto issue = [&](int tile, bool have_pg) {
+    const int k0 = tile_key(tile);
+    bf16* kd = stage_k(tile % STAGES);
+    bf16* vd = stage_v(tile % STAGES);
+    if (pow2 && k0 >= rbeg && k0 + W::TK <= rend) {
+      if (!have_pg) warp_fetch_pages<KG>(pg, c, k0);
+      warp_tile_inside<KG>(kd, vd, c, g, k0, pg, status, r);
+    } else {
+      warp_tile_any<KG>(kd, vd, c, g, k0, rbeg, rend, status, r);
+    }
+  };
   // Keys before this row's new one were written by earlier steps: tiles that end before it are
   // fetched while the kernel ahead (which writes the new key and the queries) is still running.
   int fetched = 0;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (fetched == s && s < n_tiles && min(kend, kstart + (s + 1) * BN) <= pos) {
-      load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
+    if (fetched == s && s < n_tiles && min(rend, tile_key(s) + W::TK) <= pos) {
+      issue(s, false);
       fetched = s + 1;
     }
   }
-  // The last stage of the ring is free until the first pass of the loop below: with rotation in
-  // this kernel it holds the rotated queries and the row's sines and cosines meanwhile.  Those
-  // depend on the position alone, so they too are ready before the kernel ahead has finished.
-  bf16* q_rot = stage_k(STAGES - 1);            // [16][HD]
+  // The last stage of a ring is free until the first pass of the loop below: with rotation in
+  // this kernel the first warp's holds the rotated queries and the row's sines and cosines meanwhile.
+  // Those depend on the position alone, so they too are ready before the kernel ahead has finished.
+  bf16* q_rot = smem + (size_t)(STAGES - 1) * 2 * W::ELEMS;        // [16][HD]
   float* rope_sin = reinterpret_cast<float*>(q_rot + 16 * HD);
   float* rope_cos = rope_sin + HD / 2;
-  static_assert(16 * HD * 2 + HD * 4 <= TILE * 2, "the rotated queries must fit one K tile");
+  static_assert(16 * HD * 2 + HD * 4 <= 2 * W::ELEMS * 2, "the rotated queries must fit one stage of a warp");
   const int half = rot / 2;
   if (rope_mode > 0) {
     const float fpos = (float)pos;
@@ -614,34 +727,41 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
       for (int e = 0; e < 4; ++e) o[h][n][e] = 0.f;
   }
 
+  if (rope_mode > 0) __syncthreads();                // every warp has its queries before the first warp's ring fills up
   // the groups of the pipeline: tile s is in group s, whether it went out before the wait or not
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s >= fetched && s < n_tiles) load_tiles(stage_k(s), stage_v(s), c, g, kstart + s * BN, kbeg, kend, status, r);
+    if (s >= fetched && s < n_tiles) issue(s, false);
     cp_async_commit();
   }
-  if (bt_cached) {
-    const int nblk = (kend - 1) / page_size - bt_blk0 + 1;
-    for (int i = threadIdx.x; i < nblk; i += THREADS) bt_cache[i] = bt_blk0 + i < bt_stride ? c.bt[bt_blk0 + i] : -1;
-    c.bt = bt_cache - bt_blk0;
+  int pg_tile = -1;                                  // the tile whose table entries pg holds
+  if (pow2 && STAGES - 1 < n_tiles) {
+    warp_fetch_pages<KG>(pg, c, tile_key(STAGES - 1));
+    pg_tile = STAGES - 1;
   }
   for (int it = 0; it < n_tiles; ++it) {
     cp_async_wait<STAGES - 2>();
-    __syncthreads();
+    __syncwarp();                                    // every lane's copies of tile `it` have landed; tile it - 1 is read
     const int nx = it + STAGES - 1;
-    if (nx < n_tiles)
-      load_tiles(stage_k(nx % STAGES), stage_v(nx % STAGES), c, g, kstart + nx * BN, kbeg, kend, status, r);
+    if (nx < n_tiles) {
+      issue(nx, pg_tile == nx);
+      if (pow2 && nx + 1 < n_tiles) {
+        warp_fetch_pages<KG>(pg, c, tile_key(nx + 1));
+        pg_tile = nx + 1;
+      }
+    }
     cp_async_commit();
     const bf16* ks = stage_k(it % STAGES);
     const bf16* vs = stage_v(it % STAGES);
-    float s[NH][4], alpha[NH][2];
-    unsigned pb[NH][2];
-    qk_keys<NH>(s, qf, ks, warp * 16);
-    const int wk0 = kstart + it * BN + warp * 16;
-    if (wk0 >= kbeg && wk0 + 15 < kend)
-      softmax_keys<NH, false>(s, m, l, alpha, pb, sl2, wk0, kbeg, kend - 1);
+    float s[KG][NH][4], alpha[NH][2];
+    unsigned pb[KG][NH][2];
+#pragma unroll
+    for (int kg = 0; kg < KG; ++kg) qk_keys<NH>(s[kg], qf, ks, 16 * kg);
+    const int wk0 = tile_key(it);
+    if (wk0 >= rbeg && wk0 + W::TK <= rend)
+      softmax_keys<NH, KG, false>(s, m, l, alpha, pb, sl2, wk0, rbeg, rend - 1);
     else
-      softmax_keys<NH, true>(s, m, l, alpha, pb, sl2, wk0, kbeg, kend - 1);
+      softmax_keys<NH, KG, true>(s, m, l, alpha, pb, sl2, wk0, rbeg, rend - 1);
 #pragma unroll
     for (int h = 0; h < NH; ++h)
 #pragma unroll
@@ -649,7 +769,8 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
         o[h][n][0] *= alpha[h][0]; o[h][n][1] *= alpha[h][1];
         o[h][n][2] *= alpha[h][0]; o[h][n][3] *= alpha[h][1];
       }
-    pv_keys<NH>(o, pb, vs, warp * 16);
+#pragma unroll
+    for (int kg = 0; kg < KG; ++kg) pv_keys<NH>(o, pb[kg], vs, 16 * kg);
   }
   cp_async_wait<0>();
   __syncthreads();                                   // the tiles are done with; reuse the memory
@@ -777,35 +898,34 @@ __global__ void attn_combine_kernel(const float* part_o, const float* part_ml, c
 }
 
 constexpr size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * TILE * sizeof(bf16); }
-constexpr size_t decode_smem(int stages = DECODE_STAGES) {
-  const size_t pipe = (size_t)stages * 2 * TILE * sizeof(bf16);
+constexpr size_t decode_smem(int kg = 1) {
+  const size_t pipe = (size_t)DECODE_STAGES * 2 * 4 * 16 * kg * ROW * sizeof(bf16);
   const size_t merge = (size_t)(4 * 16 * MO_ROW + 4 * 16 * 2) * sizeof(float);
   return pipe > merge ? pipe : merge;
 }
-// The deeper ring, where the head size has one and the whole grid is resident with it.
-bool decode_deep(dim3 grid) {
-  if (DEEP_STAGES <= DECODE_STAGES) return false;
-  const long long per_sm = (226 * 1024) / (long long)decode_smem(DEEP_STAGES);
-  return (long long)grid.x * grid.y * grid.z <= per_sm * fmx_num_sms();
+// Blocks of the larger tile that an SM holds; the grids that are resident at once with it take it.
+constexpr long long few_per_sm() { return FEW_KG > 1 ? (226 * 1024) / (long long)decode_smem(FEW_KG) : 0; }
+bool decode_few(dim3 grid) {
+  return FEW_KG > 1 && (long long)grid.x * grid.y * grid.z <= few_per_sm() * fmx_num_sms();
 }
-template <int STAGES, int NH> cudaError_t configure_decode_one() {
-  return cudaFuncSetAttribute(attn_decode_kernel<STAGES, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)decode_smem(STAGES));
+template <int NH, int KG> cudaError_t configure_decode_one() {
+  return cudaFuncSetAttribute(attn_decode_kernel<DECODE_STAGES, NH, KG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)decode_smem(KG));
 }
 cudaError_t configure_decode() {
-  cudaError_t e = configure_decode_one<DECODE_STAGES, 1>();
-  if (e == cudaSuccess) e = configure_decode_one<DECODE_STAGES, 2>();
-  if (e == cudaSuccess && DEEP_STAGES > DECODE_STAGES) e = configure_decode_one<DEEP_STAGES, 1>();
-  if (e == cudaSuccess && DEEP_STAGES > DECODE_STAGES) e = configure_decode_one<DEEP_STAGES, 2>();
+  cudaError_t e = configure_decode_one<1, 1>();
+  if (e == cudaSuccess) e = configure_decode_one<2, 1>();
+  if (e == cudaSuccess && FEW_KG > 1) e = configure_decode_one<1, FEW_KG>();
+  if (e == cudaSuccess && FEW_KG > 1) e = configure_decode_one<2, FEW_KG>();
   return e;
 }
-// The instantiation for a grid and a number of query heads per kv head: LAUNCH(stages, head groups of 8).
+// The instantiation for a grid and a number of query heads per kv head: LAUNCH(head groups of 8, key groups of 16).
 #define FMX_DECODE_DISPATCH(grid, rep, LAUNCH)            \
   do {                                                    \
-    if (decode_deep(grid)) {                              \
-      if ((rep) <= 8) { LAUNCH(DEEP_STAGES, 1); } else { LAUNCH(DEEP_STAGES, 2); }      \
+    if (decode_few(grid)) {                               \
+      if ((rep) <= 8) { LAUNCH(1, FEW_KG); } else { LAUNCH(2, FEW_KG); }  \
     } else {                                              \
-      if ((rep) <= 8) { LAUNCH(DECODE_STAGES, 1); } else { LAUNCH(DECODE_STAGES, 2); }  \
+      if ((rep) <= 8) { LAUNCH(1, 1); } else { LAUNCH(2, 1); }            \
     }                                                     \
   } while (0)
 }  // namespace
@@ -822,12 +942,15 @@ FMX_EXPORT long long fmx_attn_decode_scratch_floats(int rows, int nkv, int split
 // multiprocessors: as many as keep the whole grid resident at once (a second, partial round of
 // blocks costs more than it brings), with at least 128 keys to a split and at most 32 splits
 // (measured at batch 1 over 8192 keys: 17 to 32 splits 13.5 us, 48: 15.3, 64: 17.7; over 1024
-// keys: 2 splits 10.8 us, 8: 6.5).
+// keys: 2 splits 10.8 us, 8: 6.5).  Up to 32 (row, kv head) pairs the grid is sized for the blocks of the larger
+// tile, which the launch then takes (batch 4 over 8192 keys at head size 64: 17.5 us against 18.7).
 FMX_EXPORT int fmx_attn_decode_plan(int rows, int nkv, long long max_ctx, int sms) {
   if (sms <= 0) sms = fmx_num_sms();
+  const long long pairs = (long long)rows * nkv > 0 ? (long long)rows * nkv : 1;
   long long per_sm = (227 * 1024) / (long long)decode_smem();
   per_sm = per_sm < 1 ? 1 : per_sm > 5 ? 5 : per_sm;
-  long long s = sms * per_sm / ((long long)rows * nkv > 0 ? (long long)rows * nkv : 1);
+  if (FEW_KG > 1 && pairs <= 32) per_sm = few_per_sm();
+  long long s = sms * per_sm / pairs;
   const long long by_keys = (max_ctx + 127) / 128;
   if (s > by_keys) s = by_keys;
   if (s > 32) s = 32;
@@ -884,14 +1007,14 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
   if (!configured) {
     cudaError_t e = configure_decode();
     if (e != cudaSuccess) return fmx_fail("fmx_attn_decode: shared memory of %zu bytes refused: %s",
-                                          decode_smem(DEEP_STAGES), cudaGetErrorString(e));
+                                          decode_smem(FEW_KG), cudaGetErrorString(e));
     configured = true;
   }
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (long long)rows * nkv * splits * 16 * HD : nullptr;
   dim3 grid(splits, nkv, rows);
-#define FMX_DECODE_LAUNCH(ST, NHG)                                                                                    \
-  fmx_launch(attn_decode_kernel<ST, NHG>, grid, dim3(THREADS), decode_smem(ST), stream, (const bf16*)q, q_stride,       \
+#define FMX_DECODE_LAUNCH(NHG, KGR)                                                                                    \
+  fmx_launch(attn_decode_kernel<DECODE_STAGES, NHG, KGR>, grid, dim3(THREADS), decode_smem(KGR), stream, (const bf16*)q, q_stride,       \
              (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o, part_ml, nh, nkv,      \
              page_size, num_pages, scale, window, status, tickets, inv_freq, rot, interleaved, rope_mode)
   FMX_DECODE_DISPATCH(grid, nh / nkv, FMX_DECODE_LAUNCH);
@@ -939,7 +1062,7 @@ int noalloc_setup(float** ptr, cudaStream_t stream) {
       return fmx_fail("fmx_attn_decode_noalloc: cudaGetSymbolAddress on device %d: %s", dev, cudaGetErrorString(e));
     e = configure_decode();
     if (e != cudaSuccess)
-      return fmx_fail("fmx_attn_decode_noalloc: shared memory of %zu bytes refused: %s", decode_smem(DEEP_STAGES),
+      return fmx_fail("fmx_attn_decode_noalloc: shared memory of %zu bytes refused: %s", decode_smem(FEW_KG),
                       cudaGetErrorString(e));
     g_noalloc_ptr[dev] = p;
   }
@@ -974,8 +1097,8 @@ FMX_EXPORT int fmx_attn_decode_noalloc(const void* q, long long q_stride, const 
   float* part_o = scratch;
   float* part_ml = scratch + (long long)rows * nkv * splits * 16 * HD;
   dim3 grid(splits, nkv, rows);
-#define FMX_DECODE_LAUNCH(ST, NHG)                                                                                    \
-  attn_decode_kernel<ST, NHG><<<grid, THREADS, decode_smem(ST), stream>>>(                                              \
+#define FMX_DECODE_LAUNCH(NHG, KGR)                                                                                    \
+  attn_decode_kernel<DECODE_STAGES, NHG, KGR><<<grid, THREADS, decode_smem(KGR), stream>>>(                                              \
       (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,     \
       part_ml, nh, nkv, page_size, num_pages, scale, window, status, (int*)nullptr, (const float*)nullptr, 0, 0, 0)
   FMX_DECODE_DISPATCH(grid, nh / nkv, FMX_DECODE_LAUNCH);
