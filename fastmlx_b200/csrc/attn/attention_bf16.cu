@@ -903,7 +903,10 @@ constexpr size_t decode_smem(int kg = 1) {
   const size_t merge = (size_t)(4 * 16 * MO_ROW + 4 * 16 * 2) * sizeof(float);
   return pipe > merge ? pipe : merge;
 }
-// Blocks of the larger tile that an SM holds; the grids that are resident at once with it take it.
+// Blocks of the larger tile that an SM holds; the grids that are resident at once with it take it.  (The unsplit
+// rows of a large batch do not: alone the kernel was faster with it, batch 64 over 8,192 keys at head size 64 in 174 us
+// against 188, but its 512 blocks then take two rounds, and inside a decode step, where no launch of the same kernel
+// follows to fill the second round's gaps, the step was 3 to 5 % slower.)
 constexpr long long few_per_sm() { return FEW_KG > 1 ? (226 * 1024) / (long long)decode_smem(FEW_KG) : 0; }
 bool decode_few(dim3 grid) {
   return FEW_KG > 1 && (long long)grid.x * grid.y * grid.z <= few_per_sm() * fmx_num_sms();
