@@ -412,7 +412,9 @@ def _full_ctx(rows, ctx, grp):
 P_ROUNDING = 2.0 ** -9
 
 TILED_SHAPES = [(4, 2, 16, 16), (6, 3, 32, 16), (5, 1, 48, 8), (8, 8, 64, 32), (32, 8, 64, 16), (12, 4, 128, 64),
-                (24, 8, 128, 16), (3, 3, 80, 16), (2, 1, 256, 16), (16, 1, 96, 128)]
+                (24, 8, 128, 16), (3, 3, 80, 16), (2, 1, 256, 16), (16, 1, 96, 128),
+                (12, 1, 64, 16),      # more than 8 query heads to a kv head at a head size with both decode tiles
+                (6, 2, 32, 12)]       # pages of no power of two
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES)
