@@ -262,17 +262,39 @@ struct Run {
                                                  op.window, d.status, op.rot > 0 ? op.vec : nullptr, op.rot, op.trad,
                                                  op.store ? 1 : 2, stream);
     }
-    ++ex.launches;
     if (tiled) {
-      if (d.max_q_len >= TC_ATTN_MIN_TOKENS && op.tc_attention_ok && op.fn_attn_prefill_tc != nullptr && qstride % 8 == 0 &&
+      // In a mixed step the decoding rows at its head go to the split decode kernel (queries rotated and keys stored
+      // above) and the portions behind them to a tiled one: alone on a tile, a decoding row would walk its whole
+      // context in one block.
+      const int dr = rep <= 16 ? d.decode_rows : 0;
+      if (dr > 0) {
+        const int splits = ((attn_plan_fn)op.fn_attn_plan)(dr, op.nkv, d.decode_max_ctx > 1 ? d.decode_max_ctx : 1, ex.sms);
+        const long long need = splits <= 1 ? 0 : (long long)dr * op.nkv * splits * 16 * (op.hd + 2);
+        if (need > d.attn_scratch_floats)
+          return fmx_fail("the split decode attention's workspace holds %lld floats, %lld asked for", d.attn_scratch_floats, need);
+        int* tickets = need > 0 && (long long)dr * op.nkv <= d.attn_tickets_n ? d.attn_tickets : nullptr;
+        ++ex.launches;
+        if (((attn_decode_fn)op.fn_attn_decode)(qkv, qstride, op.kv, bt, bt_stride, d.row_start, d.positions, out,
+                                                need > 0 ? d.attn_scratch : nullptr, need > 0 ? d.attn_scratch_floats : 0,
+                                                tickets, dr, splits, op.nh, op.nkv, op.page_size, op.num_pages, op.scale,
+                                                op.window, d.status, nullptr, 0, 0, 0, stream) != 0)
+          return 1;
+      }
+      const int rows = d.R - dr, max_q = dr > 0 ? d.rest_max_q_len : d.max_q_len;
+      const int* row_start = d.row_start + dr;
+      const int* row_ctx = d.row_ctx + dr;
+      const int* rbt = bt + (long long)dr * bt_stride;
+      ++ex.launches;
+      if (max_q >= TC_ATTN_MIN_TOKENS && op.tc_attention_ok && op.fn_attn_prefill_tc != nullptr && qstride % 8 == 0 &&
           aligned16(qkv))
-        return ((attn_prefill_tc_fn)op.fn_attn_prefill_tc)(qkv, qstride, d.T, op.kv, bt, bt_stride, d.row_start, d.row_ctx, out,
-                                                           d.R, d.max_q_len, op.nh, op.nkv, op.page_size, op.num_pages,
+        return ((attn_prefill_tc_fn)op.fn_attn_prefill_tc)(qkv, qstride, d.T, op.kv, rbt, bt_stride, row_start, row_ctx, out,
+                                                           rows, max_q, op.nh, op.nkv, op.page_size, op.num_pages,
                                                            op.scale, 0, d.status, stream);
-      return ((attn_prefill_fn)op.fn_attn_prefill)(qkv, qstride, op.kv, bt, bt_stride, d.row_start, d.row_ctx, out, d.R,
-                                                   d.max_q_len, op.nh, op.nkv, op.page_size, op.num_pages, op.scale,
+      return ((attn_prefill_fn)op.fn_attn_prefill)(qkv, qstride, op.kv, rbt, bt_stride, row_start, row_ctx, out, rows,
+                                                   max_q, op.nh, op.nkv, op.page_size, op.num_pages, op.scale,
                                                    op.window, d.status, stream);
     }
+    ++ex.launches;
     return ((attention_simple_fn)ex.k.paged_attention_simple)(qkv, qstride, op.kv, bt, bt_stride, d.token_row, d.positions, out,
                                                               d.T, op.nh, op.nkv, op.hd, op.page_size, op.num_pages, op.scale,
                                                               op.window, d.R, dtype, d.status, stream);
@@ -324,7 +346,7 @@ struct Run {
 // ------------------------------------------------------------------------------------ the batch layout
 namespace {
 struct Layout {
-  int R, Rp, T, Tp, max_blocks, max_q, max_ctx, all_decode;
+  int R, Rp, T, Tp, max_blocks, max_q, max_ctx, all_decode, decode_rows, decode_max_ctx, rest_max_q;
   long long tokens, positions, token_row, row_start, row_ctx, row_slot, want, bt[FMX_MAX_GROUPS], sm[FMX_MAX_GROUPS], total;
 };
 
@@ -353,6 +375,17 @@ int plan_layout(const FmxBatchIn& in, Layout* L) {
   L->max_q = max_q;
   L->max_ctx = max_ctx;
   L->all_decode = all_decode;
+  // the one-token rows at the head of a mixed step
+  int dr = 0;
+  while (dr < in.R && in.q_lens[dr] == 1) ++dr;
+  L->decode_rows = L->decode_max_ctx = L->rest_max_q = 0;
+  if (dr > 0 && dr < in.R) {
+    L->decode_rows = dr;
+    for (int r = 0; r < dr; ++r)
+      if (in.ctx_lens[r] + 1 > L->decode_max_ctx) L->decode_max_ctx = in.ctx_lens[r] + 1;
+    for (int r = dr; r < in.R; ++r)
+      if (in.q_lens[r] > L->rest_max_q) L->rest_max_q = in.q_lens[r];
+  }
   long long at = 0;
   auto take = [&](long long n) { at = (at + 3) / 4 * 4; const long long o = at; at += n; return o; };   // 16-byte starts
   L->tokens = take(L->Tp);
@@ -447,6 +480,10 @@ FMX_EXPORT int fmx_exec_layout(const FmxBatchIn* in, int* host, int* dev, long l
   desc->max_q_len = L.max_q;
   desc->max_ctx_after = L.max_ctx;
   desc->all_decode = L.all_decode;
+  desc->decode_rows = L.decode_rows;
+  desc->decode_max_ctx = L.decode_max_ctx;
+  desc->rest_max_q_len = L.rest_max_q;
+  desc->reserved_ = 0;
   desc->n_splits = 0;
   desc->n_groups = in->n_groups;
   desc->tokens = dev + L.tokens;

@@ -77,6 +77,9 @@ struct FmxKernelTable {
 // One laid-out step: device pointers into the packed buffer, and the step's workspaces.
 struct FmxStepDesc {
   int T, R, n_want, max_q_len, max_ctx_after, all_decode, n_splits, n_groups;
+  // a mixed step whose first rows bring one token each: how many, the longest context among them after the step, and
+  // the longest portion among the rows behind them; all 0 where the step is not mixed so
+  int decode_rows, decode_max_ctx, rest_max_q_len, reserved_;
   const int* tokens;
   const int* positions;
   const int* token_row;

@@ -49,6 +49,11 @@ class StepContext:
     max_q_len: int = 0
     max_ctx_after: int = 0
     all_decode: bool = False           # every row brings exactly one token
+    # a mixed step whose first rows bring one token each (the scheduler puts decoding requests first): how many,
+    # the longest context among them, and the longest portion among the rest; 0 where the step is not mixed so
+    decode_rows: int = 0
+    decode_max_ctx: int = 0
+    rest_max_q_len: int = 0
     n_splits: int = 0                  # decode attention: fixed split count (0 = kernel's choice)
     scratch: dict = field(default_factory=dict)
 
@@ -78,6 +83,17 @@ class StaticBuffers:
         ev.record()
         self.events[self.at] = ev
         return self.dev
+
+
+def leading_decode_rows(q_lens, ctxs) -> dict:
+    """The one-token rows at the head of a mixed step, which attend on the split decode kernel
+    while the portions behind them take the tiled one."""
+    d = 0
+    while d < len(q_lens) and q_lens[d] == 1:
+        d += 1
+    if d == 0 or d == len(q_lens):
+        return {}
+    return {"decode_rows": d, "decode_max_ctx": max(c + 1 for c in ctxs[:d]), "rest_max_q_len": max(q_lens[d:])}
 
 
 def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_blocks: int = 0,
@@ -211,4 +227,5 @@ def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_bl
         logit_rows=dview("want"), status=status, groups=groups, caches=manager.entries,
         h_row_start=rstart.tolist(), h_row_ctx=rctx.tolist(), h_row_slot=rslot.tolist(),
         max_q_len=max(q_lens + [1]), max_ctx_after=max([c + q for c, q in zip(ctxs, q_lens)] + [1]),
-        all_decode=all(q == 1 for q in q_lens), scratch={"h2d_bytes": host.nbytes, "layout_ints": total})
+        all_decode=all(q == 1 for q in q_lens), scratch={"h2d_bytes": host.nbytes, "layout_ints": total},
+        **leading_decode_rows(q_lens, ctxs))

@@ -56,6 +56,7 @@ class FmxKernelTable(Structure):
 class FmxStepDesc(Structure):
     _fields_ = [("T", c_int), ("R", c_int), ("n_want", c_int), ("max_q_len", c_int), ("max_ctx_after", c_int),
                 ("all_decode", c_int), ("n_splits", c_int), ("n_groups", c_int),
+                ("decode_rows", c_int), ("decode_max_ctx", c_int), ("rest_max_q_len", c_int), ("reserved_", c_int),
                 ("tokens", c_void_p), ("positions", c_void_p), ("token_row", c_void_p), ("row_start", c_void_p),
                 ("row_ctx", c_void_p), ("row_slot", c_void_p), ("want", c_void_p),
                 ("block_tables", c_void_p * MAX_GROUPS), ("bt_stride", c_int * MAX_GROUPS),
@@ -299,6 +300,8 @@ class NativeProgram:
         d.T, d.R, d.n_want = ctx.T, ctx.R, n_want
         d.max_q_len, d.max_ctx_after = int(ctx.max_q_len), int(ctx.max_ctx_after)
         d.all_decode, d.n_splits, d.n_groups = int(bool(ctx.all_decode)), int(ctx.n_splits), len(ctx.groups)
+        d.decode_rows, d.decode_max_ctx, d.rest_max_q_len = (int(getattr(ctx, "decode_rows", 0)), int(getattr(ctx, "decode_max_ctx", 0)),
+                                                             int(getattr(ctx, "rest_max_q_len", 0)))
         d.tokens, d.positions, d.token_row = ctx.tokens.data_ptr(), ctx.positions.data_ptr(), ctx.token_row.data_ptr()
         d.row_start, d.row_ctx, d.row_slot = ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), ctx.row_slot.data_ptr()
         d.want = ctx.logit_rows.data_ptr() if n_want else None

@@ -355,14 +355,15 @@ def attn_decode_scratch_floats(rows: int, nkv: int, splits: int, hd: int) -> int
     return 0 if splits <= 1 else rows * nkv * splits * 16 * (hd + 2)
 
 
-def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, splits=None, rope=None) -> torch.Tensor:
+def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, splits=None, rope=None, out=None) -> torch.Tensor:
     """Every row brings one token: split over the keys, all query heads of a kv head together.
     rope = (inv_freq or None, rotary_dim, traditional, store): qkv is as the projection left it;
     the kernel rotates the queries itself and, if `store`, rotates each row's new key and puts
     it and its value into the cache (what rope_kv_write does in a kernel of its own)."""
     T = qkv.shape[0]
     R = ctx.R
-    out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    if out is None:
+        out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
     if splits is None:
         splits = getattr(ctx, "n_splits", 0) or decode_splits(R, nkv, max(1, ctx.max_ctx_after), hd, qkv.device)
     need = attn_decode_scratch_floats(R, nkv, splits, hd)
@@ -380,10 +381,11 @@ def paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, spli
     return out
 
 
-def paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window) -> torch.Tensor:
+def paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window, out=None) -> torch.Tensor:
     """Any mix of rows, tiled over 64 packed query rows and 64 keys."""
     T = qkv.shape[0]
-    out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    if out is None:
+        out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
     bt = group.block_tables
     call(f"attn_hd{hd}", "fmx_attn_prefill", qkv.data_ptr(), qkv.stride(0), kv.data_ptr(), bt.data_ptr(), bt.stride(0),
          ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), out.data_ptr(), ctx.R, int(ctx.max_q_len), nh, nkv,
@@ -402,11 +404,12 @@ def tc_attention_ok(nh: int, nkv: int, hd: int, page_size: int, window: int) -> 
             and page_size >= 8 and 128 % page_size == 0)
 
 
-def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale, variant: int = 0) -> torch.Tensor:
+def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale, variant: int = 0, out=None) -> torch.Tensor:
     """Causal attention of prompt portions on the tcgen05 tensor cores (TMA-fed, scores and
     outputs in tensor memory)."""
     T = qkv.shape[0]
-    out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    if out is None:
+        out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
     bt = group.block_tables
     call(f"attn_hd{hd}", "fmx_attn_prefill_tc", qkv.data_ptr(), qkv.stride(0), T, kv.data_ptr(), bt.data_ptr(),
          bt.stride(0), ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), out.data_ptr(), ctx.R, int(ctx.max_q_len), nh,
@@ -421,24 +424,46 @@ def decode_attention_fuses_rope(qkv, kv, ctx, nh, nkv, hd) -> bool:
             and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0 and ctx.all_decode and nh // nkv <= 16)
 
 
+def _rows_of(ctx, group, a: int, b: int, max_q_len: int, max_ctx_after: int):
+    """The rows [a, b) of a step as a step of their own for the attention kernels: the arrays per
+    row start at row a, token indices and positions stay those of the whole step."""
+    from types import SimpleNamespace
+    sub = SimpleNamespace(positions=ctx.positions, status=ctx.status, row_start=ctx.row_start[a:], row_ctx=ctx.row_ctx[a:],
+                          R=b - a, max_q_len=max_q_len, max_ctx_after=max_ctx_after, all_decode=max_q_len == 1, n_splits=0)
+    return sub, SimpleNamespace(block_tables=group.block_tables[a:b])
+
+
 def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window, rope=None) -> torch.Tensor:
     """Attention of every token of the step over the pages of its own request.
     qkv[T, >= nh*hd] holds the (rotated) queries first; -> [T, nh*hd].  bfloat16 with a head
     size in steps of 16 (at most 256) runs on the tensor cores; everything else, and all
-    of the 32-bit path, on the one-warp-per-query kernel."""
+    of the 32-bit path, on the one-warp-per-query kernel.  In a mixed step the decoding rows at
+    its head go to the split decode kernel and the portions behind them to the tiled one: alone
+    on a tile, a decoding row would walk its whole context in one block."""
     _need_cuda(qkv, kv)
     assert kv.is_contiguous() and kv.dtype == qkv.dtype and qkv.stride(1) == 1
-    if qkv.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0:
-        if ctx.all_decode and nh // nkv <= 16:
-            return paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, rope=rope)
+    tiled = qkv.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0
+    if tiled and ctx.all_decode and nh // nkv <= 16:
+        return paged_attention_decode(qkv, kv, ctx, group, nh, nkv, hd, scale, window, rope=rope)
     if rope is not None:
         raise KernelError("only the split decode kernel rotates by itself: ask decode_attention_fuses_rope first")
-    if qkv.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and qkv.stride(0) % 2 == 0:
-        if ctx.max_q_len >= TC_ATTN_MIN_TOKENS and tc_attention_ok(nh, nkv, hd, kv.shape[3], window) \
-                and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
-            return paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale)
-        return paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
-    return paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
+    if not tiled:
+        return paged_attention_simple(qkv, kv, ctx, group, nh, nkv, hd, scale, window)
+    out = None
+    d = getattr(ctx, "decode_rows", 0)
+    if d > 0 and nh // nkv <= 16:
+        key = ("attention rows", id(group))
+        views = ctx.scratch.get(key)
+        if views is None:
+            views = ctx.scratch[key] = (_rows_of(ctx, group, 0, d, 1, ctx.decode_max_ctx),
+                                        _rows_of(ctx, group, d, ctx.R, ctx.rest_max_q_len, ctx.max_ctx_after))
+        (dctx, dgroup), (ctx, group) = views
+        out = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
+        paged_attention_decode(qkv, kv, dctx, dgroup, nh, nkv, hd, scale, window, out=out)
+    if ctx.max_q_len >= TC_ATTN_MIN_TOKENS and tc_attention_ok(nh, nkv, hd, kv.shape[3], window) \
+            and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
+        return paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale, out=out)
+    return paged_attention_prefill(qkv, kv, ctx, group, nh, nkv, hd, scale, window, out=out)
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -431,6 +431,29 @@ def test_tiled_prefill_attention_mixed_rows(nh, nkv, hd, page_size, window):
     close(got, ref, torch.bfloat16, "tiled prefill attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES + [(8, 2, 64, 16), (8, 2, 128, 16)])
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("portion", [17, 130])
+def test_mixed_step_attention_takes_two_kernels(nh, nkv, hd, page_size, window, portion):
+    """A step whose first rows decode and whose last rows are portions: the dispatch hands the
+    decoding rows to the split kernel and the rest to a tiled one (the tensor-memory kernel for
+    the 130-token portion where it takes the sizes), into one output, and a single token among
+    the portions stays with them."""
+    from fastmlx_b200.engine.batch import leading_decode_rows
+    rows = [(300, 1), (1000, 1), (63, 1), (0, 1), (0, portion), (90, 1), (31, 2), (200, portion)]
+    q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, window)
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, window)
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    for name, value in leading_decode_rows([ql for _, ql in rows], [c for c, _ in rows]).items():
+        setattr(dctx, name, value)
+    assert dctx.decode_rows == 4 and dctx.decode_max_ctx == 1001 and dctx.rest_max_q_len == portion
+    dctx.scratch = {}
+    before = k().launch_count()
+    got = k().paged_attention(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, window)
+    assert k().launch_count() - before == 2 and dctx.status.tolist()[0] == 0
+    close(got, ref, torch.bfloat16, "mixed step attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
+
+
 @pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES)
 @pytest.mark.parametrize("window", [0, 70])
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
