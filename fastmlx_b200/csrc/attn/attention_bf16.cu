@@ -563,6 +563,21 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
   }
 }
 
+// ---- the splits of a row as one thread-block cluster ----
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A float of block `rank` of this cluster, at the place where this block has `local`.
+__device__ __forceinline__ float ld_cluster(const float* local, unsigned rank) {
+  unsigned remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+constexpr int MAX_CLUSTER = 8;           // splits that can be one cluster (the portable size; clusters of 9 placed badly:
+                                         // batch 8 over 8,192 keys at head size 64 38.6 us against 27.8 through tickets)
+
 // ------------------------------------------------------------------------------------ decode
 // part_o: [R, nkv, splits, 16, HD] float; part_ml: [R, nkv, splits, 16, 2] float (max in the
 // scaled log2 domain, sum).  With one split the output is written directly.
@@ -571,7 +586,7 @@ __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int* block_tables, int bt_stride,
                    const int* row_start, const int* positions, bf16* out, float* part_o, float* part_ml, int nh, int nkv,
                    int page_size, long long num_pages, float scale, int window, int* status, int* tickets,
-                   const float* __restrict__ inv_freq, int rot, int interleaved, int rope_mode) {
+                   const float* __restrict__ inv_freq, int rot, int interleaved, int rope_mode, int clustered) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   const int split = blockIdx.x, splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
@@ -779,6 +794,8 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
   // merge the four warps: each leaves (m, l, o) of its up to 16 heads
   float* mo = reinterpret_cast<float*>(smem_raw);    // [4][16][MO_ROW]
   float* mml = mo + 4 * 16 * MO_ROW;                 // [4][16][2]
+  float* fin_o = mml + 4 * 16 * 2;                   // [16][HD]: the block's partial, where its cluster reads it
+  float* fin_ml = fin_o + 16 * HD;                   // [16][2]
 #pragma unroll
   for (int h = 0; h < NH; ++h)
 #pragma unroll
@@ -815,6 +832,12 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
     }
     if (splits == 1) {
       out[((long long)t * nh + g * rep + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else if (clustered) {
+      fin_o[row * HD + d] = acc;
+      if (d == 0) {
+        fin_ml[row * 2] = M;
+        fin_ml[row * 2 + 1] = L;
+      }
     } else {
       const long long pi = (((long long)r * nkv + g) * splits + split) * 16 + row;
       __stcg(&part_o[pi * HD + d], acc);
@@ -824,7 +847,41 @@ attn_decode_kernel(const bf16* q, long long q_stride, const bf16* kv, const int*
       }
     }
   }
-  if (splits == 1 || tickets == nullptr) return;
+  if (splits == 1) return;
+  if (clustered) {
+    // The splits of this (row, kv head) are the blocks of one cluster (the split is the rank): their partials stay
+    // in shared memory, the cluster's barrier stands where the others write to L2, fence and draw a ticket, and the
+    // first block reads them through distributed shared memory, in split order.  Nobody leaves before it has.
+    cluster_sync_all();
+    if (split == 0) {
+      for (int idx = threadIdx.x; idx < rep * HD; idx += THREADS) {
+        const int row = idx / HD, d = idx - row * HD;
+        float ms[MAX_CLUSTER], ls[MAX_CLUSTER], os[MAX_CLUSTER];
+#pragma unroll
+        for (int sp = 0; sp < MAX_CLUSTER; ++sp) {
+          const bool on = sp < splits;
+          ms[sp] = on ? ld_cluster(fin_ml + row * 2, sp) : -INFINITY;
+          ls[sp] = on ? ld_cluster(fin_ml + row * 2 + 1, sp) : 0.f;
+          os[sp] = on ? ld_cluster(fin_o + row * HD + d, sp) : 0.f;
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int sp = 0; sp < MAX_CLUSTER; ++sp) M = fmaxf(M, ms[sp]);
+        const float Mu = M == -INFINITY ? 0.f : M;
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < MAX_CLUSTER; ++sp) {
+          const float f = exp2f(ms[sp] - Mu);        // 0 for the splits that are not there
+          L += f * ls[sp];
+          acc += f * os[sp];
+        }
+        out[((long long)t * nh + g * rep + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      }
+    }
+    cluster_sync_all();
+    return;
+  }
+  if (tickets == nullptr) return;
   // The block that draws the last ticket of this (row, kv head) combines the splits, in split
   // order.  Nobody waits: the others are done once their partial is written.
   __shared__ int drew_last;
@@ -900,7 +957,7 @@ __global__ void attn_combine_kernel(const float* part_o, const float* part_ml, c
 constexpr size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * TILE * sizeof(bf16); }
 constexpr size_t decode_smem(int kg = 1) {
   const size_t pipe = (size_t)DECODE_STAGES * 2 * 4 * 16 * kg * ROW * sizeof(bf16);
-  const size_t merge = (size_t)(4 * 16 * MO_ROW + 4 * 16 * 2) * sizeof(float);
+  const size_t merge = (size_t)(4 * 16 * MO_ROW + 4 * 16 * 2 + 16 * HD + 16 * 2) * sizeof(float);
   return pipe > merge ? pipe : merge;
 }
 // Blocks of the larger tile that an SM holds; the grids that are resident at once with it take it.  (The unsplit
@@ -912,8 +969,33 @@ bool decode_few(dim3 grid) {
   return FEW_KG > 1 && (long long)grid.x * grid.y * grid.z <= few_per_sm() * fmx_num_sms();
 }
 template <int NH, int KG> cudaError_t configure_decode_one() {
-  return cudaFuncSetAttribute(attn_decode_kernel<DECODE_STAGES, NH, KG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)decode_smem(KG));
+  cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<DECODE_STAGES, NH, KG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)decode_smem(KG));
+  return e;
+}
+// Can the `splits` blocks of a (row, kv head) run as one cluster?  Asked of the runtime once per size and kernel.
+bool g_clusters_allowed = true;
+template <int NH, int KG> bool cluster_fits(int splits, dim3 grid) {
+  static int known[MAX_CLUSTER + 1];                 // 0: not asked yet, 1: yes, 2: no
+  if (!g_clusters_allowed || splits < 2 || splits > MAX_CLUSTER) return false;
+  if (known[splits] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = decode_smem(KG);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel<DECODE_STAGES, NH, KG>, &cfg);
+    if (e != cudaSuccess) cudaGetLastError();
+    known[splits] = (e == cudaSuccess && n > 0) ? 1 : 2;
+  }
+  return known[splits] == 1;
 }
 cudaError_t configure_decode() {
   cudaError_t e = configure_decode_one<1, 1>();
@@ -934,6 +1016,14 @@ cudaError_t configure_decode() {
 }  // namespace
 
 FMX_EXPORT int fmx_attn_head_dim() { return HD; }
+
+// 0: the splits of a row always combine through L2 and tickets, as they do where a cluster does not fit (for tests
+// and timings of that path); 1, the default: through a cluster's shared memory where one fits.  -> the old setting
+FMX_EXPORT int fmx_attn_decode_allow_clusters(int allow) {
+  const int old = g_clusters_allowed ? 1 : 0;
+  g_clusters_allowed = allow != 0;
+  return old;
+}
 
 // Floats of scratch the decode entry needs for (rows, nkv, splits): partial outputs, then
 // their maxima and sums.
@@ -957,6 +1047,9 @@ FMX_EXPORT int fmx_attn_decode_plan(int rows, int nkv, long long max_ctx, int sm
   const long long by_keys = (max_ctx + 127) / 128;
   if (s > by_keys) s = by_keys;
   if (s > 32) s = 32;
+  // up to 8 splits are one cluster and combine in shared memory, which is worth more than a ninth split (batch 8 over
+  // 8,192 keys at head size 64: 8 splits 26.4 us, 9 through tickets 28.9)
+  if (s > MAX_CLUSTER && s < 2 * MAX_CLUSTER) s = MAX_CLUSTER;
   return s < 1 ? 1 : (int)s;
 }
 
@@ -1016,10 +1109,21 @@ FMX_EXPORT int fmx_attn_decode(const void* q, long long q_stride, const void* kv
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (long long)rows * nkv * splits * 16 * HD : nullptr;
   dim3 grid(splits, nkv, rows);
+  // With tickets (the engine's calls) and few enough splits, the splits of a row are one cluster and combine through
+  // distributed shared memory: no partial goes through L2.
 #define FMX_DECODE_LAUNCH(NHG, KGR)                                                                                    \
-  fmx_launch(attn_decode_kernel<DECODE_STAGES, NHG, KGR>, grid, dim3(THREADS), decode_smem(KGR), stream, (const bf16*)q, q_stride,       \
-             (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o, part_ml, nh, nkv,      \
-             page_size, num_pages, scale, window, status, tickets, inv_freq, rot, interleaved, rope_mode)
+  do {                                                                                                                  \
+    if (tickets != nullptr && cluster_fits<NHG, KGR>(splits, grid))                                                     \
+      fmx_launch_cluster(attn_decode_kernel<DECODE_STAGES, NHG, KGR>, grid, dim3(THREADS), decode_smem(KGR), stream,    \
+                         dim3(splits, 1, 1), (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride,        \
+                         row_start, positions, (bf16*)out, part_o, part_ml, nh, nkv, page_size, num_pages, scale,       \
+                         window, status, tickets, inv_freq, rot, interleaved, rope_mode, 1);                            \
+    else                                                                                                                \
+      fmx_launch(attn_decode_kernel<DECODE_STAGES, NHG, KGR>, grid, dim3(THREADS), decode_smem(KGR), stream,            \
+                 (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out,  \
+                 part_o, part_ml, nh, nkv, page_size, num_pages, scale, window, status, tickets, inv_freq, rot,         \
+                 interleaved, rope_mode, 0);                                                                            \
+  } while (0)
   FMX_DECODE_DISPATCH(grid, nh / nkv, FMX_DECODE_LAUNCH);
 #undef FMX_DECODE_LAUNCH
   FMX_LAUNCH_CHECK();
@@ -1103,7 +1207,7 @@ FMX_EXPORT int fmx_attn_decode_noalloc(const void* q, long long q_stride, const 
 #define FMX_DECODE_LAUNCH(NHG, KGR)                                                                                    \
   attn_decode_kernel<DECODE_STAGES, NHG, KGR><<<grid, THREADS, decode_smem(KGR), stream>>>(                                              \
       (const bf16*)q, q_stride, (const bf16*)kv, block_tables, bt_stride, row_start, positions, (bf16*)out, part_o,     \
-      part_ml, nh, nkv, page_size, num_pages, scale, window, status, (int*)nullptr, (const float*)nullptr, 0, 0, 0)
+      part_ml, nh, nkv, page_size, num_pages, scale, window, status, (int*)nullptr, (const float*)nullptr, 0, 0, 0, 0)
   FMX_DECODE_DISPATCH(grid, nh / nkv, FMX_DECODE_LAUNCH);
 #undef FMX_DECODE_LAUNCH
   FMX_LAUNCH_CHECK();

@@ -417,6 +417,12 @@ def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale, variant:
     return out
 
 
+def decode_attention_clusters(hd: int, allow: bool) -> bool:
+    """Let the split decode attention of head size `hd` combine a row's splits inside a thread-block
+    cluster (the default) or make it take the path through L2 and tickets; -> the old setting."""
+    return bool(load(f"attn_hd{hd}").fmx_attn_decode_allow_clusters(int(bool(allow))))
+
+
 def decode_attention_fuses_rope(qkv, kv, ctx, nh, nkv, hd) -> bool:
     """Will `paged_attention` take this step on the split decode kernel, which can rotate q and
     k and store k and v itself?"""

@@ -456,7 +456,7 @@ def test_mixed_step_attention_takes_two_kernels(nh, nkv, hd, page_size, window, 
 
 @pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES)
 @pytest.mark.parametrize("window", [0, 70])
-@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+@pytest.mark.parametrize("splits", [1, 2, 5, 8, 9, 32])
 def test_split_decode_attention(nh, nkv, hd, page_size, window, splits):
     rows = [(0, 1), (1, 1), (63, 1), (64, 1), (65, 1), (300, 1), (1000, 1), (127, 1)]
     q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, window)
@@ -465,6 +465,16 @@ def test_split_decode_attention(nh, nkv, hd, page_size, window, splits):
     got = k().paged_attention_decode(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, window, splits=splits)
     assert dctx.status.tolist()[0] == 0
     close(got, ref, torch.bfloat16, "split decode attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
+    # up to 8 splits are one thread-block cluster; the same through L2 and tickets, as where no cluster fits
+    was = k().decode_attention_clusters(hd, False)
+    try:
+        again = k().paged_attention_decode(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, window, splits=splits)
+    finally:
+        k().decode_attention_clusters(hd, was)
+    assert was and dctx.status.tolist()[0] == 0
+    close(again, ref, torch.bfloat16, "split decode attention through tickets", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
+    if splits <= 8:
+        assert torch.equal(again, got)          # both sum the splits in split order
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES)
