@@ -43,7 +43,7 @@ def test_filters_match_the_reference_fixture():
         assert got[0].tolist() == case["kept"], case["label"]
 
 
-@pytest.mark.parametrize("V", [12, 131, 1000, 5000])
+@pytest.mark.parametrize("V", [12, 131, 1000, 5000, 16385, 40000, 128256])     # above 16,384: a cluster of blocks per row
 @pytest.mark.parametrize("params", [dict(top_p=0.9), dict(top_p=0.3), dict(min_p=0.05), dict(min_p=0.5, min_keep=7),
                                      dict(top_k=1), dict(top_k=40), dict(top_p=0.95, min_p=0.02, top_k=50),
                                      dict(top_p=0.5, top_k=3, min_p=0.9, min_keep=5)])
