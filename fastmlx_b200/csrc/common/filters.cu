@@ -227,7 +227,7 @@ __device__ __forceinline__ float fc_peer(const float* local, unsigned rank) {
 // that a block may write its next partial while a peer still reads the last one (a peer that has passed the
 // barrier of exchange n has finished reading exchange n - 1).
 struct FcExchange {
-  float* part;      // [2] in shared memory, the same place in every block
+  float* part;      // [4] in shared memory, the same place in every block: two slots of up to two values
   int at;
   __device__ float sum(float v) {
     v = fblock_sum(v);
@@ -249,17 +249,39 @@ struct FcExchange {
     at ^= 1;
     return s;
   }
-  // exclusive prefix in index order (rank, then thread), and nothing else
-  __device__ float exscan(float v) {
+  // two maxima in one exchange
+  __device__ void max2(float& a, float& b) {
+    a = fblock_max(a);
+    b = fblock_max(b);
+    if (threadIdx.x == 0) {
+      part[at] = a;
+      part[2 + at] = b;
+    }
+    fc_sync();
+    a = b = -INFINITY;
+#pragma unroll
+    for (unsigned r = 0; r < FC; ++r) {
+      a = fmaxf(a, fc_peer(part + at, r));
+      b = fmaxf(b, fc_peer(part + 2 + at, r));
+    }
+    at ^= 1;
+  }
+  // exclusive prefix in index order (rank, then thread); *all: the sum over the whole cluster, in rank order
+  __device__ float exscan(float v, float* all = nullptr) {
     float total;
     const float before = fblock_exscan(v, &total);
     if (threadIdx.x == 0) part[at] = total;
     fc_sync();
-    float lower = 0.f;
+    float lower = 0.f, whole = 0.f;
     const unsigned me = fc_rank();
 #pragma unroll
-    for (unsigned r = 0; r < FC; ++r) lower += r < me ? fc_peer(part + at, r) : 0.f;
+    for (unsigned r = 0; r < FC; ++r) {
+      const float t = fc_peer(part + at, r);
+      lower += r < me ? t : 0.f;
+      whole += t;
+    }
     at ^= 1;
+    if (all != nullptr) *all = whole;
     return lower + before;
   }
 };
@@ -300,13 +322,14 @@ template <int EPT>
 __global__ void __launch_bounds__(FBLOCK)
 filter_mask_cluster_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ top_p,
                            const float* __restrict__ min_p, const int* __restrict__ top_k,
-                           const int* __restrict__ min_keep, unsigned char* __restrict__ keep, long long keep_ld) {
-  __shared__ float part[2];
+                           const int* __restrict__ min_keep, unsigned char* __restrict__ keep, long long keep_ld,
+                           const float* __restrict__ temperature, const float* __restrict__ uniform, int* __restrict__ out) {
+  __shared__ float part[4];
   FcExchange x{part, 0};
   const int r = blockIdx.x / FC;
   const unsigned rank = fc_rank();
   const float* row = logits + (long long)r * ld;
-  unsigned char* flags = keep + (long long)r * keep_ld;
+  unsigned char* flags = keep ? keep + (long long)r * keep_ld : nullptr;
   const int base = ((int)rank * FBLOCK + threadIdx.x) * EPT;      // thread-contiguous: index order is (rank, thread, e)
   float val[EPT];
   unsigned key[EPT];
@@ -378,9 +401,49 @@ filter_mask_cluster_kernel(const float* __restrict__ logits, long long ld, int V
   const int kk = top_k ? top_k[r] : 0;
   if (kk > 0 && kk < V) alive &= fc_top_k<EPT>(key, alive, kk, x);
 
+  if (flags != nullptr) {
 #pragma unroll
-  for (int e = 0; e < EPT; ++e)
-    if ((valid >> e) & 1u) flags[base + e] = (alive >> e) & 1u;
+    for (int e = 0; e < EPT; ++e)
+      if ((valid >> e) & 1u) flags[base + e] = (alive >> e) & 1u;
+  }
+  if (out != nullptr) {
+    // The token, as sample_kernel chooses it from a keep mask: the first index of the largest logit at temperature 0
+    // (the largest logit is always kept), else the inverse-CDF walk in index order over exp((logit - max) / T).
+    const float T = temperature ? temperature[r] : 0.f;
+    const float inv_t = T > 0.f ? 1.0f / T : 0.f;
+    float cand = -INFINITY, last = -INFINITY;          // minus the first index of the largest logit; the last index with weight
+#pragma unroll
+    for (int e = EPT - 1; e >= 0; --e)
+      if (((alive >> e) & 1u) && val[e] == mx) cand = -(float)(base + e);
+#pragma unroll
+    for (int e = 0; e < EPT; ++e)
+      if (((alive >> e) & 1u) && expf((val[e] - mx) * inv_t) > 0.f) last = (float)(base + e);
+    x.max2(cand, last);                                // indices are below 2^24: exact as floats
+    // What stands unless a thread below finds the target inside its own share: the mode at temperature 0; else the
+    // last token with weight, which is where a target within rounding of the total belongs.
+    if (rank == 0 && threadIdx.x == 0) out[r] = T > 0.f && last >= 0.f ? (int)last : (int)(-cand);
+    if (T > 0.f) {
+      float mine = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) mine += ((alive >> e) & 1u) ? expf((val[e] - mx) * inv_t) : 0.f;
+      float total;
+      const float before = x.exscan(mine, &total);     // its barrier also orders the store above before the draw's
+      const float target = uniform[r] * total;
+      if (mine > 0.f && target >= before && target < before + mine) {
+        float run = before;
+        int pick = -1;
+#pragma unroll
+        for (int e = 0; e < EPT; ++e) {
+          const float wgt = ((alive >> e) & 1u) ? expf((val[e] - mx) * inv_t) : 0.f;
+          if (wgt > 0.f && (pick < 0 || target >= run)) {       // the first element whose running sum passes the target
+            pick = base + e;
+            run += wgt;
+          }
+        }
+        out[r] = pick;
+      }
+    }
+  }
   fc_sync();                                           // nobody leaves while a peer may still read its sums
 }
 
@@ -432,36 +495,61 @@ __global__ void logit_bias_kernel(float* __restrict__ logits, long long ld, int 
 }
 }  // namespace
 
+namespace {
+// A wide row goes to a cluster of FC blocks with the row in registers; narrow ones, and rows beyond 131,072 (whose
+// share per thread would not fit the registers of a 1024-thread block), to one block.
+bool row_fits_a_cluster(int V) { return V > 16384 && (V + FC * FBLOCK - 1) / (FC * FBLOCK) <= 16; }
+
+int launch_cluster_filter(const float* logits, long long ld, int rows, int V, const float* top_p, const float* min_p,
+                          const int* top_k, const int* min_keep, unsigned char* keep, long long keep_ld,
+                          const float* temperature, const float* uniform, int* out, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)rows * FC);
+  cfg.blockDim = dim3(FBLOCK);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = FC;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, filter_mask_cluster_kernel<16>, logits, ld, V, top_p, min_p, top_k, min_keep, keep,
+                                     keep_ld, temperature, uniform, out);
+  if (e != cudaSuccess) return fmx_fail("the filters' cluster kernel: launch failed: %s", cudaGetErrorString(e));
+  FMX_LAUNCH_CHECK();
+  return 0;
+}
+}  // namespace
+
 FMX_EXPORT int fmx_filter_mask(const float* logits, long long ld, int rows, int V, const float* top_p,
                                const float* min_p, const int* top_k, const int* min_keep, unsigned char* keep,
                                long long keep_ld, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (rows < 0 || V <= 0 || ld < V || keep_ld < V) return fmx_fail("fmx_filter_mask: bad sizes rows=%d V=%d", rows, V);
   if (V > (1 << 24)) return fmx_fail("fmx_filter_mask: a vocabulary of %d is beyond exact float counting", V);
-  // wide rows: a cluster of FC blocks per row with the row in registers; narrow ones (and rows beyond 131,072, whose
-  // share per thread would not fit the registers of a 1024-thread block): one block
-  const int per_thread = (V + FC * FBLOCK - 1) / (FC * FBLOCK);
-  if (V > 16384 && per_thread <= 16) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)rows * FC);
-    cfg.blockDim = dim3(FBLOCK);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = FC;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, filter_mask_cluster_kernel<16>, logits, ld, V, top_p, min_p, top_k, min_keep, keep,
-                                       keep_ld);
-    if (e != cudaSuccess) return fmx_fail("fmx_filter_mask: launch failed: %s", cudaGetErrorString(e));
-    FMX_LAUNCH_CHECK();
-    return 0;
-  }
+  if (row_fits_a_cluster(V))
+    return launch_cluster_filter(logits, ld, rows, V, top_p, min_p, top_k, min_keep, keep, keep_ld, nullptr, nullptr, nullptr,
+                                 stream);
   filter_mask_kernel<<<rows, FBLOCK, 0, stream>>>(logits, ld, V, top_p, min_p, top_k, min_keep, keep, keep_ld);
   FMX_LAUNCH_CHECK();
   return 0;
+}
+
+// Can fmx_filter_sample take rows of this width?
+FMX_EXPORT int fmx_filter_sample_takes(int V) { return row_fits_a_cluster(V) ? 1 : 0; }
+
+// Filters and the choice of the token in one kernel, no keep mask in memory: out[r] as fmx_sample would choose it
+// from the mask that fmx_filter_mask would have written (any filter argument may be null: off).  Rows of the widths
+// that fmx_filter_sample_takes only.
+FMX_EXPORT int fmx_filter_sample(const float* logits, long long ld, int rows, int V, const float* temperature,
+                                 const float* uniform, const float* top_p, const float* min_p, const int* top_k,
+                                 const int* min_keep, int* out, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (rows < 0 || V <= 0 || ld < V) return fmx_fail("fmx_filter_sample: bad sizes rows=%d V=%d", rows, V);
+  if (!row_fits_a_cluster(V)) return fmx_fail("fmx_filter_sample: rows of %d logits go to fmx_filter_mask and fmx_sample", V);
+  if (temperature != nullptr && uniform == nullptr) return fmx_fail("fmx_filter_sample: a temperature needs uniform numbers");
+  return launch_cluster_filter(logits, ld, rows, V, top_p, min_p, top_k, min_keep, nullptr, 0, temperature, uniform, out, stream);
 }
 
 FMX_EXPORT int fmx_penalties(float* logits, long long ld, int rows, int V, const int* history, int H,

@@ -532,6 +532,24 @@ def filter_mask(logits, top_p=None, min_p=None, top_k=None, min_keep=None) -> to
     return keep
 
 
+def filter_sample_takes(V: int) -> bool:
+    """Rows of this width can be filtered and sampled by one kernel (`filter_sample`)."""
+    return bool(load("common").fmx_filter_sample_takes(int(V)))
+
+
+def filter_sample(logits, temperature, uniform, top_p=None, min_p=None, top_k=None, min_keep=None) -> torch.Tensor:
+    """The token of each row after its filters, in one kernel and without a keep mask in memory:
+    what `sample(logits, temperature, uniform, filter_mask(logits, ...))` gives.  A row is spread
+    over a thread-block cluster with its logits in registers."""
+    _need_cuda(logits, temperature, uniform, top_p, min_p, top_k, min_keep)
+    assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    call("common", "fmx_filter_sample", logits.data_ptr(), logits.stride(0), rows, V, _ptr(temperature), _ptr(uniform),
+         _ptr(top_p), _ptr(min_p), _ptr(top_k), _ptr(min_keep), out.data_ptr(), _stream())
+    return out
+
+
 def penalties(logits, history, repetition, presence, frequency, windows) -> None:
     """In place on float32 logits [rows, V].  history int32 [rows, H] (oldest first, -1 padded
     in front); repetition/presence/frequency float32 [rows] or None; windows int32 [rows, 3]."""

@@ -29,6 +29,7 @@ _SIGNATURES = {
         "fmx_paged_attention_simple": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _P, _P],
         "fmx_sample": [_P, _L, _I, _I, _P, _P, _P, _L, _P, _I, _P, _I, _P, _I, _P],
         "fmx_filter_mask": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _L, _P],
+        "fmx_filter_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
         "fmx_penalties": [_P, _L, _I, _I, _P, _I, _P, _P, _P, _P, _P],
         "fmx_logit_bias": [_P, _L, _I, _P, _P, _P, _I, _P],
     },

@@ -126,5 +126,10 @@ class Sampler:
         if greedy:
             return k.sample(logits)
         par_d, ints_d = dev
+        if hasattr(k, "filter_sample") and k.filter_sample_takes(logits.shape[1]):
+            # wide rows: filters and draw in one kernel, a row on a cluster of blocks, no mask in memory
+            if filters:
+                return k.filter_sample(logits, par_d[0], par_d[1], par_d[2], par_d[3], ints_d[0], ints_d[1])
+            return k.filter_sample(logits, par_d[0], par_d[1])
         keep = k.filter_mask(logits, par_d[2], par_d[3], ints_d[0], ints_d[1]) if filters else None
         return k.sample(logits, par_d[0], par_d[1], keep)

@@ -85,6 +85,42 @@ def test_large_vocabulary_top_k_and_top_p():
         assert p[~got[r].bool()].max() <= kept.min()
 
 
+@pytest.mark.parametrize("V", [16385, 50001, 128256])
+@pytest.mark.parametrize("params", [dict(), dict(top_p=0.9), dict(top_k=40), dict(min_p=0.05, min_keep=3),
+                                     dict(top_p=0.95, min_p=0.02, top_k=50)])
+def test_filters_and_draw_in_one_kernel(V, params):
+    """Wide rows: one kernel filters and draws, a row on a cluster of blocks.  Its token lies in the
+    set that the filter kernel alone keeps, its interval of the kept tokens' CDF holds the uniform
+    number, a row at temperature 0 takes the first largest logit, and a row's token does not
+    depend on the rows beside it."""
+    rows = 12
+    g = torch.Generator().manual_seed(V + len(params))
+    logits = torch.randn(rows, V, generator=g) * 3
+    logits[3, 100] = logits[3, 7] = logits[3].max() + 1.0              # a tie for the largest: the lower index
+    temps = torch.tensor([0.0, 0.7, 1.0, 1.5] * (rows // 4))
+    u = torch.rand(rows, generator=g)
+    u[1], u[2] = 0.0, 0.99999994
+    f = lambda name, dt: torch.full((rows,), params.get(name, 0 if name != "min_keep" else 1), dtype=dt, device=DEV)
+    args = (f("top_p", torch.float32), f("min_p", torch.float32), f("top_k", torch.int32), f("min_keep", torch.int32))
+    dev = logits.to(DEV)
+    assert k().filter_sample_takes(V)
+    got = k().filter_sample(dev, temps.to(DEV), u.to(DEV), *(args if params else ())).cpu()
+    keep = k().filter_mask(dev, *args).cpu().bool() if params else torch.ones(rows, V, dtype=torch.bool)
+    for r in range(rows):
+        i = int(got[r])
+        assert keep[r, i], (r, i)
+        if temps[r] == 0:
+            assert i == int(torch.argmax(logits[r])) and (r != 3 or i == 7)
+            continue
+        w = torch.softmax(torch.where(keep[r], logits[r].double(), torch.tensor(-float("inf"), dtype=torch.float64))
+                          / temps[r].double(), 0)
+        c = torch.cumsum(w, 0)
+        lo, hi = (c[i - 1].item() if i > 0 else 0.0), c[i].item()
+        assert lo - 1e-4 <= u[r].item() <= hi + 1e-4 and w[i] > 0, (r, i, lo, u[r].item(), hi)
+    alone = k().filter_sample(dev[5:6].contiguous(), temps[5:6].to(DEV), u[5:6].to(DEV), *((a[5:6] for a in args) if params else ()))
+    assert int(alone[0]) == int(got[5])
+
+
 def test_processors_match_the_reference_fixture():
     cases = CASES["processors"]
     from fastmlx_b200.engine.loading import make_runtime
