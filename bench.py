@@ -16,7 +16,8 @@ timed; nothing reaches around the scheduler.  One JSON line is printed:
   prefill    one 2,048-token prompt, whole; frac = flops / time / bf16 peak
   roofline   bytes a decode step must read (every weight once, the cache of the live requests)
              / its time, against the measured copy bandwidth
-  points     decode tokens per second at batch 1 and 64 (same context)
+  points     decode tokens per second at batch 1 and 64 (same context), and at the headline batch with the
+             reference's default sampling (temperature 1, top_p 0.95) instead of greedy
   shapes     for the layer sizes of Llama-3.2-1B, 3.2-3B and 3.1-8B: batches of 1, 8 and 64 requests
              with 2,048-token prompts and 256 generated tokens each, run to the end under the
              scheduler, with prefill and decode rates, time to first token and time per output
@@ -175,10 +176,10 @@ def _first_tokens(engine, ids, seen=None, times=None) -> None:
                     times[out.request_id] = time.perf_counter()
 
 
-def fill(engine, batch: int, prompt_len: int, vocab: int, seed: int) -> list[str]:
+def fill(engine, batch: int, prompt_len: int, vocab: int, seed: int, sp_kw: dict | None = None) -> list[str]:
     """Submit `batch` requests that never end by themselves and step until each has drawn its first token."""
     from fastmlx_b200 import SamplingParams
-    sp = SamplingParams(max_tokens=1 << 20, **SP_KW)
+    sp = SamplingParams(max_tokens=1 << 20, **(sp_kw or SP_KW))
     ids = [engine.submit(rand_prompt(prompt_len, vocab, seed + i), sp) for i in range(batch)]
     _first_tokens(engine, ids)
     return ids
@@ -227,7 +228,7 @@ MIN_REGION_MS = 200.0        # timed work per measurement, whatever --steps says
 
 
 def steady_decode(engine, batch: int, context: int, steps: int, warmup: int, vocab: int, nums: dict, e2e: bool,
-                  clock: ClockSampler | None = None, est_ms: float = 1.0) -> dict:
+                  clock: ClockSampler | None = None, est_ms: float = 1.0, sp_kw: dict | None = None) -> dict:
     """Steady decoding of `batch` requests whose contexts end at `context`: the scheduler prefills,
     then regions of `steps` steps are timed, first by CUDA events, then (e2e) by the host's clock."""
     import torch
@@ -235,7 +236,7 @@ def steady_decode(engine, batch: int, context: int, steps: int, warmup: int, voc
     wall_regions = max(3, regions // 2) if e2e else 0
     grow = warmup * (2 if e2e else 1) + steps * (regions + wall_regions) + 4
     prompt_len = max(16, context - grow)
-    ids = fill(engine, batch, prompt_len, vocab, seed=1000 * batch)
+    ids = fill(engine, batch, prompt_len, vocab, seed=1000 * batch, sp_kw=sp_kw)
     for _ in range(warmup):
         engine.step()
     k = engine.rt.k
@@ -433,6 +434,10 @@ def main() -> int:
         for b in (1, 64):
             pt = steady_decode(engine, b, args.context, min(steps, 64), warmup, vocab, nums, False, None, probe["ms"])
             points[f"decode_b{b}"] = round(b / (pt["ms"] / 1e3), 1)
+        # the headline batch with the reference's default sampling (temperature 1, top_p 0.95) instead of greedy
+        pt = steady_decode(engine, args.batch, args.context, min(steps, 64), warmup, vocab, nums, False, None, probe["ms"],
+                           dict(temperature=1.0, top_p=0.95, ignore_eos=True))
+        points[f"decode_b{args.batch}_top_p"] = round(args.batch / (pt["ms"] / 1e3), 1)
     stats = engine.stats()
     del engine
     gc.collect()

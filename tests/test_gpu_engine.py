@@ -93,6 +93,35 @@ def test_mixed_batch_with_temperature_is_reproducible_and_cut_invariant(dirs):
     assert all(probs[i, t] > 1e-4 for i, t in enumerate(base[1]))
 
 
+def test_sampling_over_a_wide_vocabulary_is_reproducible(tmp_path):
+    """A vocabulary of 16,640: the filters and the draw of a row run in one kernel on a cluster of
+    blocks.  With the reference's default filter (top_p 0.95) and with top-k and min-p, the
+    tokens of a request do not depend on what runs beside it or on how its prompt is cut, and the
+    plain model, fed the engine's tokens, gives each of them a probability that the filters keep."""
+    from fastmlx_b200 import Engine, SamplingParams
+    cfg = dict(tiny.TINY_A, vocab_size=16640)
+    path = tiny.make_model_dir(tmp_path, cfg, seed=5)
+    prompts = [tiny.rand_tokens(n, cfg["vocab_size"], 70 + n) for n in (3, 40, 90)]
+    sps = [SamplingParams(max_tokens=12, temperature=1.0, seed=1),                               # top_p 0.95 by default
+           SamplingParams(max_tokens=12, temperature=0.8, top_p=0.9, top_k=50, seed=2),
+           SamplingParams(max_tokens=12, temperature=1.3, top_p=1.0, min_p=0.01, seed=3)]
+
+    def run(**kw):
+        eng = Engine(path, dtype="float32", block_size=16, max_cache_tokens=1024, **kw)
+        return [o.output_token_ids for o in eng.generate(prompts, sps)]
+
+    base = run(max_concurrent_requests=4)
+    assert all(len(t) == 12 for t in base)
+    assert run(max_concurrent_requests=1, max_num_batched_tokens=16, prefill_chunk=7, cuda_graphs=False) == base
+    eng = Engine(path, dtype="float32", block_size=16, max_cache_tokens=1024)
+    for p, sp, want in zip(prompts, sps, base):
+        assert eng.generate([p], sp)[0].output_token_ids == want
+    W = tiny.load_plain_weights(path)
+    logits = plain_llama.forward(cfg, W, prompts[1] + base[1])[len(prompts[1]) - 1: -1]
+    for i, t in enumerate(base[1]):                       # top-k 50: the token is among the 50 most likely
+        assert t in torch.topk(logits[i], 50).indices.tolist()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_preemption_changes_no_token(dirs, dtype):
     """With a pool of 18 pages three requests cannot all grow: the newest is preempted and
