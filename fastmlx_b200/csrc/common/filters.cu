@@ -229,9 +229,18 @@ __device__ __forceinline__ float fc_peer(const float* local, unsigned rank) {
 struct FcExchange {
   float* part;      // [4] in shared memory, the same place in every block: two slots of up to two values
   int at;
+  float (*warps)[FBLOCK / 32];      // [2][32]: the warps' partials of the block's own sum, two slots as well
+  // One block barrier and one cluster barrier per exchange (a bisection makes 32 of them): the warps' sums meet in
+  // the first warp, whose first lane leaves the block's sum where the cluster reads it.
   __device__ float sum(float v) {
-    v = fblock_sum(v);
-    if (threadIdx.x == 0) part[at] = v;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    if (lane == 0) warps[at][warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      const float s = warp_sum(warps[at][lane]);
+      if (lane == 0) part[at] = s;
+    }
     fc_sync();
     float s = 0.f;
 #pragma unroll
@@ -325,7 +334,8 @@ filter_mask_cluster_kernel(const float* __restrict__ logits, long long ld, int V
                            const int* __restrict__ min_keep, unsigned char* __restrict__ keep, long long keep_ld,
                            const float* __restrict__ temperature, const float* __restrict__ uniform, int* __restrict__ out) {
   __shared__ float part[4];
-  FcExchange x{part, 0};
+  __shared__ float warps[2][FBLOCK / 32];
+  FcExchange x{part, 0, warps};
   const int r = blockIdx.x / FC;
   const unsigned rank = fc_rank();
   const float* row = logits + (long long)r * ld;
