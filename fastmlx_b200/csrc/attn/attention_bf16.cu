@@ -10,11 +10,14 @@
 //    scores, running maximum and sum, and the output accumulator are 32-bit (flash-style
 //    online softmax).  It takes any mix of rows: portions of prompts and single tokens.
 //
-//  * decode: every row brings one token.  A block owns (a split of the keys, a kv head, a
-//    row); its four warps take 16 keys each of every 64-key tile for the same <=16 query
-//    heads, merge at the end and write either the output or an unnormalised partial
-//    (maximum, sum, accumulator) that a second kernel combines.  Nothing waits on another
-//    block: there is no spin and nothing to hang.
+//  * decode: every row brings one token.  A block owns (a split of the keys, a kv head, a row).  The keys are
+//    the rows of the MMA and up to 8 query heads its columns (S^T = K Q^T, O^T += V^T P^T), so the few heads of
+//    a kv head are not padded to 16 rows.  Each of the four warps streams tiles of its own through its own ring
+//    in shared memory (cp.async, no block barrier in the loop); the warps merge at the end.  The splits of a
+//    (row, kv head) are either one thread-block cluster, whose first block adds up the partials (maximum, sum,
+//    accumulator) through distributed shared memory behind the hardware's cluster barrier, or write their
+//    partials to a workspace, where the block that draws the row's last ticket (or a second kernel) combines
+//    them.  No block spins on a flag: there is nothing to hang.
 //
 // Keys out of sight (beyond a row's position, before its window, or in no page) are
 // zero-filled in shared memory and masked, never read from the cache.
