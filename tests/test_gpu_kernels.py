@@ -477,6 +477,30 @@ def test_split_decode_attention(nh, nkv, hd, page_size, window, splits):
         assert torch.equal(again, got)          # both sum the splits in split order
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_split_decode_attention_on_random_shapes(seed):
+    """Shapes drawn at random: head sizes, heads per kv head up to 16, pages of any size, rows of
+    any length with and without a window, every way of splitting (one block, a cluster of up to 8,
+    tickets), and the planner's own choice."""
+    import random
+    rng = random.Random(1000 + seed)
+    hd = rng.choice([16, 32, 48, 64, 64, 80, 96, 128, 128])
+    nkv = rng.choice([1, 2, 3, 8])
+    rep = rng.choice([1, 2, 4, 4, 5, 8, 9, 16])
+    nh = nkv * rep
+    page_size = rng.choice([4, 8, 12, 16, 16, 32, 64])
+    rows = [(rng.choice([0, 1, 15, 16, 17, 63, 64, 65, rng.randrange(100, 3000)]), 1) for _ in range(rng.randint(1, 6))]
+    window = rng.choice([0, 0, rng.randrange(1, 200)])
+    q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, window, seed=seed)
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, window)
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    for splits in (None, 1, rng.randint(2, 8), rng.randint(9, 40)):
+        got = k().paged_attention_decode(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, window, splits=splits)
+        assert dctx.status.tolist()[0] == 0
+        close(got, ref, torch.bfloat16, f"decode attention nh={nh} nkv={nkv} hd={hd} page={page_size} window={window} "
+              f"rows={rows} splits={splits}", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
+
+
 @pytest.mark.parametrize("nh,nkv,hd,page_size", TILED_SHAPES)
 @pytest.mark.parametrize("rot_frac,traditional", [(1.0, False), (0.5, False), (1.0, True), (0.0, False)])
 @pytest.mark.parametrize("splits", [1, 3])
