@@ -5,6 +5,7 @@ launches), for tuning and for profiler captures on a small case.
     python -m fastmlx_b200.kernels.microbench --kernel attn_prefill --batch 1 --qlen 2048
     python -m fastmlx_b200.kernels.microbench --kernel gemv --M 8 --N 2048 --K 8192
     python -m fastmlx_b200.kernels.microbench --kernel gemm --M 2048 --N 16384 --K 2048
+    python -m fastmlx_b200.kernels.microbench --kernel sample --batch 8 --N 128256
 """
 from __future__ import annotations
 
@@ -57,7 +58,7 @@ def _attention_inputs(a, qlen):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "gemv", "gemm"])
+    ap.add_argument("--kernel", required=True, choices=["attn_decode", "attn_prefill", "gemv", "gemm", "sample"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192, help="tokens already in the cache")
     ap.add_argument("--qlen", type=int, default=2048, help="tokens per row (attn_prefill)")
@@ -106,6 +107,22 @@ def main(argv=None) -> int:
             print(f"attn_prefill {name} B={a.batch} ctx={a.ctx} qlen={a.qlen} nh={a.nh} nkv={a.nkv} hd={a.hd}: {us:.1f} us, "
                   f"{flops / us / 1e6:.0f} TFLOP/s")
         print("status", ctx.status.tolist())
+    elif a.kernel == "sample":
+        # filters and draw over --batch rows of --N logits: the reference's default (top_p 0.95), top_p with top_k, none
+        rows, V = a.batch, a.N
+        logits = torch.randn(rows, V, device=DEV) * 2
+        f = lambda v, dt=torch.float32: torch.full((rows,), v, dtype=dt, device=DEV)
+        T, u = f(1.0), torch.rand(rows, device=DEV)
+        cases = [("no filter", ()), ("top_p 0.95", (f(0.95), f(0.0), f(0, torch.int32), f(1, torch.int32))),
+                 ("top_p 0.9, top_k 50", (f(0.9), f(0.0), f(50, torch.int32), f(1, torch.int32)))]
+        for name, args in cases:
+            if not name.startswith(a.only):
+                continue
+            if k.filter_sample_takes(V):
+                us = _time_graph(lambda: k.filter_sample(logits, T, u, *args), a.launches, a.replays)
+                print(f"sample rows={rows} V={V} {name}, one kernel on a cluster per row: {us:.1f} us")
+            us = _time_graph(lambda: k.sample(logits, T, u, k.filter_mask(logits, *args) if args else None), a.launches, a.replays)
+            print(f"sample rows={rows} V={V} {name}, filter kernel then sampling kernel: {us:.1f} us")
     elif a.kernel == "gemm":
         copies = 1 if a.resident else max(1, int(300e6 // (a.N * a.K * 2)) + 1)        # more weight than L2 holds
         ws = [torch.randn(a.N, a.K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
