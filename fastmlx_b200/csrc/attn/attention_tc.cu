@@ -911,6 +911,12 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
     configured = true;
   }
   const int tok_per_tile = BM / rep;
+  // Two query tiles per CTA share every K/V tile and are the faster kernel when the grid fills the GPU.  At head
+  // size 64 a grid of at most half the SMs does better with one tile per CTA and twice the CTAs (one 512-token portion
+  // with 32 query heads: 64 CTAs 13.8 us, 128 CTAs 11.7; behind 32,768 keys 476 and 394 us); at head size 128 the
+  // two-tile kernel wins even then (587 against 803 us).
+  const long long pairs = (long long)nkv * rows * ((max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile));
+  if (variant == 0 && HD == 64 && 2 * pairs <= fmx_num_sms()) variant = 1;      // 0: this choice; 1, 2: the caller's
   if (variant != 1 && two::BN2 % page_size == 0) {      // two query tiles per CTA
     static bool configured2 = false;
     if (!configured2) {

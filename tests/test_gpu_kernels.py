@@ -539,7 +539,7 @@ TC_SHAPES = [(4, 1, 64, 16), (8, 2, 64, 16), (32, 8, 64, 16), (8, 8, 64, 32), (1
              (24, 24, 128, 64), (16, 2, 128, 8), (24, 8, 128, 16), (6, 2, 64, 16), (5, 1, 64, 32), (7, 1, 128, 16)]
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("nh,nkv,hd,page_size", TC_SHAPES)
 def test_tensor_memory_prefill_attention(nh, nkv, hd, page_size, variant):
     """The tcgen05 attention kernel on portions with and without earlier context, single
@@ -549,13 +549,13 @@ def test_tensor_memory_prefill_attention(nh, nkv, hd, page_size, variant):
     ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, 0)
     dctx, dgrp = _full_ctx(rows, ctx, grp)
     assert k().tc_attention_ok(nh, nkv, hd, page_size, 0)
-    # variant 0: two query tiles per CTA where the head size has that kernel; 1: always one
+    # variant 0: the library's choice; 1: one query tile per CTA; 2: two where the page size allows that kernel
     got = k().paged_attention_prefill_tc(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, variant=variant)
     assert dctx.status.tolist()[0] == 0
     close(got, ref, torch.bfloat16, "tensor-memory attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("key_pos", [0, 15, 16, 127, 128, 129, 255, 256, 511, 700])
 def test_tensor_memory_attention_far_key_and_unseen_keys(key_pos, variant):
     """One key among 701 dominates for one head (a tile edge or a page edge that loses it shows

@@ -100,7 +100,7 @@ def test_decode_32_bit_kernel():
 
 # ----------------------------------------------------------------------------- prompt portions
 @pytest.mark.parametrize("nh,nkv,hd,page_size", SHAPES)
-@pytest.mark.parametrize("kernel", ["tc0", "tc1", "mma"])
+@pytest.mark.parametrize("kernel", ["tc2", "tc1", "mma"])
 def test_prefill_random(nh, nkv, hd, page_size, kernel):
     q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, PREFILL_ROWS)
     ref = _ref(q, kv, PREFILL_ROWS, grp, nh, nkv, hd, hd ** -0.5)
@@ -110,7 +110,7 @@ def test_prefill_random(nh, nkv, hd, page_size, kernel):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page_size", SHAPES)
-@pytest.mark.parametrize("kernel", ["tc0", "tc1", "mma"])
+@pytest.mark.parametrize("kernel", ["tc2", "tc1", "mma"])
 @pytest.mark.parametrize("token,key_pos", [(129, 0), (129, 4000), (129, 4129), (0, 4000), (130 + 2099, 1),
                                             (130 + 2099, 2048), (2230, 8000), (2299, 64)])
 def test_prefill_far_key(nh, nkv, hd, page_size, kernel, token, key_pos):
@@ -123,7 +123,7 @@ def test_prefill_far_key(nh, nkv, hd, page_size, kernel, token, key_pos):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page_size", SHAPES)
-@pytest.mark.parametrize("kernel", ["tc0", "tc1", "mma"])
+@pytest.mark.parametrize("kernel", ["tc2", "tc1", "mma"])
 def test_prefill_counts_every_key_once(nh, nkv, hd, page_size, kernel):
     q, kv, ctx, grp = _counting_inputs(torch.bfloat16, nh, nkv, hd, page_size, PREFILL_ROWS)
     ref = _ref(q, kv, PREFILL_ROWS, grp, nh, nkv, hd, hd ** -0.5)
