@@ -424,7 +424,7 @@ __global__ void __launch_bounds__(THREADS2, 1)
 attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                         const int* block_tables, int bt_stride, const int* row_start, const int* row_ctx, bf16* out,
                         int nh, int nkv, int page_size, long long num_pages, long long kv_rows, float scale,
-                        int* status) {
+                        int* status, int ksplits, float* part_o, float* part_ml, int T) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sq = smem;                                             // [2] query tiles
@@ -432,7 +432,11 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   Bars2* bars = reinterpret_cast<Bars2*>(skv + (size_t)KV_ST * (K2_BYTES + V2_BYTES));
 
   // the pairs that see the most keys start first, for every head and row (see the one-tile kernel)
-  const int r = blockIdx.y, g = blockIdx.x, pair = gridDim.z - 1 - blockIdx.z;
+  // With `ksplits` > 1 the keys of a pair of query tiles are shared out over that many CTAs (z = pair * ksplits +
+  // split): each leaves unnormalised outputs with their scale and sum, and a second kernel combines them.  That is
+  // for grids that would leave most SMs idle: one 512-token portion behind tens of thousands of keys.
+  const int r = blockIdx.y, g = blockIdx.x, zz = gridDim.z - 1 - blockIdx.z;
+  const int pair = zz / ksplits, split = zz - pair * ksplits;
   const int rep = nh / nkv;
   const int tok_per_tile = BM / rep;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -475,7 +479,10 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const bool act_a = tok0_a < q_len && ctx >= 0, act_b = tok0_b < q_len && ctx >= 0;
   const int n_tok_a = act_a ? min(tok_per_tile, q_len - tok0_a) : 0, n_tok_b = act_b ? min(tok_per_tile, q_len - tok0_b) : 0;
   const int kend_a = ctx + tok0_a + n_tok_a, kend_b = ctx + tok0_b + n_tok_b;
-  const int n_tiles_a = act_a ? (kend_a + BN2 - 1) / BN2 : 0, n_tiles_b = act_b ? (kend_b + BN2 - 1) / BN2 : 0;
+  const int all_a = act_a ? (kend_a + BN2 - 1) / BN2 : 0, all_b = act_b ? (kend_b + BN2 - 1) / BN2 : 0;
+  // this CTA's key tiles: [j0, j0 + per) of the pair's; below, j counts from j0 and a tile's first key is (j0 + j) BN2
+  const int per = (max(all_a, all_b) + ksplits - 1) / ksplits, j0 = split * per;
+  const int n_tiles_a = min(max(all_a - j0, 0), per), n_tiles_b = min(max(all_b - j0, 0), per);
   const int n_all = max(n_tiles_a, n_tiles_b);         // tile B sees at least what A sees
   const int kend_all = max(act_a ? kend_a : 0, act_b ? kend_b : 0);
   const int pages_per_tile = BN2 / page_size;
@@ -511,7 +518,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int pi = lane;
         unsigned char* sk = skv + (size_t)stage * (K2_BYTES + V2_BYTES);
         unsigned char* sv = sk + K2_BYTES;
-        const int key0 = j * BN2 + pi * page_size;
+        const int key0 = (j0 + j) * BN2 + pi * page_size;
         long long krow = kv_rows, vrow = kv_rows;           // out of bounds: the box reads as zeros
         if (key0 < kend_all) {
           const int blk = key0 / page_size;
@@ -696,7 +703,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t sb_addr = lane_addr + S2_COL + (2 * x + b) * BN2;     // scores, then probabilities
         if (!mbar_wait(smem_u32(&bars->sd_full[x][b]), (uint32_t)((j >> 1) & 1))) { ok = false; break; }
         tc_fence_after();
-        const int key0 = j * BN2;
+        const int key0 = (j0 + j) * BN2;
         const bool need_mask = key0 + BN2 - 1 > ctx + tok0;
         uint32_t v[64];
         tmem_ld64(sb_addr, v);
@@ -748,7 +755,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     for (int j = 0; j < nt && ok; ++j) {
       if (!mbar_wait(smem_u32(&bars->s_full[x]), (uint32_t)(j & 1))) { ok = false; break; }
       tc_fence_after();
-      const int key0 = j * BN2;
+      const int key0 = (j0 + j) * BN2;
       const bool need_mask = key0 + BN2 - 1 > ctx + tok0;     // some row of the tile does not see the whole tile
       // first pass: the row's maximum (tiles left of the diagonal need no mask)
       float mx = -INFINITY;
@@ -824,6 +831,28 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     if (!ok) {
       if (lane == 0) fmx_set_status(status, FMX_WAIT_EXPIRED, 23, blockIdx.x);
+    } else if (ksplits > 1) {
+      // the partial of this split: outputs at the scale m (log2 domain) with their sum l; no tiles: nothing seen
+      if (nt > 0) tc_fence_after();
+      const long long slot = ((long long)split * T + (t0 + tok0 + tok)) * nh + head;
+      float* po = part_o + slot * HD;
+      if (rvalid) {
+        part_ml[slot * 2] = nt > 0 ? m : -INFINITY;
+        part_ml[slot * 2 + 1] = nt > 0 ? l : 0.f;
+      }
+      if (nt > 0) {
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(o_addr + c, v);                      // the whole warp loads; valid rows store
+          tmem_ld_wait();
+          if (rvalid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<uint4*>(po + c + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          }
+        }
+      }
     } else if (nt > 0) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -855,6 +884,35 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
 }
+
+// out[t, h, :] = sum over the splits of their outputs, brought to a common scale, over the sum of their sums.
+__global__ void attn_prefill_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                            const int* __restrict__ row_start, bf16* out, int rows, int nh, int T,
+                                            int ksplits) {
+  pdl_wait();
+  const long long th = blockIdx.x;                       // token * nh + head, tokens of the launch's rows only
+  const int t = (int)(th / nh) + row_start[0];
+  if (t >= row_start[rows]) return;
+  const long long idx = (long long)t * nh + th % nh;
+  float M = -INFINITY;
+  for (int sp = 0; sp < ksplits; ++sp) M = fmaxf(M, part_ml[(((long long)sp * T * nh) + idx) * 2]);
+  const float Mu = M == -INFINITY ? 0.f : M;
+  float L = 0.f;
+  for (int sp = 0; sp < ksplits; ++sp) {
+    const long long slot = (long long)sp * T * nh + idx;
+    L += exp2f(part_ml[slot * 2] - Mu) * part_ml[slot * 2 + 1];
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int sp = 0; sp < ksplits; ++sp) {
+      const long long slot = (long long)sp * T * nh + idx;
+      const float f = exp2f(part_ml[slot * 2] - Mu);
+      acc += f > 0.f ? f * part_o[slot * HD + d] : 0.f;  // a split that saw nothing left its outputs unwritten
+    }
+    out[idx * HD + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
 }  // namespace two
 
 }  // namespace
@@ -866,11 +924,39 @@ FMX_EXPORT int fmx_attn_prefill_tc_available() { return 1; }
 // that divides 128 and is at least 8.  q rows (tokens) are T; the out-of-range part of the
 // last query tile reads as zeros.  variant 1: one query tile per CTA; otherwise two (where the
 // page size divides that kernel's key tile: 128 keys at head size 64, 64 at 128).
+// How many CTAs share the keys of a pair of query tiles: 1 unless the grid of the two-tile kernel would leave more than
+// half of the SMs idle and every share still has eight key tiles to walk; 2 or 4 (one 512-token portion behind 32,768
+// keys: 472 -> 266 us at head size 64, 591 -> 342 us at head size 128; 256 tokens behind 16,384: 242 -> 80 and 299 -> 107).
+FMX_EXPORT int fmx_attn_prefill_tc_plan_splits(int rows, int max_q_len, int max_ctx_after, int nh, int nkv, int sms) {
+  if (sms <= 0) sms = fmx_num_sms();
+  if (rows <= 0 || max_q_len <= 0 || nkv <= 0 || nh % nkv) return 1;
+  const int tok_per_tile = BM / (nh / nkv);
+  const long long pairs = (long long)nkv * rows * ((max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile));
+  const int tiles = (max_ctx_after + two::BN2 - 1) / two::BN2;
+  int s = (int)(sms / (pairs > 0 ? pairs : 1));
+  if (s > 4) s = 4;
+  while (s > 1 && tiles / s < 8) --s;
+  if (s == 3) s = 2;                                  // three shares were slower than two wherever they were timed
+  return s < 1 ? 1 : s;
+}
+
+// Floats of workspace that `ksplits` shares of the keys need for a step of T tokens (0 for one share).
+FMX_EXPORT long long fmx_attn_prefill_tc_scratch_floats(int T, int nh, int ksplits) {
+  return ksplits <= 1 ? 0 : (long long)ksplits * T * nh * (HD + 2);
+}
+
+// ksplits: 0 or 1: every pair of query tiles walks all of its keys; more: that many CTAs share them (the two-tile kernel
+// only), their partials in `scratch` (fmx_attn_prefill_tc_scratch_floats), combined by a second kernel.
 FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, const void* kv, const int* block_tables,
                                    int bt_stride, const int* row_start, const int* row_ctx, void* out, int rows,
                                    int max_q_len, int nh, int nkv, int page_size, long long num_pages, float scale,
-                                   int variant, int* status, cudaStream_t stream) {
+                                   int variant, int* status, int ksplits, float* scratch, long long scratch_floats,
+                                   cudaStream_t stream) {
   if (rows == 0 || max_q_len == 0) return 0;
+  if (ksplits < 1) ksplits = 1;
+  if (ksplits > 1 && (scratch == nullptr || scratch_floats < fmx_attn_prefill_tc_scratch_floats(T, nh, ksplits)))
+    return fmx_fail("fmx_attn_prefill_tc: %d shares of the keys need %lld floats of workspace, %lld given", ksplits,
+                    fmx_attn_prefill_tc_scratch_floats(T, nh, ksplits), scratch_floats);
   if (rows < 0 || nh <= 0 || nkv <= 0 || nh % nkv) return fmx_fail("fmx_attn_prefill_tc: bad sizes rows=%d nh=%d nkv=%d", rows, nh, nkv);
   const int rep = nh / nkv;
   if (rep > 16) return fmx_fail("fmx_attn_prefill_tc: %d query heads per kv head is above 16", rep);
@@ -916,7 +1002,9 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
   // with 32 query heads: 64 CTAs 13.8 us, 128 CTAs 11.7; behind 32,768 keys 476 and 394 us); at head size 128 the
   // two-tile kernel wins even then (587 against 803 us).
   const long long pairs = (long long)nkv * rows * ((max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile));
-  if (variant == 0 && HD == 64 && 2 * pairs <= fmx_num_sms()) variant = 1;      // 0: this choice; 1, 2: the caller's
+  if (variant == 0 && HD == 64 && ksplits <= 1 && 2 * pairs <= fmx_num_sms()) variant = 1;      // 0: this choice; 1, 2: the caller's
+  if (ksplits > 1 && (variant == 1 || two::BN2 % page_size != 0))
+    return fmx_fail("fmx_attn_prefill_tc: only the kernel with two query tiles per CTA shares keys out (page size %d)", page_size);
   if (variant != 1 && two::BN2 % page_size == 0) {      // two query tiles per CTA
     static bool configured2 = false;
     if (!configured2) {
@@ -926,11 +1014,20 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
                                              cudaGetErrorString(e2));
       configured2 = true;
     }
-    dim3 grid2(nkv, rows, (max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile));
+    const long long z = (long long)((max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile)) * ksplits;
+    if (z > 65535) return fmx_fail("fmx_attn_prefill_tc: too many query tiles and shares for one launch");
+    dim3 grid2(nkv, rows, (unsigned)z);
+    float* part_o = scratch;
+    float* part_ml = ksplits > 1 ? scratch + (long long)ksplits * T * nh * HD : nullptr;
     cudaError_t e2 = fmx_launch(two::attn_prefill_tc2_kernel, grid2, dim3(two::THREADS2), two::SMEM2, stream, map_q, map_kv,
                                 block_tables, bt_stride, row_start, row_ctx, (bf16*)out, nh, nkv, page_size, num_pages,
-                                kv_rows, scale, status);
+                                kv_rows, scale, status, ksplits, part_o, part_ml, T);
     if (e2 != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launch failed: %s", cudaGetErrorString(e2));
+    if (ksplits > 1) {
+      e2 = fmx_launch(two::attn_prefill_combine_kernel, dim3((unsigned)((long long)T * nh)), dim3(HD <= 64 ? 64 : 128), 0, stream,
+                      (const float*)part_o, (const float*)part_ml, row_start, (bf16*)out, rows, nh, T, ksplits);
+      if (e2 != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launching the combining kernel failed: %s", cudaGetErrorString(e2));
+    }
     return 0;
   }
   dim3 grid(nkv, rows, (max_q_len + tok_per_tile - 1) / tok_per_tile);
@@ -942,8 +1039,10 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
 #else
 #include "common.cuh"
 FMX_EXPORT int fmx_attn_prefill_tc_available() { return 0; }
+FMX_EXPORT int fmx_attn_prefill_tc_plan_splits(int, int, int, int, int, int) { return 1; }
+FMX_EXPORT long long fmx_attn_prefill_tc_scratch_floats(int, int, int) { return 0; }
 FMX_EXPORT int fmx_attn_prefill_tc(const void*, long long, int, const void*, const int*, int, const int*, const int*, void*,
-                                   int, int, int, int, int, long long, float, int, int*, cudaStream_t) {
+                                   int, int, int, int, int, long long, float, int, int*, int, float*, long long, cudaStream_t) {
   return fmx_fail("fmx_attn_prefill_tc: this head size has no tensor-memory attention kernel");
 }
 #endif

@@ -36,8 +36,10 @@ typedef int (*attn_decode_fn)(const void*, long long, const void*, const int*, i
 typedef int (*attn_prefill_fn)(const void*, long long, const void*, const int*, int, const int*, const int*, void*, int,
                                int, int, int, int, long long, float, int, int*, cudaStream_t);
 typedef int (*attn_prefill_tc_fn)(const void*, long long, int, const void*, const int*, int, const int*, const int*,
-                                  void*, int, int, int, int, int, long long, float, int, int*, cudaStream_t);
+                                  void*, int, int, int, int, int, long long, float, int, int*, int, float*, long long,
+                                  cudaStream_t);
 typedef int (*attn_plan_fn)(int, int, long long, int);
+typedef int (*attn_prefill_tc_plan_fn)(int, int, int, int, int, int);
 typedef int (*gemv_argmax_fn)(const void*, long long, const void*, long long, int*, void*, int*, int, int, int, cudaStream_t);
 
 constexpr int GEMV_MAX_ROWS = 16;            // as kernels/__init__.py names them
@@ -284,9 +286,19 @@ struct Run {
       ++ex.launches;
       if (max_q >= TC_ATTN_MIN_TOKENS && op.tc_attention_ok && op.fn_attn_prefill_tc != nullptr && qstride % 8 == 0 &&
           aligned16(qkv))
+      {
+        // a grid that would leave most SMs idle shares the keys of each pair of query tiles out over several CTAs
+        const int max_ctx = dr > 0 ? d.rest_max_ctx : d.max_ctx_after;
+        int ks = op.fn_attn_prefill_tc_plan != nullptr && (op.hd == 64 ? 128 : 64) % op.page_size == 0
+                     ? ((attn_prefill_tc_plan_fn)op.fn_attn_prefill_tc_plan)(rows, max_q, max_ctx, op.nh, op.nkv, ex.sms)
+                     : 1;
+        if (ks > 1 && (long long)ks * d.T * op.nh * (op.hd + 2) > d.attn_scratch_floats) ks = 1;
+        if (ks > 1) ++ex.launches;
         return ((attn_prefill_tc_fn)op.fn_attn_prefill_tc)(qkv, qstride, d.T, op.kv, rbt, bt_stride, row_start, row_ctx, out,
                                                            rows, max_q, op.nh, op.nkv, op.page_size, op.num_pages,
-                                                           op.scale, 0, d.status, stream);
+                                                           op.scale, ks > 1 ? 2 : 0, d.status, ks, d.attn_scratch,
+                                                           d.attn_scratch_floats, stream);
+      }
       return ((attn_prefill_fn)op.fn_attn_prefill)(qkv, qstride, op.kv, rbt, bt_stride, row_start, row_ctx, out, rows,
                                                    max_q, op.nh, op.nkv, op.page_size, op.num_pages, op.scale,
                                                    op.window, d.status, stream);
@@ -343,7 +355,7 @@ struct Run {
 // ------------------------------------------------------------------------------------ the batch layout
 namespace {
 struct Layout {
-  int R, Rp, T, Tp, max_blocks, max_q, max_ctx, all_decode, decode_rows, decode_max_ctx, rest_max_q;
+  int R, Rp, T, Tp, max_blocks, max_q, max_ctx, all_decode, decode_rows, decode_max_ctx, rest_max_q, rest_max_ctx;
   long long tokens, positions, token_row, row_start, row_ctx, row_slot, want, bt[FMX_MAX_GROUPS], sm[FMX_MAX_GROUPS], total;
 };
 
@@ -375,13 +387,15 @@ int plan_layout(const FmxBatchIn& in, Layout* L) {
   // the one-token rows at the head of a mixed step
   int dr = 0;
   while (dr < in.R && in.q_lens[dr] == 1) ++dr;
-  L->decode_rows = L->decode_max_ctx = L->rest_max_q = 0;
+  L->decode_rows = L->decode_max_ctx = L->rest_max_q = L->rest_max_ctx = 0;
   if (dr > 0 && dr < in.R) {
     L->decode_rows = dr;
     for (int r = 0; r < dr; ++r)
       if (in.ctx_lens[r] + 1 > L->decode_max_ctx) L->decode_max_ctx = in.ctx_lens[r] + 1;
-    for (int r = dr; r < in.R; ++r)
+    for (int r = dr; r < in.R; ++r) {
       if (in.q_lens[r] > L->rest_max_q) L->rest_max_q = in.q_lens[r];
+      if (in.ctx_lens[r] + in.q_lens[r] > L->rest_max_ctx) L->rest_max_ctx = in.ctx_lens[r] + in.q_lens[r];
+    }
   }
   long long at = 0;
   auto take = [&](long long n) { at = (at + 3) / 4 * 4; const long long o = at; at += n; return o; };   // 16-byte starts
@@ -480,7 +494,7 @@ FMX_EXPORT int fmx_exec_layout(const FmxBatchIn* in, int* host, int* dev, long l
   desc->decode_rows = L.decode_rows;
   desc->decode_max_ctx = L.decode_max_ctx;
   desc->rest_max_q_len = L.rest_max_q;
-  desc->reserved_ = 0;
+  desc->rest_max_ctx = L.rest_max_ctx;
   desc->n_splits = 0;
   desc->n_groups = in->n_groups;
   desc->tokens = dev + L.tokens;

@@ -55,6 +55,7 @@ struct FmxOp {
   void* fn_attn_prefill;
   void* fn_attn_prefill_tc;
   void* fn_attn_plan;
+  void* fn_attn_prefill_tc_plan;   // how many CTAs share the keys of a pair of query tiles
   int tc_attention_ok;     // sizes the tensor-memory attention kernel takes (head size, heads per kv head, page size, no window)
 };
 
@@ -78,8 +79,9 @@ struct FmxKernelTable {
 struct FmxStepDesc {
   int T, R, n_want, max_q_len, max_ctx_after, all_decode, n_splits, n_groups;
   // a mixed step whose first rows bring one token each: how many, the longest context among them after the step, and
-  // the longest portion among the rows behind them; all 0 where the step is not mixed so
-  int decode_rows, decode_max_ctx, rest_max_q_len, reserved_;
+  // the longest portion and the longest context after the step among the rows behind them; all 0 where the step is not
+  // mixed so
+  int decode_rows, decode_max_ctx, rest_max_q_len, rest_max_ctx;
   const int* tokens;
   const int* positions;
   const int* token_row;

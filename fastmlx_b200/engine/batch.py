@@ -54,6 +54,7 @@ class StepContext:
     decode_rows: int = 0
     decode_max_ctx: int = 0
     rest_max_q_len: int = 0
+    rest_max_ctx: int = 0
     n_splits: int = 0                  # decode attention: fixed split count (0 = kernel's choice)
     scratch: dict = field(default_factory=dict)
 
@@ -93,7 +94,8 @@ def leading_decode_rows(q_lens, ctxs) -> dict:
         d += 1
     if d == 0 or d == len(q_lens):
         return {}
-    return {"decode_rows": d, "decode_max_ctx": max(c + 1 for c in ctxs[:d]), "rest_max_q_len": max(q_lens[d:])}
+    return {"decode_rows": d, "decode_max_ctx": max(c + 1 for c in ctxs[:d]), "rest_max_q_len": max(q_lens[d:]),
+            "rest_max_ctx": max(c + q for c, q in zip(ctxs[d:], q_lens[d:]))}
 
 
 def build_context(entries, manager, device, status, *, pad_rows: int = 0, pad_blocks: int = 0,

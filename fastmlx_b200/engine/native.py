@@ -44,7 +44,8 @@ class FmxOp(Structure):
                 ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("rot", c_int), ("trad", c_int),
                 ("store", c_int), ("group", c_int), ("share_kv", c_int), ("kv", c_void_p), ("page_size", c_int),
                 ("num_pages", c_longlong), ("fn_attn_decode", c_void_p), ("fn_attn_prefill", c_void_p),
-                ("fn_attn_prefill_tc", c_void_p), ("fn_attn_plan", c_void_p), ("tc_attention_ok", c_int)]
+                ("fn_attn_prefill_tc", c_void_p), ("fn_attn_plan", c_void_p), ("fn_attn_prefill_tc_plan", c_void_p),
+                ("tc_attention_ok", c_int)]
 
 
 class FmxKernelTable(Structure):
@@ -56,7 +57,7 @@ class FmxKernelTable(Structure):
 class FmxStepDesc(Structure):
     _fields_ = [("T", c_int), ("R", c_int), ("n_want", c_int), ("max_q_len", c_int), ("max_ctx_after", c_int),
                 ("all_decode", c_int), ("n_splits", c_int), ("n_groups", c_int),
-                ("decode_rows", c_int), ("decode_max_ctx", c_int), ("rest_max_q_len", c_int), ("reserved_", c_int),
+                ("decode_rows", c_int), ("decode_max_ctx", c_int), ("rest_max_q_len", c_int), ("rest_max_ctx", c_int),
                 ("tokens", c_void_p), ("positions", c_void_p), ("token_row", c_void_p), ("row_start", c_void_p),
                 ("row_ctx", c_void_p), ("row_slot", c_void_p), ("want", c_void_p),
                 ("block_tables", c_void_p * MAX_GROUPS), ("bt_stride", c_int * MAX_GROUPS),
@@ -302,6 +303,7 @@ class NativeProgram:
         d.all_decode, d.n_splits, d.n_groups = int(bool(ctx.all_decode)), int(ctx.n_splits), len(ctx.groups)
         d.decode_rows, d.decode_max_ctx, d.rest_max_q_len = (int(getattr(ctx, "decode_rows", 0)), int(getattr(ctx, "decode_max_ctx", 0)),
                                                              int(getattr(ctx, "rest_max_q_len", 0)))
+        d.rest_max_ctx = int(getattr(ctx, "rest_max_ctx", 0))
         d.tokens, d.positions, d.token_row = ctx.tokens.data_ptr(), ctx.positions.data_ptr(), ctx.token_row.data_ptr()
         d.row_start, d.row_ctx, d.row_slot = ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), ctx.row_slot.data_ptr()
         d.want = ctx.logit_rows.data_ptr() if n_want else None

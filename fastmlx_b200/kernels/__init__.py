@@ -404,16 +404,28 @@ def tc_attention_ok(nh: int, nkv: int, hd: int, page_size: int, window: int) -> 
             and page_size >= 8 and 128 % page_size == 0)
 
 
-def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale, variant: int = 0, out=None) -> torch.Tensor:
+def paged_attention_prefill_tc(qkv, kv, ctx, group, nh, nkv, hd, scale, variant: int = 0, out=None, ksplits=None) -> torch.Tensor:
     """Causal attention of prompt portions on the tcgen05 tensor cores (TMA-fed, scores and
-    outputs in tensor memory)."""
+    outputs in tensor memory).  variant 0: the library's choice of kernel, 1: one query tile per
+    CTA, 2: two.  ksplits: how many CTAs share the keys of a pair of query tiles (the two-tile
+    kernel; None: as many as the library plans for a grid that would leave most SMs idle)."""
     T = qkv.shape[0]
     if out is None:
         out = torch.empty((T, nh * hd), dtype=qkv.dtype, device=qkv.device)
     bt = group.block_tables
+    lib = load(f"attn_hd{hd}")
+    if ksplits is None:
+        ksplits = 1
+        if variant != 1 and (128 if hd == 64 else 64) % kv.shape[3] == 0:
+            ksplits = int(lib.fmx_attn_prefill_tc_plan_splits(int(ctx.R), int(ctx.max_q_len), int(ctx.max_ctx_after), nh, nkv,
+                                                               num_sms(qkv.device)))
+            if ksplits > 1 and int(lib.fmx_attn_prefill_tc_scratch_floats(T, nh, ksplits)) > ATTN_SCRATCH_FLOATS:
+                ksplits = 1
+    scratch = attention_scratch(qkv.device, int(lib.fmx_attn_prefill_tc_scratch_floats(T, nh, ksplits))) if ksplits > 1 else None
     call(f"attn_hd{hd}", "fmx_attn_prefill_tc", qkv.data_ptr(), qkv.stride(0), T, kv.data_ptr(), bt.data_ptr(),
          bt.stride(0), ctx.row_start.data_ptr(), ctx.row_ctx.data_ptr(), out.data_ptr(), ctx.R, int(ctx.max_q_len), nh,
-         nkv, kv.shape[3], kv.shape[0], float(scale), int(variant), _ptr(ctx.status), _stream())
+         nkv, kv.shape[3], kv.shape[0], float(scale), int(2 if ksplits > 1 else variant), _ptr(ctx.status), int(ksplits),
+         _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream())
     return out
 
 
@@ -462,7 +474,7 @@ def paged_attention(qkv, kv, ctx, group, nh, nkv, hd, scale, window, rope=None) 
         views = ctx.scratch.get(key)
         if views is None:
             views = ctx.scratch[key] = (_rows_of(ctx, group, 0, d, 1, ctx.decode_max_ctx),
-                                        _rows_of(ctx, group, d, ctx.R, ctx.rest_max_q_len, ctx.max_ctx_after))
+                                        _rows_of(ctx, group, d, ctx.R, ctx.rest_max_q_len, ctx.rest_max_ctx))
         (dctx, dgroup), (ctx, group) = views
         out = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
         paged_attention_decode(qkv, kv, dctx, dgroup, nh, nkv, hd, scale, window, out=out)

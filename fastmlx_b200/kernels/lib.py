@@ -41,7 +41,7 @@ _SIGNATURES = {
         "fmx_gemm_tcgen05": [_P, _L, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     },
     "attn": {
-        "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
+        "fmx_attn_prefill_tc": [_P, _L, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _I, _P, _L, _P],
         "fmx_attn_prefill": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P],
         "fmx_attn_decode": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I, _I, _P],
     },
@@ -65,6 +65,9 @@ def load(group: str) -> ctypes.CDLL:
         lib.fmx_attn_decode_scratch_floats.restype = c_longlong
         lib.fmx_attn_decode_plan.argtypes = [_I, _I, _L, _I]
         lib.fmx_attn_decode_plan.restype = c_int
+        lib.fmx_attn_prefill_tc_plan_splits.argtypes = [_I, _I, _I, _I, _I, _I]
+        lib.fmx_attn_prefill_tc_scratch_floats.argtypes = [_I, _I, _I]
+        lib.fmx_attn_prefill_tc_scratch_floats.restype = c_longlong
     if group == "bf16":
         lib.fmx_gemv_plan_width.argtypes = [_I, _I, _I]
         lib.fmx_gemv_plan_warps.argtypes = [_I, _I, _I, _I]

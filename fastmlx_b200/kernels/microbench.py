@@ -101,7 +101,14 @@ def main(argv=None) -> int:
                           lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, variant=1)))
             if (128 if a.hd == 64 else 64) % a.page == 0:
                 impls.append(("tcgen05, two query tiles per CTA",
-                              lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, variant=2)))
+                              lambda: k.paged_attention_prefill_tc(qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, variant=2, ksplits=1)))
+                for ks in (2, 4):
+                    if ks * qkv.shape[0] * a.nh * (a.hd + 2) > k.ATTN_SCRATCH_FLOATS:
+                        continue
+                    impls.append((f"tcgen05, two query tiles per CTA, keys in {ks} shares", (lambda ks: lambda: k.paged_attention_prefill_tc(
+                        qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5, variant=2, ksplits=ks))(ks)))
+                impls.append(("tcgen05, the library's choice", lambda: k.paged_attention_prefill_tc(
+                    qkv, kv, ctx, grp, a.nh, a.nkv, a.hd, a.hd ** -0.5)))
         for name, f in impls:
             us = _time_graph(f, a.launches, a.replays)
             print(f"attn_prefill {name} B={a.batch} ctx={a.ctx} qlen={a.qlen} nh={a.nh} nkv={a.nkv} hd={a.hd}: {us:.1f} us, "

@@ -79,7 +79,8 @@ class GQAAttention(Mixer):
         if b.act == BF16 and kv.dtype == self.rt.dtype and self.hd % 16 == 0 and self.hd <= 256:
             lib = klib.load(f"attn_hd{self.hd}")
             fns = dict(fn_attn_decode=_fn(lib, "fmx_attn_decode"), fn_attn_prefill=_fn(lib, "fmx_attn_prefill"),
-                       fn_attn_prefill_tc=_fn(lib, "fmx_attn_prefill_tc"), fn_attn_plan=_fn(lib, "fmx_attn_decode_plan"))
+                       fn_attn_prefill_tc=_fn(lib, "fmx_attn_prefill_tc"), fn_attn_plan=_fn(lib, "fmx_attn_decode_plan"),
+                       fn_attn_prefill_tc_plan=_fn(lib, "fmx_attn_prefill_tc_plan_splits"))
             tc_ok = int(bool(lib.fmx_attn_prefill_tc_available())
                         and self.rt.k.tc_attention_ok(self.nh, self.nkv, self.hd, page_size, self.window))
         b.op(OP_ATTENTION, in0=qkv, out0=out, vec=b.ptr(inv_freq), nh=self.nh, nkv=self.nkv, hd=self.hd, window=self.window,

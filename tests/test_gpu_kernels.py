@@ -446,7 +446,8 @@ def test_mixed_step_attention_takes_two_kernels(nh, nkv, hd, page_size, window, 
     dctx, dgrp = _full_ctx(rows, ctx, grp)
     for name, value in leading_decode_rows([ql for _, ql in rows], [c for c, _ in rows]).items():
         setattr(dctx, name, value)
-    assert dctx.decode_rows == 4 and dctx.decode_max_ctx == 1001 and dctx.rest_max_q_len == portion
+    assert dctx.decode_rows == 4 and dctx.decode_max_ctx == 1001 and dctx.rest_max_q_len == portion \
+        and dctx.rest_max_ctx == 200 + portion
     dctx.scratch = {}
     before = k().launch_count()
     got = k().paged_attention(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, window)
@@ -553,6 +554,34 @@ def test_tensor_memory_prefill_attention(nh, nkv, hd, page_size, variant):
     got = k().paged_attention_prefill_tc(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, variant=variant)
     assert dctx.status.tolist()[0] == 0
     close(got, ref, torch.bfloat16, "tensor-memory attention", scale=1.0, extra=P_ROUNDING * kv.abs().max().item())
+
+
+@pytest.mark.parametrize("ksplits", [2, 3, 4])
+@pytest.mark.parametrize("nh,nkv,hd,page_size", [s for s in TC_SHAPES if (128 if s[2] == 64 else 64) % s[3] == 0])
+def test_tensor_memory_attention_shares_keys_out(nh, nkv, hd, page_size, ksplits):
+    """The keys of a pair of query tiles shared out over several CTAs and combined by a second
+    kernel: rows whose keys end in the first share (the others then bring nothing), rows that
+    reach into every share, a portion behind a long context, single tokens."""
+    rows = [(0, 37), (1500, 130), (90, 1), (700, 2), (0, 300), (2000, 64), (64, 1)]
+    q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows)
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, 0)
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    got = k().paged_attention_prefill_tc(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5, variant=2, ksplits=ksplits)
+    assert dctx.status.tolist()[0] == 0
+    close(got, ref, torch.bfloat16, f"tensor-memory attention, keys in {ksplits} shares", scale=1.0,
+          extra=P_ROUNDING * kv.abs().max().item())
+    # one long portion alone: the library plans the shares itself
+    rows = [(3000, 200)]
+    q, kv, ctx, grp = _attention_case(torch.bfloat16, nh, nkv, hd, page_size, rows, seed=3, spike=(150, 40, nh - 1))
+    ref = plain_ops.paged_attention(q, kv, ctx, grp, nh, nkv, hd, hd ** -0.5, 0)
+    dctx, dgrp = _full_ctx(rows, ctx, grp)
+    from fastmlx_b200.kernels.lib import load
+    planned = load(f"attn_hd{hd}").fmx_attn_prefill_tc_plan_splits(1, 200, 3200, nh, nkv, k().num_sms())
+    assert planned > 1
+    got = k().paged_attention_prefill_tc(q.to(DEV), kv.to(DEV), dctx, dgrp, nh, nkv, hd, hd ** -0.5)
+    assert dctx.status.tolist()[0] == 0
+    close(got, ref, torch.bfloat16, "tensor-memory attention, planned shares, a far key that stands out", scale=1.0,
+          extra=P_ROUNDING * kv.abs().max().item())
 
 
 @pytest.mark.parametrize("variant", [1, 2])

@@ -138,7 +138,8 @@ def test_the_native_layout_is_the_python_layout():
         torch.cuda.synchronize()
         assert (d.T, d.R, d.n_want, d.max_q_len, d.max_ctx_after, d.all_decode) == \
             (ctx.T, ctx.R, 4, ctx.max_q_len, ctx.max_ctx_after, int(ctx.all_decode))
-        assert (d.decode_rows, d.decode_max_ctx, d.rest_max_q_len) == (ctx.decode_rows, ctx.decode_max_ctx, ctx.rest_max_q_len)
+        assert (d.decode_rows, d.decode_max_ctx, d.rest_max_q_len, d.rest_max_ctx) == \
+            (ctx.decode_rows, ctx.decode_max_ctx, ctx.rest_max_q_len, ctx.rest_max_ctx)
 
         def arr(ptr, n, dtype=torch.int32):
             off = (ptr - dev.data_ptr()) // 4
@@ -221,7 +222,8 @@ def test_the_native_layout_is_the_python_layout_on_random_steps(seed):
             o = (ptr - dev.data_ptr()) // 4
             return dev[o: o + n * (2 if dtype == torch.int64 else 1)].view(dtype).cpu()
         assert (d.T, d.R, d.max_q_len, d.max_ctx_after, d.all_decode) == (ctx.T, ctx.R, ctx.max_q_len, ctx.max_ctx_after, int(ctx.all_decode))
-        assert (d.decode_rows, d.decode_max_ctx, d.rest_max_q_len) == (ctx.decode_rows, ctx.decode_max_ctx, ctx.rest_max_q_len)
+        assert (d.decode_rows, d.decode_max_ctx, d.rest_max_q_len, d.rest_max_ctx) == \
+            (ctx.decode_rows, ctx.decode_max_ctx, ctx.rest_max_q_len, ctx.rest_max_ctx)
         for name, n in (("tokens", d.T), ("positions", d.T), ("token_row", d.T), ("row_start", d.R + 1), ("row_ctx", d.R),
                         ("row_slot", d.R)):
             assert torch.equal(arr(getattr(d, name), n), getattr(ctx, name).cpu()), (step, name)

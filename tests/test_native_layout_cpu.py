@@ -75,7 +75,8 @@ def test_native_layout_matches_build_context_on_the_cpu(seed):
             return host[o: o + n * (2 if dtype == np.int64 else 1)].view(dtype)
         assert (d.T, d.R, d.n_want, d.max_q_len, d.max_ctx_after, d.all_decode) == \
             (ctx.T, ctx.R, len(want), ctx.max_q_len, ctx.max_ctx_after, int(ctx.all_decode))
-        assert (d.decode_rows, d.decode_max_ctx, d.rest_max_q_len) == (ctx.decode_rows, ctx.decode_max_ctx, ctx.rest_max_q_len)
+        assert (d.decode_rows, d.decode_max_ctx, d.rest_max_q_len, d.rest_max_ctx) == \
+            (ctx.decode_rows, ctx.decode_max_ctx, ctx.rest_max_q_len, ctx.rest_max_ctx)
         for name, n in (("tokens", d.T), ("positions", d.T), ("token_row", d.T), ("row_start", d.R + 1), ("row_ctx", d.R),
                         ("row_slot", d.R)):
             assert np.array_equal(arr(getattr(d, name), n), getattr(ctx, name).numpy()), (step, name)
