@@ -885,32 +885,52 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   }
 }
 
-// out[t, h, :] = sum over the splits of their outputs, brought to a common scale, over the sum of their sums.
-__global__ void attn_prefill_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                            const int* __restrict__ row_start, bf16* out, int rows, int nh, int T,
-                                            int ksplits) {
+// out[t, h, :] = sum over the shares of their outputs, brought to a common scale, over the sum of their sums.  One block
+// per token: the shares' scales and sums of all heads go to shared memory first, then every thread walks (head, dim)
+// pairs with consecutive threads on consecutive dims.
+constexpr int COMBINE_THREADS = 256, COMBINE_MAX_HEADS = 256;
+__global__ void __launch_bounds__(COMBINE_THREADS)
+attn_prefill_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                            const int* __restrict__ row_start, bf16* out, int rows, int nh, int T, int ksplits) {
+  __shared__ float weight[4][COMBINE_MAX_HEADS];         // per share and head: 2^(m - M) / L
   pdl_wait();
-  const long long th = blockIdx.x;                       // token * nh + head, tokens of the launch's rows only
-  const int t = (int)(th / nh) + row_start[0];
+  const int t = (int)blockIdx.x + row_start[0];          // tokens of the launch's rows only
   if (t >= row_start[rows]) return;
-  const long long idx = (long long)t * nh + th % nh;
-  float M = -INFINITY;
-  for (int sp = 0; sp < ksplits; ++sp) M = fmaxf(M, part_ml[(((long long)sp * T * nh) + idx) * 2]);
-  const float Mu = M == -INFINITY ? 0.f : M;
-  float L = 0.f;
-  for (int sp = 0; sp < ksplits; ++sp) {
-    const long long slot = (long long)sp * T * nh + idx;
-    L += exp2f(part_ml[slot * 2] - Mu) * part_ml[slot * 2 + 1];
-  }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float acc = 0.f;
-    for (int sp = 0; sp < ksplits; ++sp) {
-      const long long slot = (long long)sp * T * nh + idx;
-      const float f = exp2f(part_ml[slot * 2] - Mu);
-      acc += f > 0.f ? f * part_o[slot * HD + d] : 0.f;  // a split that saw nothing left its outputs unwritten
+  for (int h = threadIdx.x; h < nh; h += COMBINE_THREADS) {
+    const long long idx = (long long)t * nh + h;
+    float m[4], l[4], M = -INFINITY;
+#pragma unroll
+    for (int sp = 0; sp < 4; ++sp) {
+      const bool on = sp < ksplits;
+      m[sp] = on ? part_ml[((long long)sp * T * nh + idx) * 2] : -INFINITY;
+      l[sp] = on ? part_ml[((long long)sp * T * nh + idx) * 2 + 1] : 0.f;
+      M = fmaxf(M, m[sp]);
     }
-    out[idx * HD + d] = __float2bfloat16_rn(acc * inv);
+    const float Mu = M == -INFINITY ? 0.f : M;
+    float L = 0.f;
+#pragma unroll
+    for (int sp = 0; sp < 4; ++sp) L += exp2f(m[sp] - Mu) * l[sp];
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+    for (int sp = 0; sp < 4; ++sp) weight[sp][h] = exp2f(m[sp] - Mu) * inv;
+  }
+  __syncthreads();
+  const int per_token = nh * HD;
+  for (int e = 4 * threadIdx.x; e < per_token; e += 4 * COMBINE_THREADS) {       // HD is a multiple of 16: four dims of one head
+    const int h = e / HD;
+    const long long at = (long long)t * per_token + e;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp = 0; sp < ksplits; ++sp) {
+      const float w = weight[sp][h];
+      if (w > 0.f) {                                     // a share that saw nothing left its outputs unwritten
+        const float4 v = *reinterpret_cast<const float4*>(part_o + (long long)sp * T * per_token + at);
+        acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+      }
+    }
+    uint2 packed;
+    packed.x = pack2(acc.x, acc.y);
+    packed.y = pack2(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(out + at) = packed;
   }
 }
 }  // namespace two
@@ -925,17 +945,18 @@ FMX_EXPORT int fmx_attn_prefill_tc_available() { return 1; }
 // last query tile reads as zeros.  variant 1: one query tile per CTA; otherwise two (where the
 // page size divides that kernel's key tile: 128 keys at head size 64, 64 at 128).
 // How many CTAs share the keys of a pair of query tiles: 1 unless the grid of the two-tile kernel would leave more than
-// half of the SMs idle and every share still has eight key tiles to walk; 2 or 4 (one 512-token portion behind 32,768
-// keys: 472 -> 266 us at head size 64, 591 -> 342 us at head size 128; 256 tokens behind 16,384: 242 -> 80 and 299 -> 107).
+// half of the SMs idle and every share still has 768 keys to walk; 2 or 4.  One 512-token portion at head size 64 / 128,
+// microseconds: behind 1,024 keys 28 -> 23 / 35 -> 29, behind 4,096 keys 70 -> 45 / 89 -> 58, behind 16,384 keys
+// 240 -> 132 / 305 -> 167; with nothing behind it 14 -> 15 / 16 -> 19, which is why short contexts are left alone.
 FMX_EXPORT int fmx_attn_prefill_tc_plan_splits(int rows, int max_q_len, int max_ctx_after, int nh, int nkv, int sms) {
   if (sms <= 0) sms = fmx_num_sms();
-  if (rows <= 0 || max_q_len <= 0 || nkv <= 0 || nh % nkv) return 1;
+  if (rows <= 0 || max_q_len <= 0 || nkv <= 0 || nh % nkv || nh > two::COMBINE_MAX_HEADS) return 1;
   const int tok_per_tile = BM / (nh / nkv);
   const long long pairs = (long long)nkv * rows * ((max_q_len + 2 * tok_per_tile - 1) / (2 * tok_per_tile));
   const int tiles = (max_ctx_after + two::BN2 - 1) / two::BN2;
   int s = (int)(sms / (pairs > 0 ? pairs : 1));
   if (s > 4) s = 4;
-  while (s > 1 && tiles / s < 8) --s;
+  while (s > 1 && tiles / s < 768 / two::BN2) --s;      // a share walks at least 768 keys
   if (s == 3) s = 2;                                  // three shares were slower than two wherever they were timed
   return s < 1 ? 1 : s;
 }
@@ -954,6 +975,8 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
                                    cudaStream_t stream) {
   if (rows == 0 || max_q_len == 0) return 0;
   if (ksplits < 1) ksplits = 1;
+  if (ksplits > 4 || (ksplits > 1 && nh > two::COMBINE_MAX_HEADS))
+    return fmx_fail("fmx_attn_prefill_tc: at most 4 shares of the keys and %d heads with them (asked: %d, %d)", two::COMBINE_MAX_HEADS, ksplits, nh);
   if (ksplits > 1 && (scratch == nullptr || scratch_floats < fmx_attn_prefill_tc_scratch_floats(T, nh, ksplits)))
     return fmx_fail("fmx_attn_prefill_tc: %d shares of the keys need %lld floats of workspace, %lld given", ksplits,
                     fmx_attn_prefill_tc_scratch_floats(T, nh, ksplits), scratch_floats);
@@ -1024,7 +1047,7 @@ FMX_EXPORT int fmx_attn_prefill_tc(const void* q, long long q_stride, int T, con
                                 kv_rows, scale, status, ksplits, part_o, part_ml, T);
     if (e2 != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launch failed: %s", cudaGetErrorString(e2));
     if (ksplits > 1) {
-      e2 = fmx_launch(two::attn_prefill_combine_kernel, dim3((unsigned)((long long)T * nh)), dim3(HD <= 64 ? 64 : 128), 0, stream,
+      e2 = fmx_launch(two::attn_prefill_combine_kernel, dim3((unsigned)T), dim3(two::COMBINE_THREADS), 0, stream,
                       (const float*)part_o, (const float*)part_ml, row_start, (bf16*)out, rows, nh, T, ksplits);
       if (e2 != cudaSuccess) return fmx_fail("fmx_attn_prefill_tc: launching the combining kernel failed: %s", cudaGetErrorString(e2));
     }
