@@ -38,6 +38,7 @@ struct GreedyOut {
   unsigned long long* best;      // [16], zero between launches
   int* ticket;                   // [1], zero between launches
   int* ids;                      // [M]
+  int blocks;                    // feature blocks of the product; the grid may be smaller and then walks them
 };
 __device__ __forceinline__ unsigned long long greedy_key(float v, int n) {
   unsigned u = __float_as_uint(v);
@@ -49,11 +50,18 @@ template <int NT, bool HI, bool DUAL, int U, int WARPS, typename TO, bool GREEDY
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long ldw, const float* __restrict__ bias,
             const bf16* residual, long long ldr, TO* out, long long ldo, int M, int N, int K, int blk,
-            GreedyOut greedy = GreedyOut{nullptr, nullptr, nullptr}) {
+            GreedyOut greedy = GreedyOut{nullptr, nullptr, nullptr, 0}) {
   constexpr int TILES = DUAL ? 2 * NT : NT;
   constexpr int ROWS = HI ? 16 : 8;
   __shared__ float red[WARPS][TILES][ROWS][9];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  // The greedy head walks its feature blocks with a grid that is resident at once (a vocabulary of 128,256 makes
+  // 4,008 blocks): a block asks for the first W tiles of its next feature block before it reduces the one it has
+  // just summed, so the reduction and the next block's first loads overlap.  Every other product: one feature
+  // block per thread block.
+  constexpr bool WALK = GREEDY;
+  int vb = blockIdx.x;
+  const int n_vb = WALK ? greedy.blocks : (int)gridDim.x;
   // the first W row of each tile, and the first output column of the block
   int row0[TILES], out0;
   if (DUAL) {
@@ -67,7 +75,7 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
     out0 = b * blk + j0;
   } else {
 #pragma unroll
-    for (int i = 0; i < TILES; ++i) row0[i] = blockIdx.x * 8 * NT + 8 * i;
+    for (int i = 0; i < TILES; ++i) row0[i] = vb * 8 * NT + 8 * i;
     out0 = row0[0];
   }
   const int n_out = DUAL ? N / 2 : N;
@@ -98,6 +106,8 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
   int kb = warp;
   if (kb < nkb) load_w(kb);                       // W is never written by a kernel: ahead of the wait
   pdl_wait();                                     // x is; it is read through plain loads, after the wait
+  __shared__ int drew_last;
+  while (true) {
   for (; kb < nkb; kb += WARPS * U) {
     uint4 alo[U], ahi[U];
 #pragma unroll
@@ -116,7 +126,18 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
       }
     if (kb + WARPS * U < nkb) load_w(kb + WARPS * U);
   }
-  pdl_trigger();                                  // the block's loads are done: room for the next kernel's
+  const int out_now = out0;
+  const bool more = WALK && vb + (int)gridDim.x < n_vb;
+  if (more) {                                     // the next feature block's first tiles, under the reduction below
+    vb += gridDim.x;
+    out0 = vb * 8 * NT;
+#pragma unroll
+    for (int i = 0; i < TILES; ++i) wp[i] = W + (long long)min(out0 + 8 * i + g, N - 1) * ldw + 8 * t;
+    kb = warp;
+    if (kb < nkb) load_w(kb);
+  } else {
+    pdl_trigger();                                // the block's loads are done: room for the next kernel's
+  }
 #pragma unroll
   for (int i = 0; i < TILES; ++i) {
     red[warp][i][g][2 * t] = acc[i][0];
@@ -129,7 +150,7 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
   __syncthreads();
   for (int idx = threadIdx.x; idx < NT * ROWS * 8; idx += WARPS * 32) {
     const int f = idx & 7, rest = idx >> 3, i = rest % NT, tok = rest / NT;      // consecutive threads: consecutive features
-    const int n = out0 + 8 * i + f;
+    const int n = out_now + 8 * i + f;
     if (GREEDY) {
       // the row's 8 * NT logits of this block sit in consecutive lanes of whole warps: their best by a
       // shuffle tree, then one atomicMax per row and block
@@ -160,10 +181,16 @@ gemv_kernel(const bf16* x, long long ldx, const bf16* __restrict__ W, long long 
     if (residual != nullptr) v = bf16r(v) + __bfloat162float(residual[(long long)tok * ldr + n]);
     store_out<TO>(out + (long long)tok * ldo + n, v);
   }
+  if (!more) break;
+  __syncthreads();                                // the sums in `red` are read; the next feature block may write them
+#pragma unroll
+  for (int i = 0; i < TILES; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+  }
   if (GREEDY) {
     // The block that draws the last ticket turns the rows' best words into ids and leaves the words and
     // the ticket at zero for the next launch.  Nobody waits for anybody.
-    __shared__ int drew_last;
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence();
@@ -186,7 +213,7 @@ void launch(const void* x, long long ldx, const void* W, long long ldw, const fl
   const int n_out = DUAL ? N / 2 : N;
   fmx_launch(gemv_kernel<NT, HI, DUAL, U, WARPS, TO>, dim3((n_out + 8 * NT - 1) / (8 * NT)), dim3(WARPS * 32), 0, stream,
              (const bf16*)x, ldx, (const bf16*)W, ldw, bias, (const bf16*)residual, ldr, (TO*)out, ldo, M, N, K, blk,
-             GreedyOut{nullptr, nullptr, nullptr});
+             GreedyOut{nullptr, nullptr, nullptr, 0});
 }
 }  // namespace
 
@@ -201,8 +228,10 @@ FMX_EXPORT int fmx_gemv_argmax(const void* x, long long ldx, const void* W, long
   if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15))
     return fmx_fail("fmx_gemv_argmax: rows must be 16-byte aligned (K=%d ldx=%lld ldw=%lld)", K, ldx, ldw);
   if (ids == nullptr || best == nullptr || ticket == nullptr || ((uintptr_t)best & 7)) return fmx_fail("fmx_gemv_argmax: needs ids, best words and a ticket");
-  const GreedyOut g{(unsigned long long*)best, ticket, ids};
-  const dim3 grid((N + 31) / 32);
+  const int blocks = (N + 31) / 32;
+  const GreedyOut g{(unsigned long long*)best, ticket, ids, blocks};
+  const int resident = 2 * fmx_num_sms();          // two blocks of 256 threads and about 124 registers fit an SM
+  const dim3 grid(blocks < resident ? blocks : resident);
   if (M > 8)
     fmx_launch(gemv_kernel<4, true, false, 2, 8, float, true>, grid, dim3(256), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw,
                (const float*)nullptr, (const bf16*)nullptr, 0LL, (float*)nullptr, 0LL, M, N, K, 0, g);

@@ -273,7 +273,7 @@ class NativeProgram:
 
     def _finish_desc(self, d: FmxStepDesc, arena: torch.Tensor, n_want: int, greedy: bool = False):
         """-> (the step's result tensor, whether the ids still have to be chosen from it)."""
-        fused = greedy and self.greedy_ok and 0 < n_want <= 16
+        fused = greedy and self.greedy_ok and 0 < n_want <= getattr(self.rt.k, "GREEDY_HEAD_MAX_ROWS", 8)
         if fused:
             result = torch.empty(n_want, dtype=torch.int32, device=self.rt.device)
             d.greedy_ids = result.data_ptr()
